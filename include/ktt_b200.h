@@ -1,0 +1,187 @@
+/* C ABI of the B200 flash-attention library (libktt_b200.so).
+ *
+ * Torch-free: every tensor crosses as a raw device pointer plus element strides, every
+ * scalar as a plain C type. The caller owns and allocates all memory (outputs, softmax
+ * statistics, gradients, workspaces); the library only launches kernels on the stream
+ * it is given. Convention follows the reference's C ABI
+ * (src/kohakutt_native/csrc/py_bridge/ktt_capi.h:1-16): a call returns 0 on success
+ * and a negative status on failure, with the message in a thread-local buffer read by
+ * ktt_b200_last_error(); nothing throws across the boundary.
+ *
+ * All tensors are bf16 unless noted; the innermost (head-dim) stride must be 1.
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KTT_B200_API __attribute__((visibility("default")))
+#define KTT_B200_ABI_VERSION 1
+
+/* Status codes (all failures are negative). */
+enum {
+    KTT_B200_OK = 0,
+    KTT_B200_ERR_UNSUPPORTED = -1, /* shape / dtype / layout the kernels do not take */
+    KTT_B200_ERR_BAD_ARGUMENT = -2, /* null pointer, negative size, bad lengths */
+    KTT_B200_ERR_LAUNCH = -3,       /* a CUDA call or kernel launch failed */
+    KTT_B200_ERR_DEVICE_WAIT = -4,  /* a bounded in-kernel wait ran out */
+};
+
+/* Mask element types of ktt_b200_attn_args.mask_dtype. */
+enum {
+    KTT_B200_MASK_NONE = 0,
+    KTT_B200_MASK_BOOL = 1, /* uint8, nonzero keeps the key */
+    KTT_B200_MASK_BF16 = 2, /* additive */
+    KTT_B200_MASK_F32 = 3,  /* additive */
+    KTT_B200_MASK_F16 = 4,  /* additive */
+};
+
+/* Causal alignment. Dense calls are top-left (query i sees keys <= i,
+ * aten_attention.cpp:431-436); packed calls are bottom-right (query r of a sequence
+ * sees its first min(Lk, r + 1 + Lk - Lq) keys, ktt_flash/varlen_plan.hpp:40-42,70). */
+enum {
+    KTT_B200_CAUSAL_NONE = 0,
+    KTT_B200_CAUSAL_TOP_LEFT = 1,
+    KTT_B200_CAUSAL_BOTTOM_RIGHT = 2,
+};
+
+/* Kernel choice of ktt_b200_attn_args.kernel. */
+enum {
+    KTT_B200_KERNEL_AUTO = 0,
+    KTT_B200_KERNEL_MMA = 1,  /* general warp-MMA kernels: any head dim <= 256, masks */
+    KTT_B200_KERNEL_TC5 = 2,  /* TMA + tcgen05/TMEM kernels: head dim 64 / 128 */
+};
+
+/* One attention problem, dense ([B, H, S, D] with arbitrary batch/head/row strides, so
+ * head views of [B, S, H*D] storages are read in place) or packed ([T, H, D] with
+ * cu_seqlens). Strides are in elements, ordered (batch, head, row); packed calls pass
+ * batch stride 0 and rows are offset by cu_seqlens[b].
+ *
+ * Replaces the operand list of bridge::sdpa / sdpa_train / sdpa_varlen / sdpa_lengths
+ * (src/kohakutt_native/csrc/core/device/tt_bridge.hpp:925-1095). */
+typedef struct ktt_b200_attn_args {
+    int32_t batch;     /* B, or the number of packed sequences */
+    int32_t heads;     /* H query heads */
+    int32_t kv_heads;  /* Hk, divides H */
+    int32_t sq;        /* query rows per batch; packed: the longest sequence (max_q) */
+    int32_t sk;        /* key rows per batch; packed: max_k */
+    int64_t total_q;   /* packed: rows of q (Tq); dense: ignored */
+    int64_t total_k;   /* packed: rows of k and v (Tk); dense: ignored */
+    int32_t d;         /* head dim of q and k */
+    int32_t dv;        /* head dim of v and out */
+    int32_t causal;    /* KTT_B200_CAUSAL_* */
+    float scale;       /* softmax scale (multiplies q.k) */
+    int32_t kernel;    /* KTT_B200_KERNEL_* */
+
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;         /* bf16, caller-allocated */
+    float* lse;        /* natural-log row log-sum-exp, fp32; may be NULL on forward */
+    int64_t q_strides[3];
+    int64_t k_strides[3];
+    int64_t v_strides[3];
+    int64_t out_strides[3];
+    int64_t lse_strides[3]; /* dense [B,H,Sq]: (H*Sq, Sq, 1); packed [H,Tq]: (0, Tq, 1) */
+
+    /* Optional mask broadcastable to [B, H, Sq, Sk]; stride 0 broadcasts a dim. For a
+     * packed call the key index is the packed key index (mask [Tk], strides 0,0,0,1).
+     * Additive values are clamped below at -5e5; a bool mask turns a dropped key's
+     * logit into -5e5 (ktt_flash/varlen_plan.hpp:12-17, program.cpp:912-919). */
+    const void* mask;
+    int32_t mask_dtype; /* KTT_B200_MASK_* */
+    int64_t mask_strides[4];
+
+    /* Optional per-batch key counts, int32 [B] on the device, clamped to [1, sk] by
+     * the kernel (ktt_flash/reader.cpp:111-160); never read on the host. */
+    const int32_t* key_lengths;
+
+    /* Packed calls: int32 [batch + 1] on the device; NULL for dense calls. */
+    const int32_t* cu_seqlens_q;
+    const int32_t* cu_seqlens_k;
+
+    /* Backward only (NULL on forward). dk / dv are already summed over each GQA group. */
+    const void* dout;
+    void* dq;
+    void* dk;
+    void* dv_out;
+    int64_t dout_strides[3];
+    int64_t dq_strides[3];
+    int64_t dk_strides[3];
+    int64_t dv_strides[3];
+    /* Backward workspace of ktt_b200_sdpa_backward_workspace() bytes, 256-byte aligned. */
+    void* workspace;
+    int64_t workspace_bytes;
+} ktt_b200_attn_args;
+
+/* Decode: one (or a few) query tokens per sequence against a static KV cache, split over
+ * the sequence. q [B, H, Sq<=16/group, D], cache k / v [B, Hk, Smax, D / Dv].
+ * Replaces ktt::_sdpa_lengths on the decode route (aten_lengths.cpp:69-99,
+ * aten_attention.cpp:578-604). */
+typedef struct ktt_b200_decode_args {
+    int32_t batch, heads, kv_heads;
+    int32_t sq;        /* query tokens per sequence; heads/kv_heads * sq <= 16 */
+    int32_t sk;        /* cache capacity Smax */
+    int32_t d, dv;     /* 64 or 128, equal */
+    float scale;
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    float* lse;        /* optional [B, H, Sq] */
+    int64_t q_strides[3];
+    int64_t k_strides[3];
+    int64_t v_strides[3];
+    int64_t out_strides[3];
+    const int32_t* key_lengths; /* int32 [B] on the device, or NULL for sk everywhere */
+    int32_t splits;    /* 0 = choose; else the number of sequence splits */
+    void* scratch;     /* ktt_b200_decode_scratch_bytes() bytes, 256-byte aligned */
+    int64_t scratch_bytes;
+} ktt_b200_decode_args;
+
+/* ktt_abi_version (ktt_capi.h:13). */
+KTT_B200_API int ktt_b200_abi_version(void);
+/* ktt_last_error (ktt_capi.h:14): message of this thread's last failing call. */
+KTT_B200_API const char* ktt_b200_last_error(void);
+
+/* ktt_counters (ktt_capi.h:24-26) reduced to this path: out[8] = forward calls on the
+ * tcgen05 kernel, forward calls on the warp-MMA kernel, backward calls, decode calls,
+ * refused calls, device-wait timeouts, reserved, reserved. */
+KTT_B200_API int ktt_b200_counters(int64_t* out8);
+KTT_B200_API int ktt_b200_reset_counters(void);
+
+/* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward
+ * kernels take the problem, 0 with the reason in ktt_b200_last_error(). Launches
+ * nothing and touches no device memory. */
+KTT_B200_API int ktt_b200_sdpa_supported(const ktt_b200_attn_args* args);
+/* ktt_flash::supports_backward (ktt_flash/program.cpp:1529-1585). */
+KTT_B200_API int ktt_b200_sdpa_backward_supported(const ktt_b200_attn_args* args);
+
+/* Forward of dense or packed attention: ktt_sdpa / ktt_sdpa_train (ktt_capi.h:122-125),
+ * bridge::sdpa_varlen and bridge::sdpa_lengths (tt_bridge.hpp:925-1095). Writes out and,
+ * when args->lse is set, the natural-log row statistics. */
+KTT_B200_API int ktt_b200_sdpa_forward(const ktt_b200_attn_args* args, void* stream);
+
+/* Bytes of workspace ktt_b200_sdpa_backward needs for the problem (0 on error). */
+KTT_B200_API int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* args);
+/* Backward (dq, dk, dv with the softmax recomputed from lse): ktt_sdpa_train_backward
+ * (ktt_capi.h:126-135), bridge::sdpa_varlen_backward, bridge::sdpa_lengths_backward. */
+KTT_B200_API int ktt_b200_sdpa_backward(const ktt_b200_attn_args* args, void* stream);
+
+/* Split-K decode against a static KV cache. */
+KTT_B200_API int64_t ktt_b200_decode_scratch_bytes(const ktt_b200_decode_args* args);
+KTT_B200_API int ktt_b200_decode(const ktt_b200_decode_args* args, void* stream);
+
+/* Merge of two partial attention results over disjoint key sets (ring attention steps):
+ * out / lse [rows] are updated in place with (out2, lse2). fp32 lse, bf16 or fp32 out.
+ * rows = B*H*S rows of dv values, row stride dv. No reference counterpart: the reference
+ * has no sequence-parallel attention. */
+KTT_B200_API int ktt_b200_merge_partials(
+    void* out, float* lse, const void* out2, const float* lse2,
+    int64_t rows, int32_t dv, int32_t out_is_f32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

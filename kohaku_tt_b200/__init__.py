@@ -1,0 +1,37 @@
+"""B200-native flash attention behind Kohaku-TT's operator surface.
+
+    import kohaku_tt_b200 as ktt
+    ktt.install()                      # F.scaled_dot_product_attention on CUDA -> these kernels
+    y = ktt.sdpa(q, k, v, key_lengths=lengths)
+    y = ktt.sdpa_varlen(q, k, v, cu_seqlens)
+    with ktt.sdpa_kernel("flash"): ...
+
+Everything runs on hand-written sm_100a CUDA in lib/libktt_b200.so (C ABI in
+include/ktt_b200.h); there is no CPU or PyTorch-math fallback.
+"""
+
+from ._lib import UnsupportedAttention, build, counters, reset_counters
+from .aten import fused_sdp_choice, install, installed
+from .attention import sdpa, sdpa_varlen
+from .numerics import KERNELS, sdpa_kernel
+from .stats import diff_stats, format_stats, rel_rms
+
+AVAILABLE = True
+
+__all__ = [
+    "AVAILABLE",
+    "KERNELS",
+    "UnsupportedAttention",
+    "build",
+    "counters",
+    "diff_stats",
+    "format_stats",
+    "fused_sdp_choice",
+    "install",
+    "installed",
+    "rel_rms",
+    "reset_counters",
+    "sdpa",
+    "sdpa_kernel",
+    "sdpa_varlen",
+]

@@ -1,0 +1,247 @@
+// The extern "C" surface: argument checks, kernel choice, counters, error text.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace ktt {
+
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<int64_t> g_counters[8];
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    return fail(KTT_B200_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+void note_call(int which) { g_counters[which].fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+
+// The first condition a forward call fails, or null. Mirrors the shape rules of
+// fused_refusal (aten_attention.cpp:62-127) and ktt_flash::refusal
+// (ktt_flash/program.cpp:847-910) that still mean something on this hardware.
+const char* forward_refusal(const ktt_b200_attn_args* a) {
+    if (!a) return "null arguments";
+    if (a->batch < 1 || a->heads < 1 || a->kv_heads < 1 || a->sq < 1 || a->sk < 1 || a->d < 1 || a->dv < 1) {
+        return "q, k and v must be non-empty";
+    }
+    if (a->heads % a->kv_heads) return "q, k and v shapes do not match (K / V heads must divide Q heads)";
+    if (a->d > 256 || a->dv > 256) return "head dims above 256 are not taken";
+    if (a->batch > 65535 || a->heads > 65535) return "batch and heads must not exceed 65535";
+    if (a->causal < 0 || a->causal > 2) return "unknown causal mode";
+    if (a->causal && a->mask_dtype != KTT_B200_MASK_NONE && !a->cu_seqlens_q) return "causal takes no mask";
+    if (a->mask_dtype < 0 || a->mask_dtype > KTT_B200_MASK_F16) return "unknown mask dtype";
+    if ((a->mask_dtype != KTT_B200_MASK_NONE) != (a->mask != nullptr)) return "mask pointer and mask dtype disagree";
+    if ((a->cu_seqlens_q == nullptr) != (a->cu_seqlens_k == nullptr)) return "packed calls need both offset arrays";
+    if (a->cu_seqlens_q && a->causal == KTT_B200_CAUSAL_TOP_LEFT) return "packed causal attention is bottom-right aligned";
+    if (a->cu_seqlens_q && a->key_lengths) return "packed calls take no key lengths";
+    if (!(a->scale == a->scale) || a->scale <= 0.f) return "the softmax scale must be positive";
+    return nullptr;
+}
+
+const char* backward_refusal(const ktt_b200_attn_args* a) {
+    if (const char* why = forward_refusal(a)) return why;
+    return nullptr;
+}
+
+void to_params(const ktt_b200_attn_args* a, AttnParams& p) {
+    std::memset(&p, 0, sizeof(p));
+    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.sq = a->sq; p.sk = a->sk; p.d = a->d; p.dv = a->dv; p.causal = a->causal;
+    p.scale = a->scale;
+    p.scale_log2 = a->scale * kLog2e;
+    p.q = static_cast<const __nv_bfloat16*>(a->q);
+    p.k = static_cast<const __nv_bfloat16*>(a->k);
+    p.v = static_cast<const __nv_bfloat16*>(a->v);
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.lse = a->lse;
+    for (int i = 0; i < 3; ++i) {
+        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i]; p.vs[i] = a->v_strides[i];
+        p.os[i] = a->out_strides[i]; p.ls[i] = a->lse_strides[i];
+        p.dos[i] = a->dout_strides[i]; p.dqs[i] = a->dq_strides[i];
+        p.dks[i] = a->dk_strides[i]; p.dvs[i] = a->dv_strides[i];
+    }
+    p.mask = a->mask;
+    p.mask_dtype = a->mask_dtype;
+    for (int i = 0; i < 4; ++i) p.ms[i] = a->mask_strides[i];
+    p.key_lengths = a->key_lengths;
+    p.cu_q = a->cu_seqlens_q;
+    p.cu_k = a->cu_seqlens_k;
+    p.dout = static_cast<const __nv_bfloat16*>(a->dout);
+    p.dq = static_cast<__nv_bfloat16*>(a->dq);
+    p.dk = static_cast<__nv_bfloat16*>(a->dk);
+    p.dv_out = static_cast<__nv_bfloat16*>(a->dv_out);
+}
+
+// Rows of the delta workspace: one fp32 per (batch, head, query row).
+void delta_layout(const ktt_b200_attn_args* a, int64_t& bs, int64_t& hs, int64_t& total) {
+    if (a->cu_seqlens_q) {
+        hs = (a->total_q + 63) / 64 * 64;
+        bs = 0;
+        total = hs * a->heads;
+    } else {
+        hs = (static_cast<int64_t>(a->sq) + 63) / 64 * 64;
+        bs = hs * a->heads;
+        total = bs * a->batch;
+    }
+}
+
+__global__ void merge_partials_kernel(
+    void* out, float* lse, const void* out2, const float* lse2, int64_t rows, int dv, int f32) {
+    const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.y) + threadIdx.y;
+    if (row >= rows) return;
+    const float a = lse[row], b = lse2[row];
+    const float m = fmaxf(a, b);
+    float wa, wb, l;
+    if (m == -INFINITY) {
+        wa = 0.f; wb = 0.f; l = -INFINITY;
+    } else {
+        const float ea = __expf(a - m), eb = __expf(b - m);
+        wa = ea / (ea + eb);
+        wb = eb / (ea + eb);
+        l = m + __logf(ea + eb);
+    }
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        const int64_t i = row * dv + c;
+        if (f32) {
+            float* o = static_cast<float*>(out);
+            o[i] = o[i] * wa + static_cast<const float*>(out2)[i] * wb;
+        } else {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+            o[i] = __float2bfloat16(
+                __bfloat162float(o[i]) * wa + __bfloat162float(static_cast<const __nv_bfloat16*>(out2)[i]) * wb);
+        }
+    }
+    __syncwarp();  // one warp per row: every lane has read lse[row]
+    if (threadIdx.x == 0) lse[row] = l;
+}
+
+}  // namespace
+}  // namespace ktt
+
+using namespace ktt;
+
+extern "C" int ktt_b200_abi_version(void) { return KTT_B200_ABI_VERSION; }
+
+extern "C" const char* ktt_b200_last_error(void) { return g_error; }
+
+extern "C" int ktt_b200_counters(int64_t* out8) {
+    if (!out8) return fail(KTT_B200_ERR_BAD_ARGUMENT, "counters: null output");
+    for (int i = 0; i < 8; ++i) out8[i] = g_counters[i].load(std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int ktt_b200_reset_counters(void) {
+    for (auto& c : g_counters) c.store(0, std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int ktt_b200_sdpa_supported(const ktt_b200_attn_args* a) {
+    if (const char* why = forward_refusal(a)) {
+        fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
+        return 0;
+    }
+    if (a->kernel == KTT_B200_KERNEL_TC5) {
+        AttnParams p;
+        to_params(a, p);
+        const char* why = nullptr;
+        if (!forward_tc5_takes(p, &why)) {
+            fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 kernel: %s", why);
+            return 0;
+        }
+    }
+    return 1;
+}
+
+extern "C" int ktt_b200_sdpa_backward_supported(const ktt_b200_attn_args* a) {
+    if (const char* why = backward_refusal(a)) {
+        fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
+        return 0;
+    }
+    return 1;
+}
+
+extern "C" int ktt_b200_sdpa_forward(const ktt_b200_attn_args* a, void* stream) {
+    if (const char* why = forward_refusal(a)) {
+        note_call(4);
+        return fail(KTT_B200_ERR_UNSUPPORTED, "sdpa_forward: %s", why);
+    }
+    if (!a->q || !a->k || !a->v || !a->out) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "sdpa_forward: null tensor pointer");
+    }
+    AttnParams p;
+    to_params(a, p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const char* why = nullptr;
+    const bool tc5 = forward_tc5_takes(p, &why);
+    if (a->kernel == KTT_B200_KERNEL_TC5 && !tc5) {
+        note_call(4);
+        return fail(KTT_B200_ERR_UNSUPPORTED, "sdpa_forward: tcgen05 kernel: %s", why);
+    }
+    if (tc5 && a->kernel != KTT_B200_KERNEL_MMA) {
+        note_call(0);
+        return launch_forward_tc5(p, st);
+    }
+    note_call(1);
+    return launch_forward_mma(p, st);
+}
+
+extern "C" int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* a) {
+    if (const char* why = backward_refusal(a)) {
+        fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
+        return 0;
+    }
+    int64_t bs, hs, total;
+    delta_layout(a, bs, hs, total);
+    return (total * 4 + 255) / 256 * 256;
+}
+
+extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream) {
+    if (const char* why = backward_refusal(a)) {
+        note_call(4);
+        return fail(KTT_B200_ERR_UNSUPPORTED, "sdpa_backward: %s", why);
+    }
+    if (!a->q || !a->k || !a->v || !a->out || !a->lse || !a->dout || !a->dq || !a->dk || !a->dv_out) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "sdpa_backward: null tensor pointer");
+    }
+    int64_t bs, hs, total;
+    delta_layout(a, bs, hs, total);
+    if (!a->workspace || a->workspace_bytes < total * 4) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "sdpa_backward: workspace holds %lld bytes, %lld needed",
+                    static_cast<long long>(a->workspace_bytes), static_cast<long long>(total * 4));
+    }
+    AttnParams p;
+    to_params(a, p);
+    p.delta = static_cast<float*>(a->workspace);
+    p.delta_bs = bs;
+    p.delta_hs = hs;
+    note_call(2);
+    return launch_backward_mma(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ktt_b200_merge_partials(
+    void* out, float* lse, const void* out2, const float* lse2,
+    int64_t rows, int32_t dv, int32_t out_is_f32, void* stream) {
+    if (!out || !lse || !out2 || !lse2 || rows < 0 || dv < 1) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "merge_partials: null pointer or bad size");
+    }
+    if (rows == 0) return 0;
+    dim3 block(32, 8);
+    const int64_t blocks = (rows + 7) / 8;
+    merge_partials_kernel<<<static_cast<unsigned>(blocks), block, 0, static_cast<cudaStream_t>(stream)>>>(
+        out, lse, out2, lse2, rows, dv, out_is_f32);
+    return check_cuda(cudaGetLastError(), "merge_partials launch");
+}

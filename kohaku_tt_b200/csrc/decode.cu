@@ -1,0 +1,530 @@
+// Memory-bound GQA decode against a static KV cache: split over the sequence.
+//
+// The reference has no dedicated decode kernel: a call with few query rows runs the
+// prefill kernel's key-lengths variant once per (batch, query head), so a GQA group
+// re-reads its K/V head once per query head (aten_attention.cpp:578-604,
+// ktt_flash/reader.cpp:111-160). Here the whole group (G query heads x Sq tokens <= 16
+// rows) shares one pass over its K/V head, and the passes are cut into equal shares of
+// 64-key tiles so that every CTA streams the same number of bytes whatever the
+// per-sequence lengths are:
+//
+//   plan    : prefix sum of ceil(len_b / 64) over the batch (lengths stay on the device)
+//   stream  : CTA c owns tile units [c*upc, (c+1)*upc) of the (batch, kv head) pairs laid
+//             end to end; per pair segment it produces an unnormalised partial
+//             (O, m, l) in fp32 scratch. K/V rows arrive by 16-byte cp.async into a
+//             swizzled ring of stages, one private pipeline per warp (16 keys per tile
+//             each), scores and P.V on warp MMA, running max / sum in fp32.
+//   combine : per pair, merge its partials with the usual max / rescale rule, divide by
+//             the sum, write bf16.
+//
+// Semantics are kohakutt.sdpa(q, k, v, key_lengths=) (attention.py:10-23): keys at or past
+// a length contribute nothing, whatever they hold; lengths are clamped to [1, Sk].
+#include "common.cuh"
+
+namespace ktt {
+
+struct DecodeParams {
+    int batch, heads, kv_heads, sq, sk, d;
+    float scale_log2;
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    __nv_bfloat16* out;
+    float* lse;
+    int64_t qs[3], ks[3], vs[3], os[3];
+    const int32_t* key_lengths;
+    int32_t* prefix;  // [batch + 1] tiles before each batch entry (one kv head)
+    float* part_m;    // [slots][16]
+    float* part_l;    // [slots][16]
+    float* part_o;    // [slots][16][d]
+    int slots;
+};
+
+namespace {
+
+constexpr int kTile = 64;      // keys per tile (16 per warp)
+constexpr int kThreads = 128;
+
+__device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
+    if (!p.key_lengths) return p.sk;
+    int l = p.key_lengths[b];
+    l = l < 1 ? 1 : l;
+    return l > p.sk ? p.sk : l;
+}
+
+// prefix[b] = sum_{b' < b} ceil(len_b' / 64); one block, any batch size.
+__global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p) {
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < p.batch; base += 1024) {
+        const int b = base + threadIdx.x;
+        const int tiles = b < p.batch ? (clamp_len(p, b) + kTile - 1) / kTile : 0;
+        int x = tiles;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, x, off);
+            if (lane >= off) x += y;
+        }
+        if (lane == 31) warp_sums[warp] = x;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, w, off);
+                if (lane >= off) w += y;
+            }
+            warp_sums[lane] = w;
+        }
+        __syncthreads();
+        const int before = carry + (warp ? warp_sums[warp - 1] : 0) + x - tiles;
+        if (b < p.batch) p.prefix[b] = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = before + tiles;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) p.prefix[p.batch] = carry;
+}
+
+// Position inside the end-to-end sequence of (batch, kv head) pairs.
+struct Cursor {
+    int b, hk, tile, ntiles, len;
+};
+
+__device__ __forceinline__ void cursor_seek(const DecodeParams& p, Cursor& c, int unit) {
+    // Largest b with kv_heads * prefix[b] <= unit.
+    int lo = 0, hi = p.batch - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (p.kv_heads * p.prefix[mid] <= unit) lo = mid; else hi = mid - 1;
+    }
+    c.b = lo;
+    c.len = clamp_len(p, lo);
+    c.ntiles = (c.len + kTile - 1) / kTile;
+    const int rem = unit - p.kv_heads * p.prefix[lo];
+    c.hk = rem / c.ntiles;
+    c.tile = rem % c.ntiles;
+}
+
+__device__ __forceinline__ void cursor_next(const DecodeParams& p, Cursor& c) {
+    if (++c.tile < c.ntiles) return;
+    c.tile = 0;
+    if (++c.hk < p.kv_heads) return;
+    c.hk = 0;
+    if (++c.b < p.batch) {
+        c.len = clamp_len(p, c.b);
+        c.ntiles = (c.len + kTile - 1) / kTile;
+    }
+}
+
+// Byte offset of element (row, col) in a [rows][D] bf16 tile whose 16-byte chunks are
+// XOR-swizzled by the row, which keeps fragment loads and ldmatrix conflict-free.
+template <int D>
+__device__ __forceinline__ int swz(int row, int col) {
+    return (row * D + ((((col >> 3) ^ (row & 7))) << 3) + (col & 7)) * 2;
+}
+
+template <int D, int NS>
+__global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const DecodeParams p) {
+    constexpr int kStage = 2 * kTile * D * 2;  // K then V, bytes
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* ring = smem;
+    float* acc = reinterpret_cast<float*>(smem + NS * kStage);  // [16][D]
+    float* sm_m = acc + 16 * D;                                 // [4][16]
+    float* sm_l = sm_m + 64;                                    // [4][16]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.heads / p.kv_heads;
+    const int rows = group * p.sq;  // valid rows of the 16-row MMA tile
+
+    const int total = p.kv_heads * p.prefix[p.batch];
+    const int upc = (total + gridDim.x - 1) / gridDim.x;
+    const int u0 = blockIdx.x * upc;
+    const int u1 = min(u0 + upc, total);
+    if (u0 >= u1) return;
+
+    Cursor prod, cons;
+    cursor_seek(p, cons, u0);
+    prod = cons;
+
+    // One warp copies its own 16 key rows of K and V for a tile into stage `st`.
+    auto issue = [&](const Cursor& c, int st) {
+        const __nv_bfloat16* kg = p.k + c.b * p.ks[0] + c.hk * p.ks[1];
+        const __nv_bfloat16* vg = p.v + c.b * p.vs[0] + c.hk * p.vs[1];
+        const uint32_t sk = smem_u32(ring + st * kStage);
+        const uint32_t sv = sk + kTile * D * 2;
+        constexpr int CH = D / 8;
+#pragma unroll
+        for (int it = 0; it < 16 * CH / 32; ++it) {
+            const int idx = it * 32 + lane;
+            const int r = warp * 16 + idx / CH, ch = idx % CH;
+            const int j = c.tile * kTile + r;
+            const bool ok = j < c.len;
+            const int64_t jj = ok ? j : 0;
+            cp_async_16(sk + swz<D>(r, ch * 8), kg + jj * p.ks[2] + ch * 8, ok);
+            cp_async_16(sv + swz<D>(r, ch * 8), vg + jj * p.vs[2] + ch * 8, ok);
+        }
+    };
+
+    // Prologue: NS - 1 tiles in flight.
+    int up = u0;
+#pragma unroll
+    for (int s = 0; s < NS - 1; ++s) {
+        if (up < u1) {
+            issue(prod, s);
+            cursor_next(p, prod);
+            ++up;
+        }
+        cp_async_commit();
+    }
+
+    uint32_t qa[D / 16][4];
+    float o[D / 8][4];
+    float m_run[2], l_run[2];
+    bool fresh = true;  // start of a pair segment: load Q, reset the running state
+
+    for (int u = u0; u < u1; ++u) {
+        const int st = (u - u0) % NS;
+        // Refill the stage consumed in the previous iteration.
+        if (up < u1) {
+            issue(prod, (up - u0) % NS);
+            cursor_next(p, prod);
+            ++up;
+        }
+        cp_async_commit();
+        cp_async_wait<NS - 1>();
+        __syncwarp();
+
+        if (fresh) {
+            fresh = false;
+            // A-fragments of this pair's query rows: row r = head-in-group * Sq + token.
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = g + half * 8;
+                const bool ok = r < rows;
+                const int gi = ok ? r / p.sq : 0, tq = ok ? r % p.sq : 0;
+                const __nv_bfloat16* qg = p.q + cons.b * p.qs[0] +
+                    (cons.hk * group + gi) * p.qs[1] + tq * p.qs[2];
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    qa[kk][half] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + t * 2) : 0u;
+                    qa[kk][half + 2] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + 8 + t * 2) : 0u;
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+            m_run[0] = m_run[1] = -INFINITY;
+            l_run[0] = l_run[1] = 0.f;
+        }
+
+        const int j0 = cons.tile * kTile + warp * 16;
+        if (j0 < cons.len) {
+            const unsigned char* sK = ring + st * kStage;
+            const unsigned char* sV = sK + kTile * D * 2;
+            float s[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    const int r = warp * 16 + n * 8 + g;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(sK + swz<D>(r, kk * 16 + t * 2));
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(sK + swz<D>(r, kk * 16 + 8 + t * 2));
+                    mma_bf16(s[n], qa[kk], b0, b1);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j0 + n * 8 + t * 2 + (e & 1);
+                    const float x = j < cons.len ? s[n][e] * p.scale_log2 : -INFINITY;
+                    s[n][e] = x;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], x);
+                }
+            }
+            float alpha[2], m_use[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+                alpha[r] = fast_exp2(m_run[r] - m_use[r]);
+                m_run[r] = m_new;
+                l_run[r] *= alpha[r];
+            }
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                o[n][0] *= alpha[0];
+                o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1];
+                o[n][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = fast_exp2(s[n][e] - m_use[e >> 1]);
+                    s[n][e] = pv;
+                    l_run[e >> 1] += pv;
+                }
+            }
+            uint32_t a[4];
+            a[0] = pack_bf16(s[0][0], s[0][1]);
+            a[1] = pack_bf16(s[0][2], s[0][3]);
+            a[2] = pack_bf16(s[1][0], s[1][1]);
+            a[3] = pack_bf16(s[1][2], s[1][3]);
+            const uint32_t sv_base = smem_u32(sV);
+#pragma unroll
+            for (int n2 = 0; n2 < D / 16; ++n2) {
+                uint32_t r[4];
+                ldmatrix_x4_trans(r, sv_base + swz<D>(warp * 16 + (lane & 15), n2 * 16 + (lane >> 4) * 8));
+                mma_bf16(o[2 * n2], a, r[0], r[1]);
+                mma_bf16(o[2 * n2 + 1], a, r[2], r[3]);
+            }
+        }
+        __syncwarp();  // all lanes are done with stage `st` before it is refilled
+
+        const bool last_of_pair = cons.tile + 1 == cons.ntiles;
+        if (last_of_pair || u + 1 == u1) {
+            // Merge the four warps' states in a fixed order (deterministic) and store the
+            // pair segment's partial.
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+            }
+            if (t == 0) {
+                sm_m[warp * 16 + g] = m_run[0];
+                sm_m[warp * 16 + g + 8] = m_run[1];
+                sm_l[warp * 16 + g] = l_run[0];
+                sm_l[warp * 16 + g + 8] = l_run[1];
+            }
+            __syncthreads();
+            float f[2], m_all[2], l_all[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = g + r * 8;
+                float mm = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w * 16 + row]);
+                const float base = (mm == -INFINITY) ? 0.f : mm;
+                float ll = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) ll += sm_l[w * 16 + row] * fast_exp2(sm_m[w * 16 + row] - base);
+                m_all[r] = mm;
+                l_all[r] = ll;
+                f[r] = fast_exp2(m_run[r] - base);
+            }
+#pragma unroll
+            for (int turn = 0; turn < 4; ++turn) {
+                if (warp == turn) {
+#pragma unroll
+                    for (int n = 0; n < D / 8; ++n) {
+                        float2* lo = reinterpret_cast<float2*>(&acc[g * D + n * 8 + t * 2]);
+                        float2* hi = reinterpret_cast<float2*>(&acc[(g + 8) * D + n * 8 + t * 2]);
+                        float2 vlo = make_float2(o[n][0] * f[0], o[n][1] * f[0]);
+                        float2 vhi = make_float2(o[n][2] * f[1], o[n][3] * f[1]);
+                        if (turn) {
+                            const float2 a0 = *lo, a1 = *hi;
+                            vlo.x += a0.x; vlo.y += a0.y;
+                            vhi.x += a1.x; vhi.y += a1.y;
+                        }
+                        *lo = vlo;
+                        *hi = vhi;
+                    }
+                }
+                __syncthreads();
+            }
+            const int pair = cons.b * p.kv_heads + cons.hk;
+            const int slot = blockIdx.x + pair;
+            float4* dst = reinterpret_cast<float4*>(p.part_o + static_cast<int64_t>(slot) * 16 * D);
+            const float4* src = reinterpret_cast<const float4*>(acc);
+            for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = src[idx];
+            if (warp == 0 && t == 0) {
+                p.part_m[slot * 16 + g] = m_all[0];
+                p.part_m[slot * 16 + g + 8] = m_all[1];
+                p.part_l[slot * 16 + g] = l_all[0];
+                p.part_l[slot * 16 + g + 8] = l_all[1];
+            }
+            __syncthreads();
+            fresh = true;
+        }
+        cursor_next(p, cons);
+    }
+    cp_async_wait<0>();
+}
+
+// One CTA per (batch, kv head) pair: merge its partials and write bf16 rows.
+template <int D>
+__global__ void __launch_bounds__(kThreads) decode_combine_kernel(const DecodeParams p, int stream_ctas) {
+    const int pair = blockIdx.x;
+    const int b = pair / p.kv_heads, hk = pair % p.kv_heads;
+    const int group = p.heads / p.kv_heads;
+    const int rows = group * p.sq;
+    const int len = clamp_len(p, b);
+    const int ntiles = (len + kTile - 1) / kTile;
+    const int total = p.kv_heads * p.prefix[p.batch];
+    const int upc = (total + stream_ctas - 1) / stream_ctas;
+    const int t0 = p.kv_heads * p.prefix[b] + hk * ntiles;
+    const int c_first = t0 / upc, c_last = (t0 + ntiles - 1) / upc;
+
+    for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
+        const int r = idx / (D / 4), c4 = idx % (D / 4);
+        float mm = -INFINITY;
+        for (int c = c_first; c <= c_last; ++c) mm = fmaxf(mm, p.part_m[(c + pair) * 16 + r]);
+        const float base = (mm == -INFINITY) ? 0.f : mm;
+        float ll = 0.f;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = c_first; c <= c_last; ++c) {
+            const int slot = c + pair;
+            const float f = fast_exp2(p.part_m[slot * 16 + r] - base);
+            ll += p.part_l[slot * 16 + r] * f;
+            const float4 v = *reinterpret_cast<const float4*>(
+                p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4);
+            sum.x += v.x * f; sum.y += v.y * f; sum.z += v.z * f; sum.w += v.w * f;
+        }
+        const float inv = ll > 0.f ? 1.f / ll : 0.f;
+        const int gi = r / p.sq, tq = r % p.sq;
+        const int h = hk * group + gi;
+        __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + tq * p.os[2] + c4 * 4;
+        uint2 packed;
+        packed.x = pack_bf16(sum.x * inv, sum.y * inv);
+        packed.y = pack_bf16(sum.z * inv, sum.w * inv);
+        *reinterpret_cast<uint2*>(og) = packed;
+        if (p.lse && c4 == 0) {
+            p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.sq + tq] =
+                ll > 0.f ? kLn2 * (mm + log2f(ll)) : -INFINITY;
+        }
+    }
+}
+
+int stream_ctas_for_device() {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return 2 * sms;
+}
+
+template <int D, int NS>
+int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
+    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + 2 * 64 * 4;
+    if (int rc = check_cuda(
+            cudaFuncSetAttribute(
+                decode_stream_kernel<D, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+            "cudaFuncSetAttribute(decode_stream)")) {
+        return rc;
+    }
+    decode_plan_kernel<<<1, 1024, 0, stream>>>(p);
+    if (int rc = check_cuda(cudaGetLastError(), "decode_plan launch")) return rc;
+    decode_stream_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);
+    if (int rc = check_cuda(cudaGetLastError(), "decode_stream launch")) return rc;
+    decode_combine_kernel<D><<<p.batch * p.kv_heads, kThreads, 0, stream>>>(p, ctas);
+    return check_cuda(cudaGetLastError(), "decode_combine launch");
+}
+
+// Scratch layout: prefix (int32, padded to 256 B), then m, l, O partials.
+struct ScratchLayout {
+    int64_t prefix_bytes, m_bytes, l_bytes, o_bytes, total;
+    int slots;
+};
+
+ScratchLayout scratch_layout(int batch, int kv_heads, int d, int ctas) {
+    ScratchLayout s;
+    s.slots = ctas + batch * kv_heads;
+    auto up = [](int64_t x) { return (x + 255) / 256 * 256; };
+    s.prefix_bytes = up(static_cast<int64_t>(batch + 1) * 4);
+    s.m_bytes = up(static_cast<int64_t>(s.slots) * 16 * 4);
+    s.l_bytes = s.m_bytes;
+    s.o_bytes = up(static_cast<int64_t>(s.slots) * 16 * d * 4);
+    s.total = s.prefix_bytes + s.m_bytes + s.l_bytes + s.o_bytes;
+    return s;
+}
+
+int decode_ctas(const ktt_b200_decode_args* a) {
+    // `splits` bounds the CTAs per (batch, kv head) pair; 0 lets the device size decide.
+    int ctas = stream_ctas_for_device();
+    if (a->splits > 0) {
+        const int64_t want = static_cast<int64_t>(a->splits) * a->batch * a->kv_heads;
+        if (want < ctas) ctas = static_cast<int>(want);
+    }
+    return ctas < 1 ? 1 : ctas;
+}
+
+const char* decode_refusal(const ktt_b200_decode_args* a) {
+    if (!a) return "null arguments";
+    if (a->batch < 1 || a->heads < 1 || a->kv_heads < 1 || a->sq < 1 || a->sk < 1) return "sizes must be positive";
+    if (a->heads % a->kv_heads) return "K / V heads must divide Q heads";
+    if (a->d != a->dv || (a->d != 64 && a->d != 128)) return "decode takes head dim 64 or 128 (D == Dv)";
+    if ((a->heads / a->kv_heads) * a->sq > 16) return "decode takes at most 16 query rows per K / V head";
+    for (int i = 0; i < 3; ++i) {
+        if (a->k_strides[i] % 8 || a->v_strides[i] % 8) return "K / V strides must be multiples of 8 elements";
+        if (a->q_strides[i] % 2 || a->out_strides[i] % 4) return "q strides must be even and out strides multiples of 4";
+    }
+    return nullptr;
+}
+
+}  // namespace
+
+}  // namespace ktt
+
+using namespace ktt;
+
+extern "C" int64_t ktt_b200_decode_scratch_bytes(const ktt_b200_decode_args* a) {
+    if (const char* why = decode_refusal(a)) {
+        fail(KTT_B200_ERR_UNSUPPORTED, "decode: %s", why);
+        return 0;
+    }
+    return scratch_layout(a->batch, a->kv_heads, a->d, decode_ctas(a)).total;
+}
+
+extern "C" int ktt_b200_decode(const ktt_b200_decode_args* a, void* stream) {
+    if (const char* why = decode_refusal(a)) return fail(KTT_B200_ERR_UNSUPPORTED, "decode: %s", why);
+    if (!a->q || !a->k || !a->v || !a->out || !a->scratch) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode: null tensor or scratch pointer");
+    }
+    const uintptr_t align = reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
+        reinterpret_cast<uintptr_t>(a->scratch);
+    if (align & 15) return fail(KTT_B200_ERR_UNSUPPORTED, "decode: k, v and scratch must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (reinterpret_cast<uintptr_t>(a->out) & 7)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "decode: q must be 4-byte and out 8-byte aligned");
+    }
+    const int ctas = decode_ctas(a);
+    const ScratchLayout lay = scratch_layout(a->batch, a->kv_heads, a->d, ctas);
+    if (a->scratch_bytes < lay.total) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode: scratch holds %lld bytes, %lld needed",
+                    static_cast<long long>(a->scratch_bytes), static_cast<long long>(lay.total));
+    }
+    DecodeParams p;
+    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.sq = a->sq; p.sk = a->sk; p.d = a->d;
+    p.scale_log2 = a->scale * kLog2e;
+    p.q = static_cast<const __nv_bfloat16*>(a->q);
+    p.k = static_cast<const __nv_bfloat16*>(a->k);
+    p.v = static_cast<const __nv_bfloat16*>(a->v);
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.lse = a->lse;
+    for (int i = 0; i < 3; ++i) {
+        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i];
+        p.vs[i] = a->v_strides[i]; p.os[i] = a->out_strides[i];
+    }
+    p.key_lengths = a->key_lengths;
+    unsigned char* base = static_cast<unsigned char*>(a->scratch);
+    p.prefix = reinterpret_cast<int32_t*>(base);
+    p.part_m = reinterpret_cast<float*>(base + lay.prefix_bytes);
+    p.part_l = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes);
+    p.part_o = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes + lay.l_bytes);
+    p.slots = lay.slots;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    note_call(3);
+    if (a->d == 64) return launch<64, 6>(p, ctas, st);
+    return launch<128, 3>(p, ctas, st);
+}

@@ -1,0 +1,128 @@
+"""The operator surface end to end on CUDA tensors: F.scaled_dot_product_attention and
+autograd land on these kernels, torch's varlen_attn does too, scopes and counters work
+(tests/hardware/ops/test_attention.py, test_sdpa_kernel.py)."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import kohaku_tt_b200 as ktt
+from oracle import attention_oracle as ao
+from tests.gpu_util import FWD_BOUND, GRAD_BOUND, cu, cumulative, packed, qkv, rel
+
+pytestmark = pytest.mark.gpu
+
+
+def _delta(before):
+    after = ktt.counters()
+    return {k: after[k] - before[k] for k in after if after[k] != before[k]}
+
+
+def test_sdpa_dispatches_here_forward_and_backward(cuda):
+    q, k, v, do = qkv(2, 8, 8, 256, 256, 64, 0, extra=1)  # benchmark config 1
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, causal=True)
+    qc, kc, vc = (t.to(cuda).requires_grad_(True) for t in (q, k, v))
+    before = ktt.counters()
+    out = F.scaled_dot_product_attention(qc, kc, vc, is_causal=True)
+    out.backward(do.to(cuda))
+    d = _delta(before)
+    assert d.get("attention_backward") == 1
+    assert d.get("attention_flash", 0) + d.get("attention_mma", 0) == 1
+    assert rel(out, ruler) <= FWD_BOUND
+    for got, want in ((qc.grad, dq), (kc.grad, dk), (vc.grad, dv)):
+        assert rel(got, want) <= GRAD_BOUND
+    # The tolerance BASELINE states for this config, beside the CPU bf16 result.
+    cpu = ao.ruler_dense(q, k, v, causal=True, dtype=torch.bfloat16)
+    ours, theirs = ktt.diff_stats(out, ruler), ktt.diff_stats(cpu, ruler)
+    assert ours["rel_median"] <= 1e-2 and ours["abs_max"] <= 2e-2
+    assert ours["abs_max"] <= 2 * theirs["abs_max"] + 1e-3
+
+
+def test_gqa_masks_and_fp32_route_here(cuda):
+    q, k, v = qkv(1, 14, 2, 300, 300, 64, 2)
+    before = ktt.counters()
+    out = F.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), is_causal=True, enable_gqa=True)
+    assert sum(_delta(before).values()) >= 1
+    assert rel(out, ao.ruler_dense(q, k, v, causal=True)) <= FWD_BOUND
+    # SDXL cross-attention shape: 77 keys, last 20 masked by a bool key-padding mask.
+    q, k, v = qkv(2, 10, 10, 512, 77, 64, 3)
+    keep = torch.ones(2, 1, 1, 77, dtype=torch.bool)
+    keep[..., 57:] = False
+    before = ktt.counters()
+    out = F.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda), attn_mask=keep.to(cuda))
+    assert sum(_delta(before).values()) >= 1
+    assert rel(out, ao.ruler_dense(q, k, v, mask=keep)) <= FWD_BOUND
+    # fp32 inputs without gradients are cast at entry (test_flash_fp32_causal.py).
+    q, k, v = ao.make_inputs([(1, 4, 128, 64)] * 3, 4, dtype=torch.float32)
+    before = ktt.counters()
+    out = F.scaled_dot_product_attention(q.to(cuda), k.to(cuda), v.to(cuda))
+    assert out.dtype == torch.float32 and sum(_delta(before).values()) >= 1
+    assert rel(out, ao.ruler_dense(q, k, v)) <= 1.2e-2
+
+
+def test_overrideable_pair_and_choice_op(cuda):
+    q, k, v, do = qkv(1, 2, 2, 77, 77, 64, 5, extra=1)
+    qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
+    assert torch.ops.aten._fused_sdp_choice(qc, kc, vc, None, 0.0, True) == 4
+    assert torch.ops.aten._fused_sdp_choice(qc, kc, vc, None, 0.1, False) == 0
+    res = torch.ops.aten._scaled_dot_product_fused_attention_overrideable(qc, kc, vc, None, 0.0, True)
+    out, lse = res[0], res[1]
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, causal=True)
+    assert rel(out, ruler) <= FWD_BOUND and lse.shape == (1, 2, 77)
+    grads = torch.ops.aten._scaled_dot_product_fused_attention_overrideable_backward(
+        do.to(cuda), qc, kc, vc, torch.empty(0, device=cuda), [True, True, True, False], out, lse,
+        res[2], res[3], res[4], res[5], 0.0, True, res[6], res[7])
+    for got, want in zip(grads[:3], (dq, dk, dv)):
+        assert rel(got, want) <= GRAD_BOUND
+
+
+def test_dropout_is_refused_not_rerouted(cuda):
+    q, k, v = (t.to(cuda) for t in qkv(1, 2, 2, 64, 64, 64, 1))
+    with pytest.raises(NotImplementedError):
+        torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.1, False)
+
+
+def test_torch_varlen_attn_runs_here(cuda):
+    from torch.nn.attention.varlen import varlen_attn
+
+    lengths = [40, 7, 90]
+    c = cumulative(lengths)
+    q, k, v, do = packed(lengths, lengths, 4, 4, 64, 8, extra=1)
+    ruler, dq, dk, dv = ao.ruler_varlen(q, k, v, c, c, causal=True, dout=do)
+    qc, kc, vc = (t.to(cuda).requires_grad_(True) for t in (q, k, v))
+    before = ktt.counters()
+    out = varlen_attn(qc, kc, vc, cu(lengths, cuda), cu(lengths, cuda), 90, 90, window_size=(-1, 0))
+    out.backward(do.to(cuda))
+    d = _delta(before)
+    assert d.get("attention_backward") == 1
+    assert rel(out, ruler) <= FWD_BOUND
+    for got, want in ((qc.grad, dq), (kc.grad, dk), (vc.grad, dv)):
+        assert rel(got, want) <= 2.5e-2
+    # The package's own entry point gives the same result.
+    again = ktt.sdpa_varlen(q.to(cuda), k.to(cuda), v.to(cuda), c, is_causal=True)
+    assert torch.equal(again, out.detach())
+
+
+def test_scope_selects_the_kernel(cuda):
+    q, k, v = (t.to(cuda) for t in qkv(1, 4, 4, 128, 128, 64, 1))
+    with ktt.sdpa_kernel("mma"):
+        before = ktt.counters()
+        F.scaled_dot_product_attention(q, k, v)
+        assert _delta(before) == {"attention_mma": 1}
+    q96 = q[..., :32].contiguous()
+    with ktt.sdpa_kernel("flash"):
+        with pytest.raises(NotImplementedError):  # head dim 32 is not a tcgen05 shape
+            F.scaled_dot_product_attention(q96, q96, q96)
+
+
+def test_merge_partials_equals_attention_over_the_union(cuda):
+    from kohaku_tt_b200 import ops
+
+    q, k, v = qkv(1, 4, 4, 200, 300, 64, 4)
+    qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
+    o1, l1 = ops.sdpa_forward(qc, kc[:, :, :130].contiguous(), vc[:, :, :130].contiguous())
+    o2, l2 = ops.sdpa_forward(qc, kc[:, :, 130:].contiguous(), vc[:, :, 130:].contiguous())
+    acc = o1.float().contiguous()
+    ops.merge_partials(acc, l1, o2.float().contiguous(), l2)
+    assert rel(acc, ao.ruler_dense(q, k, v)) <= FWD_BOUND
+    assert (l1.cpu().double() - ao.ruler_lse(q, k, v)).abs().max() <= 3e-2
