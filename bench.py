@@ -1,0 +1,425 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (N = 1): the Qwen2.5-0.5B-shaped GQA causal prefill forward, B = 1,
+14 query heads / 2 KV heads, D = 64, S = 2048, bf16, seeded N(0, 1) inputs. A step is one
+forward pass over one batch; with N > 1 every rank runs its own batch (weak scaling, no
+collective). The line also carries the forward+backward, decode, SDXL and packed
+workloads as `extra` legs, a roofline for the dominant kernel, and the reference's CPU
+path (PyTorch CPU SDPA on the same bf16 tensors) timed on this box's host cores.
+
+`--impl reference` times only that CPU path, on the headline workload.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADLINE = dict(batch=1, heads=14, kv_heads=2, seq=2048, head_dim=64)
+L2_BYTES = 126 * 1024 * 1024
+
+
+def causal_forward_flops(b, h, s, d):
+    """2 FLOP per multiply-add, QK^T + PV over visible (query, key) pairs only."""
+    return 4.0 * b * h * d * (s * (s + 1) / 2)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return {"bf16": m["bf16_tflops"], "bf16_sustained": m["bf16_tflops_sustained"],
+                "hbm": m["hbm_gbs"], "source": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and clock-event reasons through NVML while a region runs."""
+
+    REASONS = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                try:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def headline_inputs(seed, device=None, pin=False):
+    from oracle import attention_oracle as ao
+
+    c = HEADLINE
+    q, k, v = ao.make_inputs(
+        [(c["batch"], c["heads"], c["seq"], c["head_dim"]),
+         (c["batch"], c["kv_heads"], c["seq"], c["head_dim"]),
+         (c["batch"], c["kv_heads"], c["seq"], c["head_dim"])], seed)
+    if device is not None:
+        return q.to(device), k.to(device), v.to(device)
+    if pin:
+        return q.pin_memory(), k.pin_memory(), v.pin_memory()
+    return q, k, v
+
+
+def time_cpu_path(steps, warmup):
+    """The reference's CPU path for this op: torch CPU SDPA on the bf16 tensors
+    (restated in oracle.attention_oracle.cpu_dense)."""
+    from oracle import attention_oracle as ao
+
+    q, k, v = headline_inputs(0)
+    for _ in range(warmup):
+        ao.cpu_dense(q, k, v, causal=True)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        ao.cpu_dense(q, k, v, causal=True)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    c = HEADLINE
+    flops = causal_forward_flops(c["batch"], c["heads"], c["seq"], c["head_dim"])
+    times = time_cpu_path(args.steps, max(args.warmup, 1))
+    total = sum(times)
+    value = flops * len(times) / total / 1e12
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference",
+        "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {
+            "value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{len(times)} full forward passes of the headline workload through torch CPU SDPA "
+                      f"on bf16 tensors ({os.cpu_count()} host CPUs visible)",
+        },
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config():
+    c = HEADLINE
+    return {
+        "workload": "GQA causal prefill forward, Qwen2.5-0.5B shape",
+        "batch_per_gpu": c["batch"], "heads": c["heads"], "kv_heads": c["kv_heads"],
+        "seq_len": c["seq"], "head_dim": c["head_dim"],
+        "l2_policy": "each step uses the next of a ring of input sets larger than L2 in total",
+        "parallelism": "one batch per GPU, no collective",
+    }
+
+
+def timed_region(fn, steps, warmup, world):
+    """W untimed calls, then K calls between two events on the current stream, bracketed
+    by a barrier and a device synchronize; returns milliseconds (max over ranks)."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.barrier()
+        ms = t.item()
+    return ms
+
+
+def run_ours(args):
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+
+    import torch.nn.functional as F
+
+    import kohaku_tt_b200 as ktt
+    from kohaku_tt_b200 import _lib, ops
+    from oracle import attention_oracle as ao
+
+    ktt.build()
+    ktt.install()
+    peaks = measured_peaks()
+    c = HEADLINE
+    flops = causal_forward_flops(c["batch"], c["heads"], c["seq"], c["head_dim"])
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    # ---- headline: inputs resident in HBM, a ring of sets larger than L2 -------------
+    per_set = 2 * (2 * c["batch"] * c["heads"] + 2 * c["batch"] * c["kv_heads"]) * c["seq"] * c["head_dim"]
+    nsets = max(4, int(1.5 * L2_BYTES / per_set) + 1)
+    sets = [headline_inputs(1000 * rank + i % 4, dev) for i in range(4)]
+    sets = [tuple(t.clone() for t in sets[i % 4]) for i in range(nsets)]
+
+    def step(i):
+        q, k, v = sets[i % nsets]
+        return ops.sdpa_forward(q, k, v, causal=True, need_lse=True)
+
+    # Parity of the timed path, on this rank's first set, against the float64 ruler.
+    q0, k0, v0 = (t.cpu() for t in sets[0])
+    out, _ = step(0)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    parity = ktt.diff_stats(out, ao.ruler_dense(q0, k0, v0, causal=True))
+
+    ktt.reset_counters()
+    ms = timed_region(step, steps, warmup, world)
+    launches = sum(ktt.counters()[k] for k in ("attention_flash", "attention_mma")) - warmup
+    _lib.device_status()
+    kernel = "tcgen05" if ktt.counters()["attention_flash"] else "warp-mma"
+    value = flops * steps * world / (ms * 1e-3) / 1e12
+    per_launch_ms = ms / steps
+
+    # Clocks: the same loop repeated for about half a second with the sampler running.
+    with ClockSampler(local) as sampler:
+        t_end = time.time() + 0.5
+        i = 0
+        while time.time() < t_end:
+            for _ in range(50):
+                step(i)
+                i += 1
+            torch.cuda.synchronize()
+    clocks = sampler.summary()
+
+    # ---- end to end: host buffers, H2D and D2H inside the timed region -----------------
+    host = [headline_inputs(2000 * rank + i, pin=True) for i in range(4)]
+    out_host = torch.empty((c["batch"], c["heads"], c["seq"], c["head_dim"]), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        q, k, v = (t.to(dev, non_blocking=True) for t in host[i % 4])
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        out_host.copy_(o, non_blocking=True)
+
+    e2e_steps = max(10, steps // 4)
+    e2e_ms = timed_region(e2e_step, e2e_steps, warmup, world)
+    e2e_value = flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in host[0])
+    d2h = out_host.numel() * out_host.element_size()
+
+    line = {
+        "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": per_launch_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(),
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
+                "api": "torch.nn.functional.scaled_dot_product_attention on CUDA tensors"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "kernel": kernel,
+        "parity_vs_f64": {k: parity[k] for k in ("abs_max", "rel_median", "cosine", "nonfinite")},
+    }
+    achieved = flops / (per_launch_ms * 1e-3) / 1e12
+    line["roofline"] = {
+        "bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
+        "frac": achieved / peaks["bf16"], "traffic": None,
+        "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / 2250.0,
+    }
+
+    if rank == 0 and world == 1 and not args.headline_only:
+        line["extra"] = extra_legs(dev, peaks, warmup)
+        times = time_cpu_path(3, 1)
+        cpu_tflops = flops / statistics.median(times) / 1e12
+        cpu_out = ao.cpu_dense(q0, k0, v0, causal=True)
+        cpu_parity = ktt.diff_stats(cpu_out, ao.ruler_dense(q0, k0, v0, causal=True))
+        line["cpu_baseline"] = {
+            "value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "median of 3 full forward passes of the headline workload through torch CPU SDPA on "
+                      "bf16 tensors after one warm-up",
+            "parity_vs_f64": {k: cpu_parity[k] for k in ("abs_max", "rel_median", "cosine")},
+        }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def _time(fn, steps, warmup):
+    return timed_region(fn, steps, warmup, 1) / steps
+
+
+def extra_legs(dev, peaks, warmup):
+    """The other configurations of the benchmark plan, each timed the same way."""
+    import kohaku_tt_b200 as ktt
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
+    extra = {}
+    c = HEADLINE
+
+    # Forward + backward on the headline shape (3.5 x the forward FLOPs).
+    sets = []
+    for i in range(8):
+        q, k, v, do = ao.make_inputs(
+            [(1, c["heads"], c["seq"], 64), (1, c["kv_heads"], c["seq"], 64),
+             (1, c["kv_heads"], c["seq"], 64), (1, c["heads"], c["seq"], 64)], 50 + i)
+        sets.append(tuple(t.to(dev) for t in (q, k, v, do)))
+
+    def fwd_bwd(i):
+        q, k, v, do = sets[i % len(sets)]
+        out, lse = ops.sdpa_forward(q, k, v, causal=True)
+        ops.sdpa_backward(do, q, k, v, out, lse, causal=True)
+
+    ms = _time(fwd_bwd, 30, warmup)
+    f = 3.5 * causal_forward_flops(1, c["heads"], c["seq"], 64)
+    extra["fwd_bwd_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+                               "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+                               "workload": "headline shape, forward + backward"}
+
+    # Headline shape at batch 8 (the whole-box batch on one GPU).
+    q8 = [tuple(torch.cat([s[j]] * 8, 0).contiguous() for j in range(3)) for s in sets[:4]]
+    ms = _time(lambda i: ops.sdpa_forward(*q8[i % 4], causal=True), 50, warmup)
+    f = causal_forward_flops(8, c["heads"], c["seq"], 64)
+    extra["fwd_b8_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+                              "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+
+    # Decode: batch 64, 16 / 2 heads, D 128, lengths uniform in [512, 4096].
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.randint(512, 4097, (64,), generator=g, dtype=torch.int32)
+    caches = []
+    for i in range(2):  # two caches, 268 MB each: nothing of a step's reads survives in L2
+        k = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(i), device=dev, dtype=torch.float32).to(torch.bfloat16)
+        v = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(9 + i), device=dev, dtype=torch.float32).to(torch.bfloat16)
+        caches.append((k, v))
+    q = ao.make_inputs([(64, 16, 1, 128)], 3)[0].to(dev)
+    ln = lengths.to(dev)
+    ms = _time(lambda i: ops.decode(q, *caches[i % 2], key_lengths=ln), 50, warmup)
+    nbytes = float(lengths.sum()) * 2 * (128 + 128) * 2 + 2 * q.numel() * 2
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    extra["decode_kv_gbs"] = {"value": gbs, "ms": ms, "bytes": nbytes,
+                              "frac_of_measured_hbm": gbs / peaks["hbm"], "frac_of_nominal_8000": gbs / 8000.0,
+                              "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0"}
+    del caches
+
+    # SDXL self-attention: B 2, 10 heads, S 4096, D 64, head views of [B, S, 640].
+    xs = [ao.make_inputs([(2, 4096, 3 * 640)], 70 + i)[0].to(dev).view(2, 4096, 3, 10, 64) for i in range(12)]
+    ms = _time(lambda i: ops.sdpa_forward(*(xs[i % 12][:, :, j].transpose(1, 2) for j in range(3))), 30, warmup)
+    f = 4.0 * 2 * 10 * 4096 * 4096 * 64
+    extra["sdxl_self_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+                                 "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    # SDXL cross-attention: 77 keys, the last 20 masked by a bool key-padding mask.
+    q = ao.make_inputs([(2, 10, 4096, 64)], 80)[0].to(dev)
+    k, v = (t.to(dev) for t in ao.make_inputs([(2, 10, 77, 64)] * 2, 81))
+    keep = torch.ones(2, 1, 1, 77, dtype=torch.bool, device=dev)
+    keep[..., 57:] = False
+    ms = _time(lambda i: ops.sdpa_forward(q, k, v, mask=keep), 30, warmup)
+    extra["sdxl_cross_ms"] = {"ms": ms, "gflop_kept_keys": 4.0 * 2 * 10 * 4096 * 57 * 64 / 1e9}
+
+    # Packed causal training attention: 16 heads, D 128, 65,536 tokens, lengths U[64, 4096].
+    g = torch.Generator().manual_seed(0)
+    lens, total = [], 0
+    while total < 65536:
+        n = int(torch.randint(64, 4097, (1,), generator=g))
+        n = min(n, 65536 - total)
+        lens.append(n)
+        total += n
+    if lens[-1] < 64 and len(lens) > 1:
+        lens[-2] += lens.pop()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    q, k, v, do = (torch.randn((65536, 16, 128), device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(4))
+    f = sum(4.0 * 16 * 128 * n * (n + 1) / 2 for n in lens)
+    ms = _time(lambda i: ops.varlen_forward(q, k, v, cu, cu, max(lens), max(lens), causal=True), 10, warmup)
+    extra["varlen_fwd_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms, "sequences": len(lens),
+                                  "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    out, lse = ops.varlen_forward(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+    ms = _time(lambda i: ops.varlen_backward(do, q, k, v, out, lse, cu, cu, max(lens), max(lens), causal=True), 5, warmup)
+    extra["varlen_bwd_tflops"] = {"value": 2.5 * f / (ms * 1e-3) / 1e12, "ms": ms,
+                                  "frac_of_measured_bf16": 2.5 * f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    return extra
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--headline-only", action="store_true", help="skip the extra legs and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

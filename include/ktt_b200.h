@@ -152,6 +152,13 @@ KTT_B200_API const char* ktt_b200_last_error(void);
 KTT_B200_API int ktt_b200_counters(int64_t* out8);
 KTT_B200_API int ktt_b200_reset_counters(void);
 
+/* Device-side failure report, the counterpart of the reference stream's "first failing op
+ * is raised at the next call" (csrc/core/device/stream.hpp:11-47). Every wait inside the
+ * tcgen05 kernels is bounded; one that runs out records a code in a host-visible word.
+ * Returns 0, or KTT_B200_ERR_DEVICE_WAIT with *code set (and clears the word). Call it
+ * after synchronising the stream; the next forward call also checks it. */
+KTT_B200_API int ktt_b200_device_status(int* code);
+
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward
  * kernels take the problem, 0 with the reason in ktt_b200_last_error(). Launches
  * nothing and touches no device memory. */

@@ -41,6 +41,7 @@ EXPORTS = (
     "ktt_b200_last_error",
     "ktt_b200_counters",
     "ktt_b200_reset_counters",
+    "ktt_b200_device_status",
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
     "ktt_b200_sdpa_forward",
@@ -240,6 +241,13 @@ def counters():
     buf = (_i64 * 8)()
     check(lib().ktt_b200_counters(buf), "counters")
     return {name: int(buf[i]) for i, name in enumerate(COUNTER_NAMES)}
+
+
+def device_status():
+    """Raises when a tcgen05 kernel gave up a bounded wait since the last check (call
+    after a synchronize)."""
+    code = ctypes.c_int(0)
+    check(lib().ktt_b200_device_status(ctypes.byref(code)), "device_status")
 
 
 def reset_counters():

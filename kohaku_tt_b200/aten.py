@@ -98,6 +98,14 @@ def _as_bf16(q, k, v):
     return q, k, v, False
 
 
+def _bias_or_none(attn_bias):
+    """Autograd hands a backward an undefined or empty tensor when the forward had no
+    bias."""
+    if attn_bias is None or attn_bias.numel() == 0:
+        return None
+    return attn_bias
+
+
 def _empty(device, dtype=torch.int64):
     return torch.empty((0,), dtype=dtype, device=device)
 
@@ -164,6 +172,7 @@ def _bias_gradient(grad_out, q, k, v, attn_bias, logsumexp, is_causal, scale):
 
 def _efficient_backward(grad_out, q, k, v, attn_bias, out, logsumexp, philox_seed, philox_offset,
                         dropout_p, grad_input_mask, is_causal=False, *, scale=None):
+    attn_bias = _bias_or_none(attn_bias)
     _checked(q, k, v, attn_bias, dropout_p, is_causal, scale)
     dq, dk, dv = ops.sdpa_backward(grad_out, q, k, v, out, logsumexp, mask=attn_bias,
                                    causal=is_causal, scale=scale)
@@ -190,6 +199,7 @@ def _cudnn_forward(q, k, v, attn_bias, compute_log_sumexp, dropout_p=0.0, is_cau
 
 def _cudnn_backward(grad_out, q, k, v, out, logsumexp, philox_seed, philox_offset, attn_bias,
                     cum_seq_q, cum_seq_k, max_q, max_k, dropout_p, is_causal, *, scale=None):
+    attn_bias = _bias_or_none(attn_bias)
     _checked(q, k, v, attn_bias, dropout_p, is_causal, scale)
     lse = logsumexp.squeeze(-1) if logsumexp.dim() == 4 else logsumexp
     return ops.sdpa_backward(grad_out, q, k, v, out, lse.contiguous(), mask=attn_bias,
@@ -215,8 +225,8 @@ def _overrideable_forward(q, k, v, attn_bias=None, dropout_p=0.0, is_causal=Fals
 def _overrideable_backward(grad_out, q, k, v, attn_bias, grad_input_mask, out, logsumexp, cum_seq_q,
                            cum_seq_k, max_q, max_k, dropout_p, is_causal, philox_seed, philox_offset,
                            *, scale=None):
-    _checked(q, k, v, attn_bias, dropout_p, is_causal, scale)
-    bias = attn_bias if attn_bias is not None and attn_bias.numel() else None
+    bias = _bias_or_none(attn_bias)
+    _checked(q, k, v, bias, dropout_p, is_causal, scale)
     dq, dk, dv = ops.sdpa_backward(grad_out, q, k, v, out, logsumexp, mask=bias,
                                    causal=is_causal, scale=scale)
     dbias = None

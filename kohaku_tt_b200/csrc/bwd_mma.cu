@@ -73,6 +73,9 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const AttnParams p) {
     lse2[1] = row_b < si.lq ? lg[(si.q_off + row_b) * p.ls[2]] * kLog2e : INFINITY;
     delta[0] = row_a < si.lq ? dl[row_a] : 0.f;
     delta[1] = row_b < si.lq ? dl[row_b] : 0.f;
+    // A row that saw no key has lse = -inf; +inf makes every P of it exactly 0.
+    if (lse2[0] == -INFINITY) lse2[0] = INFINITY;
+    if (lse2[1] == -INFINITY) lse2[1] = INFINITY;
 
     int kend = si.klen;
     if (p.causal) {
@@ -86,8 +89,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const AttnParams p) {
 
     for (int k0 = 0; k0 < kend; k0 += BN) {
         __syncthreads();
-        load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.lk, p.d);
-        load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.lk, p.dv);
+        load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.klen, p.d);
+        load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.klen, p.dv);
         __syncthreads();
 
         float s[BN / 8][4], dp[BN / 8][4];
@@ -176,8 +179,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const AttnParams p) {
 
     const __nv_bfloat16* kg = p.k + b * p.ks[0] + hk * p.ks[1] + static_cast<int64_t>(si.k_off) * p.ks[2];
     const __nv_bfloat16* vg = p.v + b * p.vs[0] + hk * p.vs[1] + static_cast<int64_t>(si.k_off) * p.vs[2];
-    load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.lk, p.d);
-    load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.lk, p.dv);
+    load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.klen, p.d);
+    load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.klen, p.dv);
 
     const int key_a = k0 + warp * 16 + g, key_b = key_a + 8;
 
@@ -208,7 +211,9 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const AttnParams p) {
             load_tile<BQ, DP, kThreads>(sdO, dog, p.dos[2], q0, si.lq, p.dv);
             if (threadIdx.x < BQ) {
                 const int i = q0 + threadIdx.x;
-                sLse[threadIdx.x] = i < si.lq ? lg[(si.q_off + i) * p.ls[2]] * kLog2e : INFINITY;
+                float l2 = i < si.lq ? lg[(si.q_off + i) * p.ls[2]] * kLog2e : INFINITY;
+                if (l2 == -INFINITY) l2 = INFINITY;  // a row without keys: P exactly 0
+                sLse[threadIdx.x] = l2;
                 sDelta[threadIdx.x] = i < si.lq ? dl[i] : 0.f;
             }
             __syncthreads();

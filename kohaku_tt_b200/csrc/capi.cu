@@ -61,6 +61,7 @@ void to_params(const ktt_b200_attn_args* a, AttnParams& p) {
     std::memset(&p, 0, sizeof(p));
     p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
     p.sq = a->sq; p.sk = a->sk; p.d = a->d; p.dv = a->dv; p.causal = a->causal;
+    p.total_q = a->total_q; p.total_k = a->total_k;
     p.scale = a->scale;
     p.scale_log2 = a->scale * kLog2e;
     p.q = static_cast<const __nv_bfloat16*>(a->q);
@@ -141,6 +142,14 @@ extern "C" const char* ktt_b200_last_error(void) { return g_error; }
 extern "C" int ktt_b200_counters(int64_t* out8) {
     if (!out8) return fail(KTT_B200_ERR_BAD_ARGUMENT, "counters: null output");
     for (int i = 0; i < 8; ++i) out8[i] = g_counters[i].load(std::memory_order_relaxed);
+    return 0;
+}
+
+extern "C" int ktt_b200_device_status(int* code) {
+    int c = 0;
+    const int rc = device_status(&c);
+    if (code) *code = c;
+    if (rc) return fail(rc, "a tcgen05 kernel gave up waiting (code %d)", c);
     return 0;
 }
 

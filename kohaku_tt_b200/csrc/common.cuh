@@ -18,6 +18,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 // Kernel-side view of ktt_b200_attn_args (same fields, device-friendly types).
 struct AttnParams {
     int batch, heads, kv_heads, sq, sk, d, dv, causal;
+    int64_t total_q, total_k;  // packed calls: rows of q and of k / v
     float scale;
     float scale_log2;  // scale * log2(e)
     const __nv_bfloat16* q;
@@ -159,5 +160,7 @@ int launch_forward_mma(const AttnParams& p, cudaStream_t stream);
 int launch_backward_mma(const AttnParams& p, cudaStream_t stream);
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
+// 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).
+int device_status(int* code);
 
 }  // namespace ktt

@@ -60,8 +60,8 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(const AttnParams p) {
 
     for (int k0 = 0; k0 < kend; k0 += BN) {
         __syncthreads();  // previous tile fully consumed (and sQ written on the first pass)
-        load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.lk, p.d);
-        load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.lk, p.dv);
+        load_tile<BN, DP, kThreads>(sK, kg, p.ks[2], k0, si.klen, p.d);
+        load_tile<BN, DP, kThreads>(sV, vg, p.vs[2], k0, si.klen, p.dv);
         __syncthreads();
 
         float s[BN / 8][4];

@@ -1,5 +1,705 @@
+// Prefill / training forward on the Blackwell tensor path: TMA tile loads, tcgen05.mma
+// with accumulators in tensor memory, online softmax in registers.
+//
+// One CTA owns 128 query rows of one (batch, head) and streams 128-key blocks:
+//
+//   warp 5 (producer)  TMA loads of Q once and of K/V blocks into a ring of stages
+//                      (128-byte swizzled tiles, mbarrier transaction counts)
+//   warp 4 (MMA)       one elected lane issues  S = Q K^T  (128 x 128 x D, both operands
+//                      K-major from shared memory, fp32 accumulator in TMEM columns
+//                      [0, 128)) and  O += P V  (128 x D x 128, P K-major and V MN-major
+//                      from shared memory, accumulator in TMEM columns [128, 128 + D))
+//   warps 0-3 (softmax) thread r owns query row r: reads its S row from TMEM, frees the
+//                      S buffer at once (the next S = Q K^T overlaps this block's
+//                      softmax), keeps the running maximum and sum in fp32, writes
+//                      P (bf16) into a double-buffered swizzled tile, and rescales O in
+//                      TMEM only when the maximum moved by more than 2^8 (the lazy
+//                      rescale of ktt_flash/compute.cpp, flash.md "row reference")
+//
+// Same arithmetic contract as the reference's flash forward (ktt_flash/compute.cpp:
+// 193-491): base-2 softmax with fp32 statistics, P rounded to bf16 before P V, fp32
+// accumulation, O / l and lse = ln2 (m + log2 l) at the end.
+//
+// Every wait on an mbarrier is bounded: when one runs out the CTA records a code in a
+// host-visible status word, stops waiting everywhere, frees its tensor memory and exits.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+
 namespace ktt {
-bool forward_tc5_takes(const AttnParams&, const char** why) { *why = "not built"; return false; }
-int launch_forward_tc5(const AttnParams&, cudaStream_t) { return fail(KTT_B200_ERR_UNSUPPORTED, "not built"); }
+namespace {
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 128;          // keys per block
+constexpr int kThreads = 192;     // 4 softmax warps + MMA warp + producer warp
+constexpr int kTmemCols = 256;    // S: [0, 128), O: [128, 128 + D)
+constexpr float kRescaleGap = 8.f;  // in log2 units
+constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false when it gave up (its own limit, or another role's).
+__device__ __noinline__ bool mbar_wait_slow(
+    uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status) {
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicCAS_system(status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(
+    uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, code, status);
+}
+
+__device__ __forceinline__ void tma_load_4d(
+    uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+          "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte swizzled tile (sm_100 format: version 1
+// at bit 46, layout type 2 = SWIZZLE_128B at bit 61). Offsets in bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(lbo >> 4) << 16;
+    d |= static_cast<uint64_t>(sbo >> 4) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, A K-major, B
+// K-major or MN-major, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+// ---- shared-memory plan -----------------------------------------------------------------
+
+template <int D>
+struct Plan {
+    static constexpr int kSub = D / 64;              // 64-column sub-tiles per operand tile
+    static constexpr int kTile = 128 * 64 * 2;       // one [128][64] bf16 sub-tile: 16 KiB
+    static constexpr int kStages = D == 64 ? 3 : 2;  // K/V ring depth
+    static constexpr int kQ = 0;
+    static constexpr int kK = kQ + kSub * kTile;
+    static constexpr int kV = kK + kStages * kSub * kTile;
+    static constexpr int kP = kV + kStages * kSub * kTile;  // 2 buffers x 2 sub-tiles
+    static constexpr int kBars = kP + 2 * 2 * kTile;
+    static constexpr int kBytes = kBars + 256;
+    // barrier indices (8 bytes each)
+    static constexpr int bQFull = 0;
+    static constexpr int bKVFull = 1;                 // + stage
+    static constexpr int bKVEmpty = bKVFull + kStages;
+    static constexpr int bSFull = bKVEmpty + kStages;
+    static constexpr int bSFree = bSFull + 1;
+    static constexpr int bPFull = bSFree + 1;         // + buffer
+    static constexpr int bPEmpty = bPFull + 2;        // + buffer
+    static constexpr int bODone = bPEmpty + 2;
+    static constexpr int bCount = bODone + 1;
+    static_assert(bCount * 8 + 16 <= 256, "barrier area");
+};
+
+struct Tc5Params {
+    AttnParams a;
+    int* status;        // host-visible: first wait that ran out, or 0
+    int dim_of[3][3];   // per operand (q, k, v): tensor-map coordinate slot (1..3) of the
+                        // row, head and batch dims
+};
+
+// ---- the kernel ------------------------------------------------------------------------
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const Tc5Params tp) {
+    using P = Plan<D>;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // The runtime aligns dynamic shared memory to 16 bytes only; swizzled tiles need 1024.
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + P::kBars;
+    auto bar = [&](int i) { return bars + 8u * i; };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
+
+    const AttnParams& p = tp.a;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int qb = gridDim.x - 1 - blockIdx.x;  // longest causal rows first
+    const SeqInfo si = seq_info(p, b);
+    const int q0 = qb * kBM;
+    if (q0 >= si.lq) return;  // whole CTA, before any barrier or allocation
+    const int hk = h / (p.heads / p.kv_heads);
+
+    int kend = si.klen;
+    if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
+    const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(P::bQFull), 1);
+        for (int s = 0; s < P::kStages; ++s) {
+            mbar_init(bar(P::bKVFull + s), 1);
+            mbar_init(bar(P::bKVEmpty + s), 1);
+        }
+        mbar_init(bar(P::bSFull), 1);
+        mbar_init(bar(P::bSFree), 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(P::bPFull + i), 128);
+            mbar_init(bar(P::bPEmpty + i), 1);
+        }
+        mbar_init(bar(P::bODone), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem;          // columns [0, 128)
+    const uint32_t tmem_o = tmem + 128;    // columns [128, 128 + D)
+
+    // Tensor-map coordinates: slot 0 is the head dim; rows, head and batch sit in the
+    // slots the host sorted them into by stride.
+    auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
+        c[tp.dim_of[operand][0]] = row;
+        c[tp.dim_of[operand][1]] = head;
+        c[tp.dim_of[operand][2]] = batch;
+    };
+
+    if (warp == 5) {
+        // ---------------- producer ----------------
+        if (lane == 0 && nblocks > 0) {
+            int c[4], cv[4];
+            const int batch = p.cu_q ? 0 : b;
+            c[0] = cv[0] = 0;
+            coords(0, si.q_off + q0, h, batch, c);
+            mbar_expect_tx(bar(P::bQFull), P::kSub * P::kTile);
+            for (int s = 0; s < P::kSub; ++s) {
+                tma_load_4d(sbase + P::kQ + s * P::kTile, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
+            }
+            int issued = 0;
+            for (int j = 0; j < nblocks; ++j) {
+                const int st = j % P::kStages;
+                if (j >= P::kStages) {
+                    if (!mbar_wait(bar(P::bKVEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status)) break;
+                }
+                coords(1, si.k_off + j * kBN, hk, batch, c);
+                coords(2, si.k_off + j * kBN, hk, batch, cv);
+                mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kTile);
+                for (int s = 0; s < P::kSub; ++s) {
+                    tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
+                    tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
+                }
+                ++issued;
+            }
+            if (*abort_flag) {
+                // Let copies already in flight land before the CTA's memory goes away.
+                for (int j = max(0, issued - P::kStages); j < issued; ++j) {
+                    const int st = j % P::kStages;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar(P::bKVFull + st), (j / P::kStages) & 1) && clock64() - t0 < kWaitCycles / 8) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && nblocks > 0) {
+            constexpr uint32_t idesc_s = instr_desc(kBN, false);
+            constexpr uint32_t idesc_o = instr_desc(D, true);
+            bool ok = mbar_wait(bar(P::bQFull), 0, abort_flag, 200, tp.status);
+            auto issue_s = [&](int j) {
+                const int st = j % P::kStages;
+                const uint32_t qa = sbase + P::kQ, ka = sbase + P::kK + st * P::kSub * P::kTile;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (ks / 4) * P::kTile + (ks % 4) * 32;
+                    tc_mma(tmem_s, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
+                }
+                tc_commit(bar(P::bSFull));
+            };
+            if (ok) ok = mbar_wait(bar(P::bKVFull + 0), 0, abort_flag, 210, tp.status);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0);
+            }
+            for (int j = 0; ok && j < nblocks; ++j) {
+                if (j + 1 < nblocks) {
+                    const int st1 = (j + 1) % P::kStages;
+                    ok = mbar_wait(bar(P::bKVFull + st1), ((j + 1) / P::kStages) & 1, abort_flag, 220 + st1, tp.status);
+                    if (ok) ok = mbar_wait(bar(P::bSFree), j & 1, abort_flag, 230, tp.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                const int pb = j & 1;
+                ok = mbar_wait(bar(P::bPFull + pb), (j >> 1) & 1, abort_flag, 240 + pb, tp.status);
+                if (!ok) break;
+                tc_fence_after();
+                const int st = j % P::kStages;
+                const uint32_t pa = sbase + P::kP + pb * 2 * P::kTile;
+                const uint32_t va = sbase + P::kV + st * P::kSub * P::kTile;
+#pragma unroll
+                for (int ks = 0; ks < kBN / 16; ++ks) {
+                    const uint32_t aoff = (ks / 4) * P::kTile + (ks % 4) * 32;
+                    // V is MN-major: 16 keys down = 16 rows of 128 bytes; the next 64
+                    // columns of D (second sub-tile) are one tile further (LBO).
+                    tc_mma(tmem_o, smem_desc(pa + aoff, 16, 1024), smem_desc(va + ks * 2048, P::kTile, 1024),
+                           idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(bar(P::bKVEmpty + st));
+                tc_commit(bar(P::bPEmpty + pb));
+                if (j + 1 == nblocks) tc_commit(bar(P::bODone));
+            }
+        }
+    } else {
+        // ---------------- softmax: thread = query row ----------------
+        const int row = warp * 32 + lane;           // row inside the tile = TMEM lane
+        const int qi = q0 + row;                    // row inside the sequence
+        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+        float m_ref = -INFINITY;  // reference maximum (base-2 logits), moved lazily
+        float l_sum = 0.f;
+        bool ok = true;
+        // Keys this row may see: [0, row_limit).
+        int row_limit = si.klen;
+        if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
+
+        for (int j = 0; j < nblocks; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), j & 1, abort_flag, 300, tp.status));
+            if (!ok) break;
+            tc_fence_after();
+            float s[kBN];
+#pragma unroll
+            for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tmem_s + lane_addr + c * 32, s + c * 32);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(P::bSFree));  // S is in registers: the next Q K^T may start
+
+            const int limit = row_limit - j * kBN;  // columns [0, limit) are visible
+            float mx = -INFINITY;
+            if (limit >= kBN) {
+#pragma unroll
+                for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, s[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBN; ++c) {
+                    s[c] = c < limit ? s[c] : -INFINITY;
+                    mx = fmaxf(mx, s[c]);
+                }
+            }
+            mx *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
+
+            // Lazy rescale: move the reference only when this block exceeds it by 2^8.
+            const bool move = mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, move)) {
+                float f = 1.f;
+                if (move) {
+                    f = fast_exp2(m_ref - mx);  // 0 on the first block
+                    m_ref = mx;
+                    l_sum *= f;
+                }
+                if (j > 0) {
+                    // O holds blocks [0, j): wait until block j - 1 has been accumulated.
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, 310, tp.status));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= f;
+                        tmem_st32(tmem_o + lane_addr + c * 32, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            // P buffer j & 1 was last read by block j - 2.
+            if (j >= 2) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 320, tp.status));
+                if (!ok) break;
+            }
+            unsigned char* pbuf = smem + P::kP + (j & 1) * 2 * P::kTile + row * 128;
+#pragma unroll
+            for (int cc = 0; cc < kBN / 8; ++cc) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(fmaf(s[cc * 8 + 2 * e], p.scale_log2, -m_use));
+                    const float p1 = fast_exp2(fmaf(s[cc * 8 + 2 * e + 1], p.scale_log2, -m_use));
+                    l_sum += p0 + p1;
+                    w[e] = pack_bf16(p0, p1);
+                }
+                // chunk cc of the row: sub-tile cc / 8, 16-byte slot (cc % 8) ^ (row % 8)
+                *reinterpret_cast<uint4*>(pbuf + (cc >> 3) * P::kTile + (((cc & 7) ^ (row & 7)) << 4)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            fence_async_smem();   // generic-proxy writes -> visible to the tensor core
+            tc_fence_before();    // orders the TMEM rescale before the arrive as well
+            mbar_arrive(bar(P::bPFull + (j & 1)));
+        }
+
+        // Epilogue: O / l and the row statistic. Every lane takes part in the TMEM reads
+        // (they are warp-wide); only the stores depend on the row being real.
+        if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bODone), 0, abort_flag, 330, tp.status));
+        if (ok) {
+            const bool real = qi < si.lq;
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2];
+            if (nblocks > 0) tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                if (nblocks > 0) {
+                    tmem_ld32(tmem_o + lane_addr + c * 32, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                }
+                if (real) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = pack_bf16(o[e * 8 + 0] * inv, o[e * 8 + 1] * inv);
+                        v.y = pack_bf16(o[e * 8 + 2] * inv, o[e * 8 + 3] * inv);
+                        v.z = pack_bf16(o[e * 8 + 4] * inv, o[e * 8 + 5] * inv);
+                        v.w = pack_bf16(o[e * 8 + 6] * inv, o[e * 8 + 7] * inv);
+                        *reinterpret_cast<uint4*>(og + c * 32 + e * 8) = v;
+                    }
+                }
+            }
+            if (real && p.lse) {
+                p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =
+                    l_sum > 0.f ? kLn2 * (m_ref + log2f(l_sum)) : -INFINITY;
+            }
+        }
+    }
+
+    // Teardown: everyone arrives (all waits above are bounded), then the allocating warp
+    // frees tensor memory.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(
+    CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeFn>(sym);
+        }
+    });
+    return fn;
+}
+
+int* status_word(int** device_view) {
+    // One pinned, device-mapped word per process: kernels record a wait that ran out
+    // there and the host reads it without a synchronisation.
+    static int* host = nullptr;
+    static int* dev = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped) == cudaSuccess) {
+            *host = 0;
+            if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev), host, 0) != cudaSuccess) dev = nullptr;
+        }
+    });
+    if (device_view) *device_view = dev;
+    return host;
+}
+
+// Order of the row / head / batch dims by stride, as the tensor map wants them ascending.
+struct DimOrder {
+    int slot_of[3];  // slot (1..3) of row, head, batch
+};
+
+bool encode_map(
+    CUtensorMap* map, const void* base, int d, int64_t rows, int64_t heads, int64_t batch,
+    const int64_t strides[3], const DimOrder& order, const char** why) {
+    EncodeFn fn = encode_fn();
+    if (!fn) {
+        *why = "cuTensorMapEncodeTiled is not available";
+        return false;
+    }
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), 1, 1, 1};
+    cuuint64_t str[4] = {0, 0, 0, 0};  // str[i] = byte stride of dim i + 1
+    cuuint32_t box[4] = {64, 1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const int64_t sizes[3] = {rows, heads, batch};
+    for (int i = 0; i < 3; ++i) {
+        const int slot = order.slot_of[i];
+        dims[slot] = static_cast<cuuint64_t>(sizes[i]);
+        str[slot - 1] = static_cast<cuuint64_t>(strides[i]) * 2;
+        if (i == 0) box[slot] = kBN;
+    }
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, str, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        *why = "cuTensorMapEncodeTiled refused the tensor layout";
+        return false;
+    }
+    return true;
+}
+
+// Effective (row, head, batch) sizes and strides of one operand, with size-1 dims given a
+// stride that keeps the ascending order valid; false when the layout cannot be a tensor map.
+bool operand_layout(
+    const void* base, int64_t rows, int64_t heads, int64_t batch, const int64_t in[3],
+    int64_t out[3], const char** why) {
+    if (reinterpret_cast<uintptr_t>(base) & 15) {
+        *why = "operands must be 16-byte aligned";
+        return false;
+    }
+    // in: (batch, head, row) element strides -> out: (row, head, batch)
+    out[0] = in[2];
+    out[1] = in[1];
+    out[2] = in[0];
+    const int64_t sizes[3] = {rows, heads, batch};
+    int64_t span = 64;  // a stride for size-1 dims: past everything else
+    for (int i = 0; i < 3; ++i) {
+        if (sizes[i] > 1) {
+            if (out[i] <= 0 || out[i] % 8) {
+                *why = "row, head and batch strides must be positive multiples of 8 elements";
+                return false;
+            }
+            span = span > out[i] * sizes[i] ? span : out[i] * sizes[i];
+        }
+    }
+    span = (span + 7) / 8 * 8;
+    for (int i = 0; i < 3; ++i) {
+        if (sizes[i] <= 1) out[i] = span;
+    }
+    return true;
+}
+
+DimOrder order_of(const int64_t strides[3]) {
+    int idx[3] = {0, 1, 2};
+    for (int a = 0; a < 3; ++a) {
+        for (int c = a + 1; c < 3; ++c) {
+            if (strides[idx[c]] < strides[idx[a]]) {
+                const int t = idx[a];
+                idx[a] = idx[c];
+                idx[c] = t;
+            }
+        }
+    }
+    DimOrder o;
+    for (int pos = 0; pos < 3; ++pos) o.slot_of[idx[pos]] = pos + 1;
+    return o;
+}
+
+}  // namespace
+
+bool forward_tc5_takes(const AttnParams& p, const char** why) {
+    if (p.d != p.dv || (p.d != 64 && p.d != 128)) {
+        *why = "head dim must be 64 or 128 with D == Dv";
+        return false;
+    }
+    if (p.mask_dtype != KTT_B200_MASK_NONE) {
+        *why = "masks run on the warp-MMA kernel";
+        return false;
+    }
+    if (p.key_lengths) {
+        // TMA cannot blank the rows past a length, and they may hold anything.
+        *why = "key lengths run on the warp-MMA and decode kernels";
+        return false;
+    }
+    for (int i = 0; i < 3; ++i) {
+        if (p.os[i] % 8) {
+            *why = "output strides must be multiples of 8 elements";
+            return false;
+        }
+    }
+    if (reinterpret_cast<uintptr_t>(p.out) & 15) {
+        *why = "the output must be 16-byte aligned";
+        return false;
+    }
+    const int64_t tq = p.cu_q ? p.total_q : p.sq, tk = p.cu_q ? p.total_k : p.sk;
+    const int64_t bq = p.cu_q ? 1 : p.batch;
+    int64_t s[3];
+    return operand_layout(p.q, tq, p.heads, bq, p.qs, s, why) &&
+           operand_layout(p.k, tk, p.kv_heads, bq, p.ks, s, why) &&
+           operand_layout(p.v, tk, p.kv_heads, bq, p.vs, s, why);
+}
+
+template <int D>
+int launch_tc5(const AttnParams& p, cudaStream_t stream) {
+    using P = Plan<D>;
+    const char* why = "";
+    const int64_t tq = p.cu_q ? p.total_q : p.sq, tk = p.cu_q ? p.total_k : p.sk;
+    const int64_t bq = p.cu_q ? 1 : p.batch;
+    int64_t sq[3], sk[3], sv[3];
+    if (!operand_layout(p.q, tq, p.heads, bq, p.qs, sq, &why) ||
+        !operand_layout(p.k, tk, p.kv_heads, bq, p.ks, sk, &why) ||
+        !operand_layout(p.v, tk, p.kv_heads, bq, p.vs, sv, &why)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+    }
+    const DimOrder orders[3] = {order_of(sq), order_of(sk), order_of(sv)};
+    CUtensorMap mq, mk, mv;
+    if (!encode_map(&mq, p.q, D, tq, p.heads, bq, sq, orders[0], &why) ||
+        !encode_map(&mk, p.k, D, tk, p.kv_heads, bq, sk, orders[1], &why) ||
+        !encode_map(&mv, p.v, D, tk, p.kv_heads, bq, sv, orders[2], &why)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+    }
+    Tc5Params tp;
+    tp.a = p;
+    int* dev_status = nullptr;
+    int* host_status = status_word(&dev_status);
+    if (!host_status || !dev_status) return fail(KTT_B200_ERR_LAUNCH, "tcgen05 forward: no status word");
+    if (*host_status != 0) {
+        const int code = *host_status;
+        *host_status = 0;
+        note_call(5);
+        return fail(KTT_B200_ERR_DEVICE_WAIT, "an earlier tcgen05 launch gave up waiting (code %d)", code);
+    }
+    tp.status = dev_status;
+    for (int o = 0; o < 3; ++o) {
+        for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
+    }
+    constexpr int smem = P::kBytes + 1024;  // slack for the 1024-byte alignment
+    if (int rc = check_cuda(
+            cudaFuncSetAttribute(fwd_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+            "cudaFuncSetAttribute(fwd_tc5)")) {
+        return rc;
+    }
+    dim3 grid((p.sq + kBM - 1) / kBM, p.heads, p.batch);
+    fwd_tc5_kernel<D><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
+    return check_cuda(cudaGetLastError(), "fwd_tc5 launch");
+}
+
+int launch_forward_tc5(const AttnParams& p, cudaStream_t stream) {
+    if (p.d == 64) return launch_tc5<64>(p, stream);
+    return launch_tc5<128>(p, stream);
+}
+
+int device_status(int* code) {
+    int* host = status_word(nullptr);
+    if (!host || *host == 0) {
+        if (code) *code = 0;
+        return 0;
+    }
+    if (code) *code = *host;
+    *host = 0;
+    note_call(5);
+    return KTT_B200_ERR_DEVICE_WAIT;
+}
+
+}  // namespace ktt
