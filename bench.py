@@ -174,23 +174,36 @@ def workload_config():
         "batch_per_gpu": c["batch"], "heads": c["heads"], "kv_heads": c["kv_heads"],
         "seq_len": c["seq"], "head_dim": c["head_dim"],
         "l2_policy": "each step uses the next of a ring of input sets larger than L2 in total",
+        "launch": "the K timed steps are one CUDA graph replay (K kernel launches back to back)",
         "parallelism": "one batch per GPU, no collective",
     }
 
 
-def timed_region(fn, steps, warmup, world):
+def timed_region(fn, steps, warmup, world, graph=False):
     """W untimed calls, then K calls between two events on the current stream, bracketed
-    by a barrier and a device synchronize; returns milliseconds (max over ranks)."""
+    by a barrier and a device synchronize; returns milliseconds (max over ranks). With
+    `graph` the K calls are captured once into a CUDA graph and the timed region is its
+    replay, so the device sees K back-to-back launches without host gaps."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    replay = None
+    if graph:
+        replay = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(replay):
+            for i in range(steps):
+                fn(warmup + i)
+        torch.cuda.synchronize()
     if world > 1:
         torch.distributed.barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     start.record()
-    for i in range(steps):
-        fn(warmup + i)
+    if replay is not None:
+        replay.replay()
+    else:
+        for i in range(steps):
+            fn(warmup + i)
     stop.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(stop)
@@ -242,7 +255,7 @@ def run_ours(args):
     parity = ktt.diff_stats(out, ao.ruler_dense(q0, k0, v0, causal=True))
 
     ktt.reset_counters()
-    ms = timed_region(step, steps, warmup, world)
+    ms = timed_region(step, steps, warmup, world, graph=not args.eager)
     launches = sum(ktt.counters()[k] for k in ("attention_flash", "attention_mma")) - warmup
     _lib.device_status()
     kernel = "tcgen05" if ktt.counters()["attention_flash"] else "warp-mma"
@@ -314,7 +327,7 @@ def run_ours(args):
 
 
 def _time(fn, steps, warmup):
-    return timed_region(fn, steps, warmup, 1) / steps
+    return timed_region(fn, steps, warmup, 1, graph=True) / steps
 
 
 def extra_legs(dev, peaks, warmup):
@@ -413,6 +426,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--headline-only", action="store_true", help="skip the extra legs and the CPU baseline")
     args = ap.parse_args()
     if args.impl == "reference":

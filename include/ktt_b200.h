@@ -159,6 +159,13 @@ KTT_B200_API int ktt_b200_reset_counters(void);
  * after synchronising the stream; the next forward call also checks it. */
 KTT_B200_API int ktt_b200_device_status(int* code);
 
+/* Profiling zones, the counterpart of the reference's FLASH_PROFILE device zones
+ * (ktt_flash/compute.cpp:25-30, program.hpp:56-65): with a device buffer of 64 x 8 int64
+ * set, CTA (0, 0, 0) of every tcgen05 forward launch stamps clock64 per key block (slots:
+ * S ready, pass 1 done, previous P V done, pass 2 done, P published, MMA lane before the
+ * next Q K^T, after the wait for P, after issuing P V). NULL turns it off (default). */
+KTT_B200_API int ktt_b200_set_trace(void* device_buffer);
+
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward
  * kernels take the problem, 0 with the reason in ktt_b200_last_error(). Launches
  * nothing and touches no device memory. */

@@ -42,6 +42,7 @@ EXPORTS = (
     "ktt_b200_counters",
     "ktt_b200_reset_counters",
     "ktt_b200_device_status",
+    "ktt_b200_set_trace",
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
     "ktt_b200_sdpa_forward",
@@ -197,6 +198,7 @@ def lib():
     handle.ktt_b200_decode_scratch_bytes.argtypes = [ctypes.POINTER(DecodeArgs)]
     handle.ktt_b200_decode_scratch_bytes.restype = _i64
     handle.ktt_b200_decode.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
+    handle.ktt_b200_set_trace.argtypes = [_ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]
     if handle.ktt_b200_abi_version() != 1:
         raise RuntimeError("kohaku_tt_b200: libktt_b200.so has another ABI version")

@@ -312,16 +312,11 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const AttnParams p) {
     }
 }
 
-template <typename K>
-int set_smem(K kernel, int smem, const char* what) {
-    return check_cuda(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), what);
-}
 
 template <int DP, int BN>
 int launch_dq(const AttnParams& p, cudaStream_t stream) {
     constexpr int smem = (2 * 64 + 2 * BN) * (DP + kPad) * 2;
-    if (int rc = set_smem(bwd_dq_kernel<DP, BN>, smem, "cudaFuncSetAttribute(bwd_dq)")) return rc;
+    if (int rc = ensure_smem(bwd_dq_kernel<DP, BN>, smem, "cudaFuncSetAttribute(bwd_dq)")) return rc;
     dim3 grid((p.sq + 63) / 64, p.heads, p.batch);
     bwd_dq_kernel<DP, BN><<<grid, kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "bwd_dq launch");
@@ -330,7 +325,7 @@ int launch_dq(const AttnParams& p, cudaStream_t stream) {
 template <int DP, int BQ, bool DK, bool DV>
 int launch_dkv(const AttnParams& p, cudaStream_t stream) {
     constexpr int smem = (2 * 64 + 2 * BQ) * (DP + kPad) * 2 + 2 * BQ * 4;
-    if (int rc = set_smem(bwd_dkv_kernel<DP, BQ, DK, DV>, smem, "cudaFuncSetAttribute(bwd_dkv)")) return rc;
+    if (int rc = ensure_smem(bwd_dkv_kernel<DP, BQ, DK, DV>, smem, "cudaFuncSetAttribute(bwd_dkv)")) return rc;
     dim3 grid((p.sk + 63) / 64, p.kv_heads, p.batch);
     bwd_dkv_kernel<DP, BQ, DK, DV><<<grid, kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "bwd_dkv launch");

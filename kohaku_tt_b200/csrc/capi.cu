@@ -3,6 +3,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "common.cuh"
 
@@ -27,6 +30,21 @@ int check_cuda(cudaError_t e, const char* what) {
 }
 
 void note_call(int which) { g_counters[which].fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+std::mutex g_smem_mutex;
+std::set<std::pair<const void*, int>> g_smem_done;
+}  // namespace
+
+bool smem_limit_known(const void* kernel, int device) {
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    return g_smem_done.count({kernel, device}) != 0;
+}
+
+void smem_limit_remember(const void* kernel, int device) {
+    std::lock_guard<std::mutex> lock(g_smem_mutex);
+    g_smem_done.insert({kernel, device});
+}
 
 namespace {
 
@@ -150,6 +168,11 @@ extern "C" int ktt_b200_device_status(int* code) {
     const int rc = device_status(&c);
     if (code) *code = c;
     if (rc) return fail(rc, "a tcgen05 kernel gave up waiting (code %d)", c);
+    return 0;
+}
+
+extern "C" int ktt_b200_set_trace(void* device_buffer) {
+    set_trace_buffer(static_cast<long long*>(device_buffer));
     return 0;
 }
 

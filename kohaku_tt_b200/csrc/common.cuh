@@ -99,7 +99,7 @@ __device__ __forceinline__ float mask_value(
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // pure: the compiler may schedule it freely
     return y;
 }
 
@@ -155,6 +155,26 @@ int check_cuda(cudaError_t e, const char* what);
 // 4 refused, 5 device-wait timeouts.
 void note_call(int which);
 
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device): the attribute
+// is sticky, and setting it outside of every launch keeps launches legal during stream
+// capture.
+bool smem_limit_known(const void* kernel, int device);   // capi.cu
+void smem_limit_remember(const void* kernel, int device);
+
+template <typename K>
+int ensure_smem(K kernel, int bytes, const char* what) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    const void* key = reinterpret_cast<const void*>(kernel);
+    if (smem_limit_known(key, dev)) return 0;
+    if (int rc = check_cuda(
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), what)) {
+        return rc;
+    }
+    smem_limit_remember(key, dev);
+    return 0;
+}
+
 // Launchers (one per kernel family).
 int launch_forward_mma(const AttnParams& p, cudaStream_t stream);
 int launch_backward_mma(const AttnParams& p, cudaStream_t stream);
@@ -162,5 +182,7 @@ int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).
 int device_status(int* code);
+// Profiling zones of the tcgen05 forward: a device buffer of 64 x 8 int64, or null.
+void set_trace_buffer(long long* device_buffer);
 
 }  // namespace ktt

@@ -417,12 +417,7 @@ int stream_ctas_for_device() {
 template <int D, int NS>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
     constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + 2 * 64 * 4;
-    if (int rc = check_cuda(
-            cudaFuncSetAttribute(
-                decode_stream_kernel<D, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-            "cudaFuncSetAttribute(decode_stream)")) {
-        return rc;
-    }
+    if (int rc = ensure_smem(decode_stream_kernel<D, NS>, smem, "cudaFuncSetAttribute(decode_stream)")) return rc;
     decode_plan_kernel<<<1, 1024, 0, stream>>>(p);
     if (int rc = check_cuda(cudaGetLastError(), "decode_plan launch")) return rc;
     decode_stream_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);

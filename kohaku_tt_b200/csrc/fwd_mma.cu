@@ -176,13 +176,7 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(const AttnParams p) {
 template <int DP, int BN>
 int launch(const AttnParams& p, cudaStream_t stream) {
     constexpr int smem = (kBM + 2 * BN) * (DP + kPad) * 2;
-    // Per device and per function; cheap enough to repeat on every call.
-    if (int rc = check_cuda(
-            cudaFuncSetAttribute(
-                fwd_mma_kernel<DP, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-            "cudaFuncSetAttribute(fwd_mma)")) {
-        return rc;
-    }
+    if (int rc = ensure_smem(fwd_mma_kernel<DP, BN>, smem, "cudaFuncSetAttribute(fwd_mma)")) return rc;
     dim3 grid((p.sq + kBM - 1) / kBM, p.heads, p.batch);
     fwd_mma_kernel<DP, BN><<<grid, kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "fwd_mma launch");

@@ -32,7 +32,6 @@ namespace ktt {
 namespace {
 
 constexpr int kBM = 128;          // query rows per CTA
-constexpr int kBN = 128;          // keys per block
 constexpr int kThreads = 192;     // 4 softmax warps + MMA warp + producer warp
 constexpr int kTmemCols = 256;    // S: [0, 128), O: [128, 128 + D)
 constexpr float kRescaleGap = 8.f;  // in log2 units
@@ -116,6 +115,28 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         : "memory");
 }
 
+// Same with the A operand in tensor memory (P): [a_tmem] holds 128 lanes x 8 columns of
+// packed bf16 pairs per K = 16 step.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane (32 packed bf16 values).
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(taddr)
+        : "memory");
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
@@ -146,6 +167,20 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x on the FMA pipe: round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic
+// for 2^f on [-0.5, 0.5] (max relative error 7.5e-5, far inside bf16 rounding) and n added
+// to the exponent field. The reference evaluates its exponentials the same way, with a
+// degree-2 polynomial on the multiply-add path (ktt_flash/sfpu.hpp:29-30).
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.f);
+    const float t = x + 12582912.f;
+    const float f = x - (t - 12582912.f);
+    float r = fmaf(f, 0.0551716648f, 0.2426111251f);
+    r = fmaf(r, f, 0.6932609677f);
+    r = fmaf(r, f, 0.9999280572f);
+    return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+
 // Shared-memory matrix descriptor for a 128-byte swizzled tile (sm_100 format: version 1
 // at bit 46, layout type 2 = SWIZZLE_128B at bit 61). Offsets in bytes.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
@@ -167,16 +202,19 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 
 // ---- shared-memory plan -----------------------------------------------------------------
 
-template <int D>
+// D: head dim (64 or 128). BN: keys per block, chosen so that one CTA needs about 112 KiB
+// of shared memory and 256 TMEM columns and two CTAs share an SM: while one CTA's softmax
+// warps work, the other CTA's MMAs and loads run.
+template <int D, int BN>
 struct Plan {
-    static constexpr int kSub = D / 64;              // 64-column sub-tiles per operand tile
-    static constexpr int kTile = 128 * 64 * 2;       // one [128][64] bf16 sub-tile: 16 KiB
-    static constexpr int kStages = D == 64 ? 3 : 2;  // K/V ring depth
+    static constexpr int kSub = D / 64;                  // 64-column sub-tiles of Q, K, V
+    static constexpr int kQSub = kBM * 128;              // one [128][64] bf16 sub-tile
+    static constexpr int kKVSub = BN * 128;              // one [BN][64] bf16 sub-tile
+    static constexpr int kStages = D == 64 ? 3 : 2;      // K/V ring depth (two CTAs per SM must fit)
     static constexpr int kQ = 0;
-    static constexpr int kK = kQ + kSub * kTile;
-    static constexpr int kV = kK + kStages * kSub * kTile;
-    static constexpr int kP = kV + kStages * kSub * kTile;  // 2 buffers x 2 sub-tiles
-    static constexpr int kBars = kP + 2 * 2 * kTile;
+    static constexpr int kK = kQ + kSub * kQSub;
+    static constexpr int kV = kK + kStages * kSub * kKVSub;
+    static constexpr int kBars = kV + kStages * kSub * kKVSub;
     static constexpr int kBytes = kBars + 256;
     // barrier indices (8 bytes each)
     static constexpr int bQFull = 0;
@@ -184,11 +222,11 @@ struct Plan {
     static constexpr int bKVEmpty = bKVFull + kStages;
     static constexpr int bSFull = bKVEmpty + kStages;
     static constexpr int bSFree = bSFull + 1;
-    static constexpr int bPFull = bSFree + 1;         // + buffer
-    static constexpr int bPEmpty = bPFull + 2;        // + buffer
-    static constexpr int bODone = bPEmpty + 2;
-    static constexpr int bCount = bODone + 1;
+    static constexpr int bPFull = bSFree + 1;
+    static constexpr int bPEmpty = bPFull + 1;
+    static constexpr int bCount = bPEmpty + 1;
     static_assert(bCount * 8 + 16 <= 256, "barrier area");
+    static_assert(BN % 64 == 0 && BN <= 128, "block of keys");
 };
 
 struct Tc5Params {
@@ -196,20 +234,33 @@ struct Tc5Params {
     int* status;        // host-visible: first wait that ran out, or 0
     int dim_of[3][3];   // per operand (q, k, v): tensor-map coordinate slot (1..3) of the
                         // row, head and batch dims
+    long long* trace;   // optional [64][8] clock64 stamps of CTA (0, 0, 0), else null
 };
+
+// Profiling zones (the counterpart of the reference's FLASH_PROFILE device zones,
+// ktt_flash/compute.cpp:25-30): CTA (0, 0, 0) stamps clock64 per key block.
+//   slots 0-4: softmax row 0 after S ready / pass 1 / P V of the previous block done /
+//              pass 2 / P published;  slots 5-7: MMA lane after its waits for the next
+//              Q K^T / after the wait for P / after issuing P V.
+__device__ __forceinline__ void zone(const Tc5Params& tp, bool who, int j, int slot) {
+    if (tp.trace && who && j < 64) tp.trace[j * 8 + slot] = clock64();
+}
 
 // ---- the kernel ------------------------------------------------------------------------
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
+template <int D, int BN>
+__global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const Tc5Params tp) {
-    using P = Plan<D>;
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    // The runtime aligns dynamic shared memory to 16 bytes only; swizzled tiles need 1024.
-    unsigned char* smem = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    using P = Plan<D, BN>;
+    extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
+    // Swizzled tiles need a 1024-byte aligned base. The dynamic window starts there on
+    // every launch seen so far; refuse to run rather than compute garbage if it does not.
+    if (sbase & 1023u) {
+        if (threadIdx.x == 0) atomicCAS_system(tp.status, 0, 900);
+        return;
+    }
     const uint32_t bars = sbase + P::kBars;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
@@ -226,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
 
     int kend = si.klen;
     if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
-    const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
+    const int nblocks = kend > 0 ? (kend + BN - 1) / BN : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(P::bQFull), 1);
@@ -236,11 +287,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         }
         mbar_init(bar(P::bSFull), 1);
         mbar_init(bar(P::bSFree), 128);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(P::bPFull + i), 128);
-            mbar_init(bar(P::bPEmpty + i), 1);
-        }
-        mbar_init(bar(P::bODone), 1);
+        mbar_init(bar(P::bPFull), 128);
+        mbar_init(bar(P::bPEmpty), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -250,8 +298,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem;          // columns [0, 128)
-    const uint32_t tmem_o = tmem + 128;    // columns [128, 128 + D)
+    // Columns: S fp32 [0, BN); P bf16 pairs [BN, BN + BN / 2) when D = 128 (BN = 64) or
+    // [192, 256) when D = 64 (BN = 128); O fp32 [128, 128 + D).
+    const uint32_t tmem_s = tmem;
+    const uint32_t tmem_o = tmem + 128;
+    const uint32_t tmem_p = tmem + (D == 64 ? 192 : BN);
 
     // Tensor-map coordinates: slot 0 is the head dim; rows, head and batch sit in the
     // slots the host sorted them into by stride.
@@ -268,9 +319,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             const int batch = p.cu_q ? 0 : b;
             c[0] = cv[0] = 0;
             coords(0, si.q_off + q0, h, batch, c);
-            mbar_expect_tx(bar(P::bQFull), P::kSub * P::kTile);
+            mbar_expect_tx(bar(P::bQFull), P::kSub * P::kQSub);
             for (int s = 0; s < P::kSub; ++s) {
-                tma_load_4d(sbase + P::kQ + s * P::kTile, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
+                tma_load_4d(sbase + P::kQ + s * P::kQSub, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
             }
             int issued = 0;
             for (int j = 0; j < nblocks; ++j) {
@@ -278,12 +329,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                 if (j >= P::kStages) {
                     if (!mbar_wait(bar(P::bKVEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status)) break;
                 }
-                coords(1, si.k_off + j * kBN, hk, batch, c);
-                coords(2, si.k_off + j * kBN, hk, batch, cv);
-                mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kTile);
+                coords(1, si.k_off + j * BN, hk, batch, c);
+                coords(2, si.k_off + j * BN, hk, batch, cv);
+                mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kKVSub);
                 for (int s = 0; s < P::kSub; ++s) {
-                    tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
-                    tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
+                    tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kKVSub, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
+                    tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kKVSub, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
                 }
                 ++issued;
             }
@@ -300,16 +351,21 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     } else if (warp == 4) {
         // ---------------- MMA issuer ----------------
         if (lane == 0 && nblocks > 0) {
-            constexpr uint32_t idesc_s = instr_desc(kBN, false);
+            constexpr uint32_t idesc_s = instr_desc(BN, false);
             constexpr uint32_t idesc_o = instr_desc(D, true);
             bool ok = mbar_wait(bar(P::bQFull), 0, abort_flag, 200, tp.status);
+            const bool mtracer = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            // Descriptors differ only in their 14-bit start-address field (bytes / 16):
+            // build each base once and add constants per MMA.
+            const uint64_t q_desc = smem_desc(sbase + P::kQ, 16, 1024);
+            const uint64_t k_desc = smem_desc(sbase + P::kK, 16, 1024);
+            const uint64_t v_desc = smem_desc(sbase + P::kV, P::kKVSub, 1024);
             auto issue_s = [&](int j) {
-                const int st = j % P::kStages;
-                const uint32_t qa = sbase + P::kQ, ka = sbase + P::kK + st * P::kSub * P::kTile;
+                const uint64_t kd = k_desc + static_cast<uint64_t>(((j % P::kStages) * P::kSub * P::kKVSub) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * P::kTile + (ks % 4) * 32;
-                    tc_mma(tmem_s, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
+                    tc_mma(tmem_s, q_desc + (((ks / 4) * P::kQSub + (ks % 4) * 32) >> 4),
+                           kd + (((ks / 4) * P::kKVSub + (ks % 4) * 32) >> 4), idesc_s, ks > 0);
                 }
                 tc_commit(bar(P::bSFull));
             };
@@ -325,26 +381,24 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                     if (ok) ok = mbar_wait(bar(P::bSFree), j & 1, abort_flag, 230, tp.status);
                     if (!ok) break;
                     tc_fence_after();
+                    zone(tp, mtracer, j, 5);
                     issue_s(j + 1);
                 }
-                const int pb = j & 1;
-                ok = mbar_wait(bar(P::bPFull + pb), (j >> 1) & 1, abort_flag, 240 + pb, tp.status);
+                ok = mbar_wait(bar(P::bPFull), j & 1, abort_flag, 240, tp.status);
                 if (!ok) break;
                 tc_fence_after();
+                zone(tp, mtracer, j, 6);
                 const int st = j % P::kStages;
-                const uint32_t pa = sbase + P::kP + pb * 2 * P::kTile;
-                const uint32_t va = sbase + P::kV + st * P::kSub * P::kTile;
+                const uint64_t vd = v_desc + static_cast<uint64_t>((st * P::kSub * P::kKVSub) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < kBN / 16; ++ks) {
-                    const uint32_t aoff = (ks / 4) * P::kTile + (ks % 4) * 32;
+                for (int ks = 0; ks < BN / 16; ++ks) {
                     // V is MN-major: 16 keys down = 16 rows of 128 bytes; the next 64
-                    // columns of D (second sub-tile) are one tile further (LBO).
-                    tc_mma(tmem_o, smem_desc(pa + aoff, 16, 1024), smem_desc(va + ks * 2048, P::kTile, 1024),
-                           idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    // columns of D (second sub-tile) are one sub-tile further (LBO).
+                    tc_mma_ts(tmem_o, tmem_p + ks * 8, vd + ((ks * 2048) >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(bar(P::bKVEmpty + st));
-                tc_commit(bar(P::bPEmpty + pb));
-                if (j + 1 == nblocks) tc_commit(bar(P::bODone));
+                tc_commit(bar(P::bPEmpty));
+                zone(tp, mtracer, j, 7);
             }
         }
     } else {
@@ -353,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         const int qi = q0 + row;                    // row inside the sequence
         const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
         float m_ref = -INFINITY;  // reference maximum (base-2 logits), moved lazily
-        float l_sum = 0.f;
+        float l_acc[4] = {0.f, 0.f, 0.f, 0.f};
         bool ok = true;
         // Keys this row may see: [0, row_limit).
         int row_limit = si.klen;
@@ -363,40 +417,49 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), j & 1, abort_flag, 300, tp.status));
             if (!ok) break;
             tc_fence_after();
-            float s[kBN];
-#pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tmem_s + lane_addr + c * 32, s + c * 32);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(bar(P::bSFree));  // S is in registers: the next Q K^T may start
+            const bool tracer = row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            zone(tp, tracer, j, 0);
+            const int limit = row_limit - j * BN;  // columns [0, limit) are visible
 
-            const int limit = row_limit - j * kBN;  // columns [0, limit) are visible
-            float mx = -INFINITY;
-            if (limit >= kBN) {
+            // Pass 1: the block's row maximum (next chunk's TMEM load in flight meanwhile).
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            {
+                float mbuf[2][32];
+                tmem_ld32(tmem_s + lane_addr, mbuf[0]);
 #pragma unroll
-                for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, s[c]);
-            } else {
+                for (int c = 0; c < BN / 32; ++c) {
+                    const float* s = mbuf[c & 1];
+                    tmem_wait_ld();
+                    if (c + 1 < BN / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, mbuf[(c + 1) & 1]);
+                    if (limit >= (c + 1) * 32) {
 #pragma unroll
-                for (int c = 0; c < kBN; ++c) {
-                    s[c] = c < limit ? s[c] : -INFINITY;
-                    mx = fmaxf(mx, s[c]);
+                        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], c * 32 + e < limit ? s[e] : -INFINITY);
+                    }
                 }
             }
-            mx *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            zone(tp, tracer, j, 1);
 
+            // O holds blocks [0, j) and P holds block j - 1 until that block's P V is done.
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty), (j - 1) & 1, abort_flag, 310, tp.status));
+                if (!ok) break;
+            }
+            zone(tp, tracer, j, 2);
             // Lazy rescale: move the reference only when this block exceeds it by 2^8.
-            const bool move = mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx > -INFINITY);
+            const bool move = mx > m_ref + kRescaleGap;
             if (__any_sync(0xffffffffu, move)) {
                 float f = 1.f;
                 if (move) {
                     f = fast_exp2(m_ref - mx);  // 0 on the first block
                     m_ref = mx;
-                    l_sum *= f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) l_acc[e] *= f;
                 }
                 if (j > 0) {
-                    // O holds blocks [0, j): wait until block j - 1 has been accumulated.
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, 310, tp.status));
-                    if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
@@ -411,36 +474,62 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                 }
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            // P buffer j & 1 was last read by block j - 2.
-            if (j >= 2) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty + (j & 1)), ((j >> 1) - 1) & 1, abort_flag, 320, tp.status));
-                if (!ok) break;
-            }
-            unsigned char* pbuf = smem + P::kP + (j & 1) * 2 * P::kTile + row * 128;
+
+            // Pass 2: P = 2^(s * scale - m), packed to bf16 pairs, into tensor memory where
+            // the P V MMA reads it as its A operand. The load of the next 32 columns is in
+            // flight while this chunk is exponentiated.
+            float sbuf[2][32];
+            tmem_ld32(tmem_s + lane_addr, sbuf[0]);
 #pragma unroll
-            for (int cc = 0; cc < kBN / 8; ++cc) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(fmaf(s[cc * 8 + 2 * e], p.scale_log2, -m_use));
-                    const float p1 = fast_exp2(fmaf(s[cc * 8 + 2 * e + 1], p.scale_log2, -m_use));
-                    l_sum += p0 + p1;
-                    w[e] = pack_bf16(p0, p1);
+            for (int c = 0; c < BN / 32; ++c) {
+                float* s = sbuf[c & 1];
+                tmem_wait_ld();
+                if (c + 1 < BN / 32) {
+                    tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, sbuf[(c + 1) & 1]);
+                } else {
+                    tc_fence_before();
+                    mbar_arrive(bar(P::bSFree));  // S has been read: the next Q K^T may start
                 }
-                // chunk cc of the row: sub-tile cc / 8, 16-byte slot (cc % 8) ^ (row % 8)
-                *reinterpret_cast<uint4*>(pbuf + (cc >> 3) * P::kTile + (((cc & 7) ^ (row & 7)) << 4)) =
-                    make_uint4(w[0], w[1], w[2], w[3]);
+                uint32_t w[16];
+                if (limit >= (c + 1) * 32) {
+                    // Every column visible: half of the exponentials run on the FMA pipe as
+                    // a polynomial (the MUFU unit is the narrowest pipe of this loop).
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float p0 = fast_exp2(fmaf(s[2 * e], p.scale_log2, -m_use));
+                        const float p1 = exp2_poly(fmaf(s[2 * e + 1], p.scale_log2, -m_use));
+                        l_acc[e & 3] += p0 + p1;
+                        w[e] = pack_bf16(p0, p1);
+                    }
+                } else {
+                    // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float s0 = c * 32 + 2 * e < limit ? s[2 * e] : -INFINITY;
+                        const float s1 = c * 32 + 2 * e + 1 < limit ? s[2 * e + 1] : -INFINITY;
+                        const float p0 = fast_exp2(fmaf(s0, p.scale_log2, -m_use));
+                        const float p1 = fast_exp2(fmaf(s1, p.scale_log2, -m_use));
+                        l_acc[e & 3] += p0 + p1;
+                        w[e] = pack_bf16(p0, p1);
+                    }
+                }
+                tmem_st16(tmem_p + lane_addr + c * 16, w);
             }
-            fence_async_smem();   // generic-proxy writes -> visible to the tensor core
-            tc_fence_before();    // orders the TMEM rescale before the arrive as well
-            mbar_arrive(bar(P::bPFull + (j & 1)));
+            tmem_wait_st();
+            zone(tp, tracer, j, 3);
+            tc_fence_before();    // P and any rescaled O are in TMEM before the arrive
+            mbar_arrive(bar(P::bPFull));
+            zone(tp, tracer, j, 4);
         }
 
         // Epilogue: O / l and the row statistic. Every lane takes part in the TMEM reads
         // (they are warp-wide); only the stores depend on the row being real.
-        if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bODone), 0, abort_flag, 330, tp.status));
+        if (ok && nblocks > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty), (nblocks - 1) & 1, abort_flag, 330, tp.status));
+        }
         if (ok) {
             const bool real = qi < si.lq;
+            const float l_sum = (l_acc[0] + l_acc[1]) + (l_acc[2] + l_acc[3]);
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2];
             if (nblocks > 0) tc_fence_after();
@@ -525,6 +614,8 @@ int* status_word(int** device_view) {
     return host;
 }
 
+long long* g_trace = nullptr;  // set by ktt_b200_set_trace; read at every launch
+
 // Order of the row / head / batch dims by stride, as the tensor map wants them ascending.
 struct DimOrder {
     int slot_of[3];  // slot (1..3) of row, head, batch
@@ -532,7 +623,7 @@ struct DimOrder {
 
 bool encode_map(
     CUtensorMap* map, const void* base, int d, int64_t rows, int64_t heads, int64_t batch,
-    const int64_t strides[3], const DimOrder& order, const char** why) {
+    const int64_t strides[3], const DimOrder& order, int box_rows, const char** why) {
     EncodeFn fn = encode_fn();
     if (!fn) {
         *why = "cuTensorMapEncodeTiled is not available";
@@ -547,7 +638,7 @@ bool encode_map(
         const int slot = order.slot_of[i];
         dims[slot] = static_cast<cuuint64_t>(sizes[i]);
         str[slot - 1] = static_cast<cuuint64_t>(strides[i]) * 2;
-        if (i == 0) box[slot] = kBN;
+        if (i == 0) box[slot] = static_cast<cuuint32_t>(box_rows);
     }
     const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, str, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -640,9 +731,9 @@ bool forward_tc5_takes(const AttnParams& p, const char** why) {
            operand_layout(p.v, tk, p.kv_heads, bq, p.vs, s, why);
 }
 
-template <int D>
+template <int D, int BN>
 int launch_tc5(const AttnParams& p, cudaStream_t stream) {
-    using P = Plan<D>;
+    using P = Plan<D, BN>;
     const char* why = "";
     const int64_t tq = p.cu_q ? p.total_q : p.sq, tk = p.cu_q ? p.total_k : p.sk;
     const int64_t bq = p.cu_q ? 1 : p.batch;
@@ -654,9 +745,9 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
     }
     const DimOrder orders[3] = {order_of(sq), order_of(sk), order_of(sv)};
     CUtensorMap mq, mk, mv;
-    if (!encode_map(&mq, p.q, D, tq, p.heads, bq, sq, orders[0], &why) ||
-        !encode_map(&mk, p.k, D, tk, p.kv_heads, bq, sk, orders[1], &why) ||
-        !encode_map(&mv, p.v, D, tk, p.kv_heads, bq, sv, orders[2], &why)) {
+    if (!encode_map(&mq, p.q, D, tq, p.heads, bq, sq, orders[0], kBM, &why) ||
+        !encode_map(&mk, p.k, D, tk, p.kv_heads, bq, sk, orders[1], BN, &why) ||
+        !encode_map(&mv, p.v, D, tk, p.kv_heads, bq, sv, orders[2], BN, &why)) {
         return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
     }
     Tc5Params tp;
@@ -671,23 +762,22 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
         return fail(KTT_B200_ERR_DEVICE_WAIT, "an earlier tcgen05 launch gave up waiting (code %d)", code);
     }
     tp.status = dev_status;
+    tp.trace = g_trace;
     for (int o = 0; o < 3; ++o) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
-    constexpr int smem = P::kBytes + 1024;  // slack for the 1024-byte alignment
-    if (int rc = check_cuda(
-            cudaFuncSetAttribute(fwd_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-            "cudaFuncSetAttribute(fwd_tc5)")) {
-        return rc;
-    }
+    constexpr int smem = P::kBytes;
+    if (int rc = ensure_smem(fwd_tc5_kernel<D, BN>, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
     dim3 grid((p.sq + kBM - 1) / kBM, p.heads, p.batch);
-    fwd_tc5_kernel<D><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
+    fwd_tc5_kernel<D, BN><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
     return check_cuda(cudaGetLastError(), "fwd_tc5 launch");
 }
 
+void set_trace_buffer(long long* device_buffer) { g_trace = device_buffer; }
+
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream) {
-    if (p.d == 64) return launch_tc5<64>(p, stream);
-    return launch_tc5<128>(p, stream);
+    if (p.d == 64) return launch_tc5<64, 128>(p, stream);
+    return launch_tc5<128, 64>(p, stream);
 }
 
 int device_status(int* code) {
