@@ -188,6 +188,22 @@ KTT_B200_API int ktt_b200_sdpa_backward(const ktt_b200_attn_args* args, void* st
 KTT_B200_API int64_t ktt_b200_decode_scratch_bytes(const ktt_b200_decode_args* args);
 KTT_B200_API int ktt_b200_decode(const ktt_b200_decode_args* args, void* stream);
 
+/* ktt_b200_decode for callers that must not allocate device memory while they run (a
+ * server that hands out all of the GPU at start-up and gives a plugin only input and
+ * output buffers; a decode loop that cannot afford the device-wide stall a cudaMalloc can
+ * cause). It has no counterpart in the reference. The split-K partials go to a fixed
+ * 4 MiB array inside the library, so args->scratch and args->scratch_bytes are ignored
+ * and the call makes no allocation of any kind.
+ *  - A call whose partials exceed 4 MiB (more than 216 (batch, kv head) pairs at head dim
+ *    128 on a 148-SM GPU, 728 at head dim 64) is refused with KTT_B200_ERR_UNSUPPORTED.
+ *  - The first call on a device does a one-time set-up (address of the array, kernel
+ *    attributes); make it before any stream capture.
+ *  - Every call on a device uses the same array. It needs no clearing between calls, but
+ *    calls that overlap on the GPU (different streams, no ordering) corrupt each other:
+ *    keep them on one stream or order them with events.
+ *  - Every GPU that loads the library holds the 4 MiB until the process ends. */
+KTT_B200_API int ktt_b200_decode_static(const ktt_b200_decode_args* args, void* stream);
+
 /* Merge of two partial attention results over disjoint key sets (ring attention steps):
  * out / lse [rows] are updated in place with (out2, lse2). fp32 lse, bf16 or fp32 out.
  * rows = B*H*S rows of dv values, row stride dv. No reference counterpart: the reference

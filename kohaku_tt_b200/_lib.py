@@ -50,6 +50,7 @@ EXPORTS = (
     "ktt_b200_sdpa_backward",
     "ktt_b200_decode_scratch_bytes",
     "ktt_b200_decode",
+    "ktt_b200_decode_static",
     "ktt_b200_merge_partials",
 )
 
@@ -198,6 +199,7 @@ def lib():
     handle.ktt_b200_decode_scratch_bytes.argtypes = [ctypes.POINTER(DecodeArgs)]
     handle.ktt_b200_decode_scratch_bytes.restype = _i64
     handle.ktt_b200_decode.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
+    handle.ktt_b200_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
     handle.ktt_b200_set_trace.argtypes = [_ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]
     if handle.ktt_b200_abi_version() != 1:

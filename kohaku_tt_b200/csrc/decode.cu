@@ -19,6 +19,8 @@
 //
 // Semantics are kohakutt.sdpa(q, k, v, key_lengths=) (attention.py:10-23): keys at or past
 // a length contribute nothing, whatever they hold; lengths are clamped to [1, Sk].
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ktt {
@@ -513,6 +515,108 @@ extern "C" int ktt_b200_decode(const ktt_b200_decode_args* a, void* stream) {
     }
     p.key_lengths = a->key_lengths;
     unsigned char* base = static_cast<unsigned char*>(a->scratch);
+    p.prefix = reinterpret_cast<int32_t*>(base);
+    p.part_m = reinterpret_cast<float*>(base + lay.prefix_bytes);
+    p.part_l = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes);
+    p.part_o = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes + lay.l_bytes);
+    p.slots = lay.slots;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    note_call(3);
+    if (a->d == 64) return launch<64, 6>(p, ctas, st);
+    return launch<128, 3>(p, ctas, st);
+}
+
+// ---- decode without any allocation ---------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory once they are running: an
+// inference server that carves up the whole GPU at start-up and hands its plugins nothing
+// but input and output buffers, or a decode loop with a latency budget in which a
+// cudaMalloc (which can stall the whole device) is not acceptable. For them the split-K
+// partials live in a fixed array that is part of the loaded module instead of in
+// caller-provided scratch.
+
+namespace ktt {
+namespace {
+
+// Room for the partials of 216 (batch, kv head) pairs at head dim 128 on a 148-SM part,
+// or 728 pairs at head dim 64. Each GPU that loads the library holds these 4 MiB until
+// the process exits.
+constexpr int64_t kStaticScratchBytes = 4ll << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device. In host code the array's name
+// is only a handle for the runtime, not an address a kernel can use, so the address is
+// asked for once per device (with that device current) and kept.
+int static_scratch_address(unsigned char** out) {
+    static std::mutex mutex;
+    static unsigned char* address[64] = {};
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "decode_static: cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!address[dev]) {
+        void* ptr = nullptr;
+        if (int rc = check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch), "decode_static: cudaGetSymbolAddress")) {
+            return rc;
+        }
+        address[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = address[dev];
+    return 0;
+}
+
+}  // namespace
+}  // namespace ktt
+
+// Same computation as ktt_b200_decode with the split-K partials in the library's own fixed
+// device array: no cudaMalloc, cudaFree or other allocating call is made, here or below.
+// args->scratch and args->scratch_bytes are ignored.
+//
+// Limits and rules:
+//  - The partials of the call must fit 4 MiB (see kStaticScratchBytes); a larger problem is
+//    refused with KTT_B200_ERR_UNSUPPORTED and a message that names both sizes. Use
+//    ktt_b200_decode with caller scratch for those.
+//  - The first call on each device looks up the array's device address and raises the
+//    kernel's shared-memory limit. Make that first call outside of any stream capture.
+//  - All calls on a device share the one array. Nothing in it has to be cleared between
+//    calls (every word a call reads, it has written first), but two calls whose kernels
+//    overlap on the GPU, for example on different streams, overwrite each other's
+//    partials. Keep calls to this entry point on one stream, or order them with events.
+extern "C" int ktt_b200_decode_static(const ktt_b200_decode_args* a, void* stream) {
+    if (const char* why = decode_refusal(a)) return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: %s", why);
+    if (!a->q || !a->k || !a->v || !a->out) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_static: null tensor pointer");
+    }
+    if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v)) & 15) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: k and v must be 16-byte aligned");
+    }
+    if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (reinterpret_cast<uintptr_t>(a->out) & 7)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: q must be 4-byte and out 8-byte aligned");
+    }
+    const int ctas = decode_ctas(a);
+    const ScratchLayout lay = scratch_layout(a->batch, a->kv_heads, a->d, ctas);
+    if (lay.total > kStaticScratchBytes) {
+        return fail(KTT_B200_ERR_UNSUPPORTED,
+                    "decode_static: this call needs %lld bytes of split-K partials, the built-in array holds %lld; "
+                    "use ktt_b200_decode with caller-provided scratch",
+                    static_cast<long long>(lay.total), static_cast<long long>(kStaticScratchBytes));
+    }
+    unsigned char* base = nullptr;
+    if (int rc = static_scratch_address(&base)) return rc;
+    DecodeParams p;
+    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.sq = a->sq; p.sk = a->sk; p.d = a->d;
+    p.scale_log2 = a->scale * kLog2e;
+    p.q = static_cast<const __nv_bfloat16*>(a->q);
+    p.k = static_cast<const __nv_bfloat16*>(a->k);
+    p.v = static_cast<const __nv_bfloat16*>(a->v);
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.lse = a->lse;
+    for (int i = 0; i < 3; ++i) {
+        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i];
+        p.vs[i] = a->v_strides[i]; p.os[i] = a->out_strides[i];
+    }
+    p.key_lengths = a->key_lengths;
     p.prefix = reinterpret_cast<int32_t*>(base);
     p.part_m = reinterpret_cast<float*>(base + lay.prefix_bytes);
     p.part_l = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes);
