@@ -163,7 +163,9 @@ KTT_B200_API int ktt_b200_device_status(int* code);
  * (ktt_flash/compute.cpp:25-30, program.hpp:56-65): with a device buffer of 64 x 8 int64
  * set, CTA (0, 0, 0) of every tcgen05 forward launch stamps clock64 per key block (slots:
  * S ready, pass 1 done, previous P V done, pass 2 done, P published, MMA lane before the
- * next Q K^T, after the wait for P, after issuing P V). NULL turns it off (default). */
+ * next Q K^T, after the wait for P, after issuing P V), and rows 64 .. 64 + 1023 receive per
+ * CTA its start and end on the global nanosecond timer, its SM and its key-block count; the
+ * buffer then holds (64 + 1024) x 8 int64. NULL turns it off (default). */
 KTT_B200_API int ktt_b200_set_trace(void* device_buffer);
 
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward

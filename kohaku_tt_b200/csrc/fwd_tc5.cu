@@ -32,8 +32,9 @@ namespace ktt {
 namespace {
 
 constexpr int kBM = 128;          // query rows per CTA
-constexpr int kThreads = 192;     // 4 softmax warps + MMA warp + producer warp
-constexpr int kTmemCols = 256;    // S: [0, 128), O: [128, 128 + D)
+constexpr int kBN = 128;          // keys per block
+constexpr int kThreads = 320;     // 8 softmax warps + MMA warp + producer warp
+constexpr int kTmemCols = 512;    // two S / P buffers, O_a, O_b
 constexpr float kRescaleGap = 8.f;  // in log2 units
 constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
 
@@ -42,8 +43,12 @@ constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {  // one elected lane
+    asm volatile(
+        "{\n.reg .pred q;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n}"
+        ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -80,9 +85,11 @@ __device__ __forceinline__ bool mbar_wait(
 
 __device__ __forceinline__ void tma_load_4d(
     uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+    asm volatile(  // one elected lane of the converged producer warp
+        "{\n.reg .pred q;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];\n}"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
@@ -103,14 +110,25 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// The tensor-core and TMA instructions below are issued by one elected lane of a CONVERGED
+// warp: every lane of the role's warp executes the surrounding code and `elect.sync`
+// predicates the instruction itself. Measured on B200: the same tcgen05.mma issued from a
+// lone lane of a diverged warp (the other lanes parked at a barrier) takes ~265 cycles per
+// instruction whatever its shape; from a converged warp it runs at the tensor core's rate
+// (65 cycles for 128 x 128 x 16).
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n.reg .pred q;\n"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}"
+        ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n.reg .pred p;\n"
+        "{\n.reg .pred p, q;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -119,9 +137,10 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
 // packed bf16 pairs per K = 16 step.
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n.reg .pred p;\n"
+        "{\n.reg .pred p, q;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        "elect.sync _|q, 0xffffffff;\n"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -181,6 +200,24 @@ __device__ __forceinline__ float exp2_poly(float x) {
     return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
 }
 
+// The same for two values at once on the packed fp32 pipe (fma.rn.f32x2 / add.f32x2 halve
+// the instruction count of the softmax loop, which is issue-bound).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    const float2 magic = make_float2(12582912.f, 12582912.f);
+    x.x = fmaxf(x.x, -125.f);
+    x.y = fmaxf(x.y, -125.f);
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 r = __ffma2_rn(f, make_float2(0.0551716648f, 0.0551716648f), make_float2(0.2426111251f, 0.2426111251f));
+    r = __ffma2_rn(r, f, make_float2(0.6932609677f, 0.6932609677f));
+    r = __ffma2_rn(r, f, make_float2(0.9999280572f, 0.9999280572f));
+    // n into the exponent field: one integer multiply-add per value (wraps like a shift).
+    r.x = __int_as_float(__float_as_int(t.x) * (1 << 23) + __float_as_int(r.x));
+    r.y = __int_as_float(__float_as_int(t.y) * (1 << 23) + __float_as_int(r.y));
+    return r;
+}
+
 // Shared-memory matrix descriptor for a 128-byte swizzled tile (sm_100 format: version 1
 // at bit 46, layout type 2 = SWIZZLE_128B at bit 61). Offsets in bytes.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
@@ -202,31 +239,34 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 
 // ---- shared-memory plan -----------------------------------------------------------------
 
-// D: head dim (64 or 128). BN: keys per block, chosen so that one CTA needs about 112 KiB
-// of shared memory and 256 TMEM columns and two CTAs share an SM: while one CTA's softmax
-// warps work, the other CTA's MMAs and loads run.
-template <int D, int BN>
+// One CTA per SM: 128 query rows, 128-key blocks, ten warps.
+//   warps 0-3  softmax group a: thread r owns row r and the block's keys [0, 64)
+//   warps 4-7  softmax group b: thread r owns row r and the block's keys [64, 128)
+//   warp 8     MMA issuer, warp 9 TMA producer
+// Each group keeps its own running maximum, sum and output accumulator (O_a, O_b), so the
+// two threads of a row never talk inside the loop; the halves are merged once at the end.
+// Tensor memory (512 columns): S / P buffers [0, 128) and [128, 256) (P overwrites the S
+// columns it came from as packed bf16), O_a [256, 256 + D), O_b [256 + D, 256 + 2 D).
+template <int D>
 struct Plan {
     static constexpr int kSub = D / 64;                  // 64-column sub-tiles of Q, K, V
-    static constexpr int kQSub = kBM * 128;              // one [128][64] bf16 sub-tile
-    static constexpr int kKVSub = BN * 128;              // one [BN][64] bf16 sub-tile
-    static constexpr int kStages = D == 64 ? 3 : 2;      // K/V ring depth (two CTAs per SM must fit)
+    static constexpr int kTile = 128 * 128;              // one [128][64] bf16 sub-tile
+    static constexpr int kStages = D == 64 ? 4 : 3;      // K/V ring depth
     static constexpr int kQ = 0;
-    static constexpr int kK = kQ + kSub * kQSub;
-    static constexpr int kV = kK + kStages * kSub * kKVSub;
-    static constexpr int kBars = kV + kStages * kSub * kKVSub;
+    static constexpr int kK = kQ + kSub * kTile;
+    static constexpr int kV = kK + kStages * kSub * kTile;
+    static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [2][128]: (m, l) per half
+    static constexpr int kBars = kML + 2 * 128 * 8;
     static constexpr int kBytes = kBars + 256;
     // barrier indices (8 bytes each)
     static constexpr int bQFull = 0;
     static constexpr int bKVFull = 1;                 // + stage
     static constexpr int bKVEmpty = bKVFull + kStages;
-    static constexpr int bSFull = bKVEmpty + kStages;
-    static constexpr int bSFree = bSFull + 1;
-    static constexpr int bPFull = bSFree + 1;
-    static constexpr int bPEmpty = bPFull + 1;
-    static constexpr int bCount = bPEmpty + 1;
+    static constexpr int bSFull = bKVEmpty + kStages;  // + buffer
+    static constexpr int bPFull = bSFull + 2;          // + half
+    static constexpr int bPVDone = bPFull + 2;         // + half
+    static constexpr int bCount = bPVDone + 2;
     static_assert(bCount * 8 + 16 <= 256, "barrier area");
-    static_assert(BN % 64 == 0 && BN <= 128, "block of keys");
 };
 
 struct Tc5Params {
@@ -239,20 +279,20 @@ struct Tc5Params {
 
 // Profiling zones (the counterpart of the reference's FLASH_PROFILE device zones,
 // ktt_flash/compute.cpp:25-30): CTA (0, 0, 0) stamps clock64 per key block.
-//   slots 0-4: softmax row 0 after S ready / pass 1 / P V of the previous block done /
-//              pass 2 / P published;  slots 5-7: MMA lane after its waits for the next
-//              Q K^T / after the wait for P / after issuing P V.
+//   slots 0-3: softmax row 0 of group a after S ready / S in registers and maximum known /
+//              exponentials done / P published;  slot 4: group b row 0 after P published;
+//   slots 5-7: MMA lane after issuing P V of half a / of half b / the next-but-one Q K^T.
 __device__ __forceinline__ void zone(const Tc5Params& tp, bool who, int j, int slot) {
     if (tp.trace && who && j < 64) tp.trace[j * 8 + slot] = clock64();
 }
 
 // ---- the kernel ------------------------------------------------------------------------
 
-template <int D, int BN>
-__global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const Tc5Params tp) {
-    using P = Plan<D, BN>;
+    using P = Plan<D>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
     // Swizzled tiles need a 1024-byte aligned base. The dynamic window starts there on
@@ -261,6 +301,10 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
         if (threadIdx.x == 0) atomicCAS_system(tp.status, 0, 900);
         return;
     }
+    // Second profiling zone set: rows 64.. of the trace buffer hold, per CTA, its start and
+    // end on the global nanosecond timer, its SM and its key-block count.
+    long long cta_t0 = 0;
+    if (tp.trace && threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
     const uint32_t bars = sbase + P::kBars;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
@@ -268,8 +312,11 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int qb = gridDim.x - 1 - blockIdx.x;  // longest causal rows first
+    // Heads vary fastest and query tiles run from the last (longest under a causal mask) to
+    // the first, so the CTAs the scheduler hands out first are the longest ones of every
+    // head, and the heads of one GQA group stream the same K/V tiles at the same time.
+    const int b = blockIdx.z, h = blockIdx.x;
+    const int qb = gridDim.y - 1 - blockIdx.y;
     const SeqInfo si = seq_info(p, b);
     const int q0 = qb * kBM;
     if (q0 >= si.lq) return;  // whole CTA, before any barrier or allocation
@@ -277,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
 
     int kend = si.klen;
     if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
-    const int nblocks = kend > 0 ? (kend + BN - 1) / BN : 0;
+    const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(P::bQFull), 1);
@@ -285,24 +332,21 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
             mbar_init(bar(P::bKVFull + s), 1);
             mbar_init(bar(P::bKVEmpty + s), 1);
         }
-        mbar_init(bar(P::bSFull), 1);
-        mbar_init(bar(P::bSFree), 128);
-        mbar_init(bar(P::bPFull), 128);
-        mbar_init(bar(P::bPEmpty), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(P::bSFull + i), 1);
+            mbar_init(bar(P::bPFull + i), 128);
+            mbar_init(bar(P::bPVDone + i), 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
-    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // Columns: S fp32 [0, BN); P bf16 pairs [BN, BN + BN / 2) when D = 128 (BN = 64) or
-    // [192, 256) when D = 64 (BN = 128); O fp32 [128, 128 + D).
-    const uint32_t tmem_s = tmem;
-    const uint32_t tmem_o = tmem + 128;
-    const uint32_t tmem_p = tmem + (D == 64 ? 192 : BN);
+    const uint32_t tmem_o = tmem + 256;    // O_a, then O_b
 
     // Tensor-map coordinates: slot 0 is the head dim; rows, head and batch sit in the
     // slots the host sorted them into by stride.
@@ -312,29 +356,29 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
         c[tp.dim_of[operand][2]] = batch;
     };
 
-    if (warp == 5) {
-        // ---------------- producer ----------------
-        if (lane == 0 && nblocks > 0) {
+    if (warp == 9) {
+        // ---------------- producer (whole warp, converged) ----------------
+        if (nblocks > 0) {
             int c[4], cv[4];
             const int batch = p.cu_q ? 0 : b;
             c[0] = cv[0] = 0;
             coords(0, si.q_off + q0, h, batch, c);
-            mbar_expect_tx(bar(P::bQFull), P::kSub * P::kQSub);
+            mbar_expect_tx(bar(P::bQFull), P::kSub * P::kTile);
             for (int s = 0; s < P::kSub; ++s) {
-                tma_load_4d(sbase + P::kQ + s * P::kQSub, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
+                tma_load_4d(sbase + P::kQ + s * P::kTile, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
             }
             int issued = 0;
             for (int j = 0; j < nblocks; ++j) {
                 const int st = j % P::kStages;
                 if (j >= P::kStages) {
-                    if (!mbar_wait(bar(P::bKVEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status)) break;
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bKVEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status))) break;
                 }
-                coords(1, si.k_off + j * BN, hk, batch, c);
-                coords(2, si.k_off + j * BN, hk, batch, cv);
-                mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kKVSub);
+                coords(1, si.k_off + j * kBN, hk, batch, c);
+                coords(2, si.k_off + j * kBN, hk, batch, cv);
+                mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kTile);
                 for (int s = 0; s < P::kSub; ++s) {
-                    tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kKVSub, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
-                    tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kKVSub, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
+                    tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
+                    tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
                 }
                 ++issued;
             }
@@ -348,107 +392,111 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
                 }
             }
         }
-    } else if (warp == 4) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0 && nblocks > 0) {
-            constexpr uint32_t idesc_s = instr_desc(BN, false);
+    } else if (warp == 8) {
+        // ---------------- MMA issuer (whole warp, converged) ----------------
+        if (nblocks > 0) {
+            constexpr uint32_t idesc_s = instr_desc(kBN, false);
             constexpr uint32_t idesc_o = instr_desc(D, true);
-            bool ok = mbar_wait(bar(P::bQFull), 0, abort_flag, 200, tp.status);
-            const bool mtracer = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            const bool mtracer = lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
             // Descriptors differ only in their 14-bit start-address field (bytes / 16):
             // build each base once and add constants per MMA.
             const uint64_t q_desc = smem_desc(sbase + P::kQ, 16, 1024);
             const uint64_t k_desc = smem_desc(sbase + P::kK, 16, 1024);
-            const uint64_t v_desc = smem_desc(sbase + P::kV, P::kKVSub, 1024);
+            const uint64_t v_desc = smem_desc(sbase + P::kV, P::kTile, 1024);
             auto issue_s = [&](int j) {
-                const uint64_t kd = k_desc + static_cast<uint64_t>(((j % P::kStages) * P::kSub * P::kKVSub) >> 4);
+                const uint64_t kd = k_desc + static_cast<uint64_t>(((j % P::kStages) * P::kSub * P::kTile) >> 4);
+                const uint32_t d_s = tmem + (j & 1) * 128;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    tc_mma(tmem_s, q_desc + (((ks / 4) * P::kQSub + (ks % 4) * 32) >> 4),
-                           kd + (((ks / 4) * P::kKVSub + (ks % 4) * 32) >> 4), idesc_s, ks > 0);
+                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                    tc_mma(d_s, q_desc + off, kd + off, idesc_s, ks > 0);
                 }
-                tc_commit(bar(P::bSFull));
+                tc_commit(bar(P::bSFull + (j & 1)));
             };
-            if (ok) ok = mbar_wait(bar(P::bKVFull + 0), 0, abort_flag, 210, tp.status);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bQFull), 0, abort_flag, 200, tp.status));
+            for (int j = 0; ok && j < 2 && j < nblocks; ++j) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + j), 0, abort_flag, 210 + j, tp.status));
+                if (ok) {
+                    tc_fence_after();
+                    issue_s(j);
+                }
             }
             for (int j = 0; ok && j < nblocks; ++j) {
-                if (j + 1 < nblocks) {
-                    const int st1 = (j + 1) % P::kStages;
-                    ok = mbar_wait(bar(P::bKVFull + st1), ((j + 1) / P::kStages) & 1, abort_flag, 220 + st1, tp.status);
-                    if (ok) ok = mbar_wait(bar(P::bSFree), j & 1, abort_flag, 230, tp.status);
+                const int st = j % P::kStages;
+                const uint64_t vd = v_desc + static_cast<uint64_t>((st * P::kSub * P::kTile) >> 4);
+                const uint32_t p_tmem = tmem + (j & 1) * 128;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), j & 1, abort_flag, 240 + g, tp.status));
                     if (!ok) break;
                     tc_fence_after();
-                    zone(tp, mtracer, j, 5);
-                    issue_s(j + 1);
-                }
-                ok = mbar_wait(bar(P::bPFull), j & 1, abort_flag, 240, tp.status);
-                if (!ok) break;
-                tc_fence_after();
-                zone(tp, mtracer, j, 6);
-                const int st = j % P::kStages;
-                const uint64_t vd = v_desc + static_cast<uint64_t>((st * P::kSub * P::kKVSub) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    // V is MN-major: 16 keys down = 16 rows of 128 bytes; the next 64
-                    // columns of D (second sub-tile) are one sub-tile further (LBO).
-                    tc_mma_ts(tmem_o, tmem_p + ks * 8, vd + ((ks * 2048) >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        // A: this half's P, 8 TMEM columns per 16 keys. B: V is MN-major, 16
+                        // keys down = 16 rows of 128 bytes; the second 64 columns of D are
+                        // one sub-tile further (LBO).
+                        tc_mma_ts(tmem_o + g * D, p_tmem + g * 64 + ks * 8,
+                                  vd + (((g * 4 + ks) * 2048) >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar(P::bPVDone + g));
+                    zone(tp, mtracer, j, 5 + g);
                 }
+                if (!ok) break;
                 tc_commit(bar(P::bKVEmpty + st));
-                tc_commit(bar(P::bPEmpty));
-                zone(tp, mtracer, j, 7);
+                if (j + 2 < nblocks) {
+                    // Both groups have published P of block j, so they are done with this S
+                    // buffer; MMAs run in issue order, so the P V reads above precede the
+                    // overwrite.
+                    const int st2 = (j + 2) % P::kStages;
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + st2), ((j + 2) / P::kStages) & 1, abort_flag, 220 + st2, tp.status));
+                    if (!ok) break;
+                    tc_fence_after();
+                    zone(tp, mtracer, j, 4);
+                    issue_s(j + 2);
+                    zone(tp, mtracer, j, 7);
+                }
             }
         }
     } else {
-        // ---------------- softmax: thread = query row ----------------
-        const int row = warp * 32 + lane;           // row inside the tile = TMEM lane
-        const int qi = q0 + row;                    // row inside the sequence
-        const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-        float m_ref = -INFINITY;  // reference maximum (base-2 logits), moved lazily
-        float l_acc[4] = {0.f, 0.f, 0.f, 0.f};
+        // ---------------- softmax: thread = (query row, half of the block's keys) ----------------
+        const int g = warp >> 2;                        // 0: keys [0, 64), 1: keys [64, 128)
+        const int row = (warp & 3) * 32 + lane;         // row inside the tile = TMEM lane
+        const int qi = q0 + row;                        // row inside the sequence
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool tracer = row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        float m_ref = -INFINITY;  // this half's reference maximum (base-2 logits), moved lazily
+        float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // running sums, 4 lanes
         bool ok = true;
         // Keys this row may see: [0, row_limit).
         int row_limit = si.klen;
         if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
 
         for (int j = 0; j < nblocks; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), j & 1, abort_flag, 300, tp.status));
+            const uint32_t s_addr = tmem + (j & 1) * 128 + g * 64 + lane_addr;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull + (j & 1)), (j >> 1) & 1, abort_flag, 300 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
-            const bool tracer = row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-            zone(tp, tracer, j, 0);
-            const int limit = row_limit - j * BN;  // columns [0, limit) are visible
-
-            // Pass 1: the block's row maximum (next chunk's TMEM load in flight meanwhile).
+            zone(tp, tracer && g == 0, j, 0);
+            float s[64];
+            tmem_ld32(s_addr, s);
+            tmem_ld32(s_addr + 32, s + 32);
+            tmem_wait_ld();
+            const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            {
-                float mbuf[2][32];
-                tmem_ld32(tmem_s + lane_addr, mbuf[0]);
+            const bool whole = limit >= 64;
+            if (whole) {
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    const float* s = mbuf[c & 1];
-                    tmem_wait_ld();
-                    if (c + 1 < BN / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, mbuf[(c + 1) & 1]);
-                    if (limit >= (c + 1) * 32) {
+                for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+            } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], c * 32 + e < limit ? s[e] : -INFINITY);
-                    }
+                for (int e = 0; e < 64; ++e) {
+                    s[e] = e < limit ? s[e] : -INFINITY;
+                    mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            zone(tp, tracer, j, 1);
+            zone(tp, tracer && g == 0, j, 1);
 
-            // O holds blocks [0, j) and P holds block j - 1 until that block's P V is done.
-            if (j > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty), (j - 1) & 1, abort_flag, 310, tp.status));
-                if (!ok) break;
-            }
-            zone(tp, tracer, j, 2);
             // Lazy rescale: move the reference only when this block exceeds it by 2^8.
             const bool move = mx > m_ref + kRescaleGap;
             if (__any_sync(0xffffffffu, move)) {
@@ -456,108 +504,115 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
                 if (move) {
                     f = fast_exp2(m_ref - mx);  // 0 on the first block
                     m_ref = mx;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) l_acc[e] *= f;
+                    l2[0] = __fmul2_rn(l2[0], make_float2(f, f));
+                    l2[1] = __fmul2_rn(l2[1], make_float2(f, f));
                 }
                 if (j > 0) {
+                    // O of this half holds blocks [0, j): wait for block j - 1's P V.
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + g), (j - 1) & 1, abort_flag, 310 + g, tp.status));
+                    if (!ok) break;
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
                         float o[32];
-                        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+                        tmem_ld32(tmem_o + g * D + lane_addr + c * 32, o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 32; ++e) o[e] *= f;
-                        tmem_st32(tmem_o + lane_addr + c * 32, o);
+                        tmem_st32(tmem_o + g * D + lane_addr + c * 32, o);
                     }
                     tmem_wait_st();
                 }
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
 
-            // Pass 2: P = 2^(s * scale - m), packed to bf16 pairs, into tensor memory where
-            // the P V MMA reads it as its A operand. The load of the next 32 columns is in
-            // flight while this chunk is exponentiated.
-            float sbuf[2][32];
-            tmem_ld32(tmem_s + lane_addr, sbuf[0]);
+            // P = 2^(s * scale - m) as packed bf16 pairs, two values per instruction where
+            // the packed fp32 pipe allows.
+            uint32_t w[32];
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
+            if (whole) {
+                // Every column visible: every other pair of exponentials runs on the FMA pipe
+                // as a polynomial (MUFU is the narrowest pipe of this loop).
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                float* s = sbuf[c & 1];
-                tmem_wait_ld();
-                if (c + 1 < BN / 32) {
-                    tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, sbuf[(c + 1) & 1]);
-                } else {
-                    tc_fence_before();
-                    mbar_arrive(bar(P::bSFree));  // S has been read: the next Q K^T may start
-                }
-                uint32_t w[16];
-                if (limit >= (c + 1) * 32) {
-                    // Every column visible: half of the exponentials run on the FMA pipe as
-                    // a polynomial (the MUFU unit is the narrowest pipe of this loop).
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float p0 = fast_exp2(fmaf(s[2 * e], p.scale_log2, -m_use));
-                        const float p1 = exp2_poly(fmaf(s[2 * e + 1], p.scale_log2, -m_use));
-                        l_acc[e & 3] += p0 + p1;
-                        w[e] = pack_bf16(p0, p1);
+                for (int e = 0; e < 32; ++e) {
+                    const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
+                    float2 pr;
+                    if (e & 1) {
+                        pr = exp2_poly2(x);
+                    } else {
+                        pr.x = fast_exp2(x.x);
+                        pr.y = fast_exp2(x.y);
                     }
-                } else {
-                    // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float s0 = c * 32 + 2 * e < limit ? s[2 * e] : -INFINITY;
-                        const float s1 = c * 32 + 2 * e + 1 < limit ? s[2 * e + 1] : -INFINITY;
-                        const float p0 = fast_exp2(fmaf(s0, p.scale_log2, -m_use));
-                        const float p1 = fast_exp2(fmaf(s1, p.scale_log2, -m_use));
-                        l_acc[e & 3] += p0 + p1;
-                        w[e] = pack_bf16(p0, p1);
-                    }
+                    l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
+                    w[e] = pack_bf16(pr.x, pr.y);
                 }
-                tmem_st16(tmem_p + lane_addr + c * 16, w);
+            } else {
+                // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
+                    const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
+                    w[e] = pack_bf16(pr.x, pr.y);
+                }
             }
+            zone(tp, tracer && g == 0, j, 2);
+            // P overwrites the first 32 of the 64 S columns this thread has just read.
+            tmem_st32(s_addr, reinterpret_cast<const float*>(w));
             tmem_wait_st();
-            zone(tp, tracer, j, 3);
-            tc_fence_before();    // P and any rescaled O are in TMEM before the arrive
-            mbar_arrive(bar(P::bPFull));
-            zone(tp, tracer, j, 4);
+            tc_fence_before();
+            mbar_arrive(bar(P::bPFull + g));
+            zone(tp, tracer && g == 0, j, 3);
         }
 
-        // Epilogue: O / l and the row statistic. Every lane takes part in the TMEM reads
-        // (they are warp-wide); only the stores depend on the row being real.
+        // Epilogue: merge the two halves of each row and normalise. Every lane takes part in
+        // the TMEM reads and in the 256-thread barrier whatever happened above.
         if (ok && nblocks > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPEmpty), (nblocks - 1) & 1, abort_flag, 330, tp.status));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 0), (nblocks - 1) & 1, abort_flag, 330, tp.status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 1), (nblocks - 1) & 1, abort_flag, 331, tp.status));
         }
+        float2* ml = reinterpret_cast<float2*>(smem + P::kML);
+        const float l_mine = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
+        ml[g * 128 + row] = make_float2(m_ref, l_mine);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (ok) {
-            const bool real = qi < si.lq;
-            const float l_sum = (l_acc[0] + l_acc[1]) + (l_acc[2] + l_acc[3]);
+            const float2 other = ml[(g ^ 1) * 128 + row];
+            const float m_all = fmaxf(m_ref, other.x);
+            const float base = (m_all == -INFINITY) ? 0.f : m_all;
+            const float f_mine = fast_exp2(m_ref - base), f_other = fast_exp2(other.x - base);
+            const float l_sum = l_mine * f_mine + other.y * f_other;
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2];
+            const float fa = (g == 0 ? f_mine : f_other) * inv, fb = (g == 0 ? f_other : f_mine) * inv;
+            const bool real = qi < si.lq;
+            // Group a writes output columns [0, D / 2), group b the rest.
+            __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2] + g * (D / 2);
             if (nblocks > 0) tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                float o[32];
+            for (int c = 0; c < D / 64; ++c) {
+                float oa[32], ob[32];
                 if (nblocks > 0) {
-                    tmem_ld32(tmem_o + lane_addr + c * 32, o);
+                    tmem_ld32(tmem_o + lane_addr + g * (D / 2) + c * 32, oa);
+                    tmem_ld32(tmem_o + D + lane_addr + g * (D / 2) + c * 32, ob);
                     tmem_wait_ld();
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                    for (int e = 0; e < 32; ++e) oa[e] = ob[e] = 0.f;
                 }
                 if (real) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         uint4 v;
-                        v.x = pack_bf16(o[e * 8 + 0] * inv, o[e * 8 + 1] * inv);
-                        v.y = pack_bf16(o[e * 8 + 2] * inv, o[e * 8 + 3] * inv);
-                        v.z = pack_bf16(o[e * 8 + 4] * inv, o[e * 8 + 5] * inv);
-                        v.w = pack_bf16(o[e * 8 + 6] * inv, o[e * 8 + 7] * inv);
+                        v.x = pack_bf16(oa[e * 8 + 0] * fa + ob[e * 8 + 0] * fb, oa[e * 8 + 1] * fa + ob[e * 8 + 1] * fb);
+                        v.y = pack_bf16(oa[e * 8 + 2] * fa + ob[e * 8 + 2] * fb, oa[e * 8 + 3] * fa + ob[e * 8 + 3] * fb);
+                        v.z = pack_bf16(oa[e * 8 + 4] * fa + ob[e * 8 + 4] * fb, oa[e * 8 + 5] * fa + ob[e * 8 + 5] * fb);
+                        v.w = pack_bf16(oa[e * 8 + 6] * fa + ob[e * 8 + 6] * fb, oa[e * 8 + 7] * fa + ob[e * 8 + 7] * fb);
                         *reinterpret_cast<uint4*>(og + c * 32 + e * 8) = v;
                     }
                 }
             }
-            if (real && p.lse) {
+            if (real && g == 0 && p.lse) {
                 p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =
-                    l_sum > 0.f ? kLn2 * (m_ref + log2f(l_sum)) : -INFINITY;
+                    l_sum > 0.f ? kLn2 * (m_all + log2f(l_sum)) : -INFINITY;
             }
         }
     }
@@ -566,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
     // frees tensor memory.
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         if (*abort_flag) {
             const long long t0 = clock64();
             while (clock64() - t0 < 2000000) {
@@ -574,6 +629,20 @@ __global__ void __launch_bounds__(kThreads, 2) fwd_tc5_kernel(
         }
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+    }
+    if (tp.trace && threadIdx.x == 0) {
+        const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (cta < 1024) {
+            long long t1;
+            unsigned smid;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            long long* row = tp.trace + (64 + cta) * 8;
+            row[0] = cta_t0;
+            row[1] = t1;
+            row[2] = smid;
+            row[3] = nblocks;
+        }
     }
 }
 
@@ -731,9 +800,10 @@ bool forward_tc5_takes(const AttnParams& p, const char** why) {
            operand_layout(p.v, tk, p.kv_heads, bq, p.vs, s, why);
 }
 
-template <int D, int BN>
+template <int D>
 int launch_tc5(const AttnParams& p, cudaStream_t stream) {
-    using P = Plan<D, BN>;
+    using P = Plan<D>;
+    constexpr int BN = kBN;
     const char* why = "";
     const int64_t tq = p.cu_q ? p.total_q : p.sq, tk = p.cu_q ? p.total_k : p.sk;
     const int64_t bq = p.cu_q ? 1 : p.batch;
@@ -767,17 +837,17 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     constexpr int smem = P::kBytes;
-    if (int rc = ensure_smem(fwd_tc5_kernel<D, BN>, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
-    dim3 grid((p.sq + kBM - 1) / kBM, p.heads, p.batch);
-    fwd_tc5_kernel<D, BN><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
+    if (int rc = ensure_smem(fwd_tc5_kernel<D>, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
+    dim3 grid(p.heads, (p.sq + kBM - 1) / kBM, p.batch);
+    fwd_tc5_kernel<D><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
     return check_cuda(cudaGetLastError(), "fwd_tc5 launch");
 }
 
 void set_trace_buffer(long long* device_buffer) { g_trace = device_buffer; }
 
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream) {
-    if (p.d == 64) return launch_tc5<64, 128>(p, stream);
-    return launch_tc5<128, 64>(p, stream);
+    if (p.d == 64) return launch_tc5<64>(p, stream);
+    return launch_tc5<128>(p, stream);
 }
 
 int device_status(int* code) {
