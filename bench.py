@@ -320,26 +320,66 @@ def run_ours(args):
                       "bf16 tensors after one warm-up",
             "parity_vs_f64": {k: cpu_parity[k] for k in ("abs_max", "rel_median", "cosine")},
         }
+    if world > 1 and not args.headline_only:
+        ring = ring_leg(dev, peaks, rank, world)
+        if rank == 0:
+            line.setdefault("extra", {})["ring_attention"] = ring
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
+def ring_leg(dev, peaks, rank, world):
+    """The long-context configuration: one causal sequence of 16,384 x N tokens (131,072 at
+    N = 8), 16 heads, D 128, sharded zigzag over the N GPUs, K/V blocks passed around the
+    ring by NCCL send/recv. Every rank takes part; times are the max over ranks."""
+    from kohaku_tt_b200 import parallel
+
+    tokens, heads, d = 16384, 16, 128
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    q, k, v, do = (torch.randn((1, heads, tokens, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                   for _ in range(4))
+    seq = tokens * world
+    fwd_flops = 4.0 * heads * d * (seq * (seq + 1) / 2)
+
+    def timed(fn, steps):
+        fn()
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) / steps], dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t.item()
+
+    ms_f = timed(lambda: parallel.ring_forward(q, k, v), 3)
+    out, lse = parallel.ring_forward(q, k, v)
+    ms_b = timed(lambda: parallel.ring_backward(do, q, k, v, out, lse), 1)
+    kv_bytes = 2 * tokens * heads * d * 2
+    return {
+        "workload": f"one causal sequence of {seq} tokens, 16 heads, D 128, zigzag over {world} GPUs",
+        "forward_tflops": fwd_flops / (ms_f * 1e-3) / 1e12, "forward_ms": ms_f,
+        "forward_frac_of_measured_bf16_per_gpu": fwd_flops / (ms_f * 1e-3) / 1e12 / world / peaks["bf16"],
+        "backward_tflops": 2.5 * fwd_flops / (ms_b * 1e-3) / 1e12, "backward_ms": ms_b,
+        "ring_bytes_per_step_per_gpu": kv_bytes,
+    }
+
+
 def _time(fn, steps, warmup):
     return timed_region(fn, steps, warmup, 1, graph=True) / steps
 
 
-def extra_legs(dev, peaks, warmup):
-    """The other configurations of the benchmark plan, each timed the same way."""
-    import kohaku_tt_b200 as ktt
+def leg_fwd_bwd(dev, peaks, warmup):
+    """Forward + backward on the headline shape (3.5 x the forward FLOPs)."""
     from kohaku_tt_b200 import ops
     from oracle import attention_oracle as ao
 
-    extra = {}
     c = HEADLINE
-
-    # Forward + backward on the headline shape (3.5 x the forward FLOPs).
     sets = []
     for i in range(8):
         q, k, v, do = ao.make_inputs(
@@ -354,18 +394,33 @@ def extra_legs(dev, peaks, warmup):
 
     ms = _time(fwd_bwd, 30, warmup)
     f = 3.5 * causal_forward_flops(1, c["heads"], c["seq"], 64)
-    extra["fwd_bwd_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
-                               "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
-                               "workload": "headline shape, forward + backward"}
+    return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+            "workload": "headline shape, forward + backward"}
 
-    # Headline shape at batch 8 (the whole-box batch on one GPU).
-    q8 = [tuple(torch.cat([s[j]] * 8, 0).contiguous() for j in range(3)) for s in sets[:4]]
+
+def leg_fwd_b8(dev, peaks, warmup):
+    """Headline shape at batch 8 (the whole-box batch on one GPU)."""
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
+    c = HEADLINE
+    q8 = []
+    for i in range(4):
+        q, k, v = ao.make_inputs(
+            [(8, c["heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64)], 60 + i)
+        q8.append((q.to(dev), k.to(dev), v.to(dev)))
     ms = _time(lambda i: ops.sdpa_forward(*q8[i % 4], causal=True), 50, warmup)
     f = causal_forward_flops(8, c["heads"], c["seq"], 64)
-    extra["fwd_b8_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
-                              "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
 
-    # Decode: batch 64, 16 / 2 heads, D 128, lengths uniform in [512, 4096].
+
+def leg_decode(dev, peaks, warmup):
+    """Decode: batch 64, 16 / 2 heads, D 128, lengths uniform in [512, 4096]."""
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
     g = torch.Generator().manual_seed(0)
     lengths = torch.randint(512, 4097, (64,), generator=g, dtype=torch.int32)
     caches = []
@@ -378,26 +433,41 @@ def extra_legs(dev, peaks, warmup):
     ms = _time(lambda i: ops.decode(q, *caches[i % 2], key_lengths=ln), 50, warmup)
     nbytes = float(lengths.sum()) * 2 * (128 + 128) * 2 + 2 * q.numel() * 2
     gbs = nbytes / (ms * 1e-3) / 1e9
-    extra["decode_kv_gbs"] = {"value": gbs, "ms": ms, "bytes": nbytes,
-                              "frac_of_measured_hbm": gbs / peaks["hbm"], "frac_of_nominal_8000": gbs / 8000.0,
-                              "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0"}
-    del caches
+    return {"value": gbs, "ms": ms, "bytes": nbytes,
+            "frac_of_measured_hbm": gbs / peaks["hbm"], "frac_of_nominal_8000": gbs / 8000.0,
+            "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0"}
 
-    # SDXL self-attention: B 2, 10 heads, S 4096, D 64, head views of [B, S, 640].
+
+def leg_sdxl_self(dev, peaks, warmup):
+    """SDXL self-attention: B 2, 10 heads, S 4096, D 64, head views of [B, S, 640]."""
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
     xs = [ao.make_inputs([(2, 4096, 3 * 640)], 70 + i)[0].to(dev).view(2, 4096, 3, 10, 64) for i in range(12)]
     ms = _time(lambda i: ops.sdpa_forward(*(xs[i % 12][:, :, j].transpose(1, 2) for j in range(3))), 30, warmup)
     f = 4.0 * 2 * 10 * 4096 * 4096 * 64
-    extra["sdxl_self_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
-                                 "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
-    # SDXL cross-attention: 77 keys, the last 20 masked by a bool key-padding mask.
+    return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+
+
+def leg_sdxl_cross(dev, peaks, warmup):
+    """SDXL cross-attention: 77 keys, the last 20 masked by a bool key-padding mask."""
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
     q = ao.make_inputs([(2, 10, 4096, 64)], 80)[0].to(dev)
     k, v = (t.to(dev) for t in ao.make_inputs([(2, 10, 77, 64)] * 2, 81))
     keep = torch.ones(2, 1, 1, 77, dtype=torch.bool, device=dev)
     keep[..., 57:] = False
     ms = _time(lambda i: ops.sdpa_forward(q, k, v, mask=keep), 30, warmup)
-    extra["sdxl_cross_ms"] = {"ms": ms, "gflop_kept_keys": 4.0 * 2 * 10 * 4096 * 57 * 64 / 1e9}
+    return {"ms": ms, "gflop_kept_keys": 4.0 * 2 * 10 * 4096 * 57 * 64 / 1e9}
 
-    # Packed causal training attention: 16 heads, D 128, 65,536 tokens, lengths U[64, 4096].
+
+def leg_varlen(dev, peaks, warmup):
+    """Packed causal training attention: 16 heads, D 128, 65,536 tokens, lengths
+    U[64, 4096] (seed 0), forward and backward."""
+    from kohaku_tt_b200 import ops
+
     g = torch.Generator().manual_seed(0)
     lens, total = [], 0
     while total < 65536:
@@ -411,13 +481,38 @@ def extra_legs(dev, peaks, warmup):
     q, k, v, do = (torch.randn((65536, 16, 128), device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(4))
     f = sum(4.0 * 16 * 128 * n * (n + 1) / 2 for n in lens)
     ms = _time(lambda i: ops.varlen_forward(q, k, v, cu, cu, max(lens), max(lens), causal=True), 10, warmup)
-    extra["varlen_fwd_tflops"] = {"value": f / (ms * 1e-3) / 1e12, "ms": ms, "sequences": len(lens),
-                                  "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    fwd = {"value": f / (ms * 1e-3) / 1e12, "ms": ms, "sequences": len(lens),
+           "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
     out, lse = ops.varlen_forward(q, k, v, cu, cu, max(lens), max(lens), causal=True)
     ms = _time(lambda i: ops.varlen_backward(do, q, k, v, out, lse, cu, cu, max(lens), max(lens), causal=True), 5, warmup)
-    extra["varlen_bwd_tflops"] = {"value": 2.5 * f / (ms * 1e-3) / 1e12, "ms": ms,
-                                  "frac_of_measured_bf16": 2.5 * f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
-    return extra
+    bwd = {"value": 2.5 * f / (ms * 1e-3) / 1e12, "ms": ms,
+           "frac_of_measured_bf16": 2.5 * f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+    return {"forward": fwd, "backward": bwd}
+
+
+LEGS = {
+    "fwd_bwd_tflops": leg_fwd_bwd,
+    "fwd_b8_tflops": leg_fwd_b8,
+    "decode_kv_gbs": leg_decode,
+    "sdxl_self_tflops": leg_sdxl_self,
+    "sdxl_cross_ms": leg_sdxl_cross,
+    "varlen_tflops": leg_varlen,
+}
+
+
+def extra_legs(dev, peaks, warmup):
+    """The other configurations of the benchmark plan, each timed the same way."""
+    return {name: fn(dev, peaks, warmup) for name, fn in LEGS.items()}
+
+
+def run_leg(args):
+    """`--leg NAME`: one extra leg alone (for profiling a single kernel family)."""
+    torch.cuda.set_device(0)
+    import kohaku_tt_b200 as ktt
+
+    ktt.build()
+    ktt.install()
+    print(json.dumps({args.leg: LEGS[args.leg](torch.device("cuda", 0), measured_peaks(), max(args.warmup, 3))}))
 
 
 def main():
@@ -428,8 +523,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--headline-only", action="store_true", help="skip the extra legs and the CPU baseline")
+    ap.add_argument("--leg", default=None, choices=sorted(LEGS), help="run one extra leg alone and print it")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.leg:
+        run_leg(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

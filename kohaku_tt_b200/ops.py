@@ -131,7 +131,12 @@ def _dense_args(q, k, v, mask, key_lengths, causal, scale, kernel):
     args = _lib.AttnArgs()
     args.batch, args.heads, args.kv_heads = b, h, k.shape[1]
     args.sq, args.sk, args.d, args.dv = sq, k.shape[2], d, v.shape[3]
-    args.causal = _lib.CAUSAL_TOP_LEFT if causal else _lib.CAUSAL_NONE
+    # True is PyTorch's top-left alignment; "bottom_right" puts the diagonal at the last
+    # query and key (what a ring step over the tail of a longer sequence needs).
+    if causal == "bottom_right":
+        args.causal = _lib.CAUSAL_BOTTOM_RIGHT
+    else:
+        args.causal = _lib.CAUSAL_TOP_LEFT if causal else _lib.CAUSAL_NONE
     args.scale = float(scale) if scale is not None else 1.0 / math.sqrt(d)
     args.kernel = _kernel_code(kernel)
     args.q, args.k, args.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
