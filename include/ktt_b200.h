@@ -137,7 +137,8 @@ typedef struct ktt_b200_decode_args {
     int64_t out_strides[3];
     const int32_t* key_lengths; /* int32 [B] on the device, or NULL for sk everywhere */
     int32_t splits;    /* 0 = choose; else the number of sequence splits */
-    void* scratch;     /* ktt_b200_decode_scratch_bytes() bytes, 256-byte aligned */
+    void* scratch;     /* ktt_b200_decode_scratch_bytes() bytes, 256-byte aligned, zero-filled
+                          once before its first use (the kernel leaves its counters zero) */
     int64_t scratch_bytes;
 } ktt_b200_decode_args;
 

@@ -1,4 +1,4 @@
-// Memory-bound GQA decode against a static KV cache: split over the sequence.
+// Memory-bound GQA decode against a static KV cache: split over the sequence, one launch.
 //
 // The reference has no dedicated decode kernel: a call with few query rows runs the
 // prefill kernel's key-lengths variant once per (batch, query head), so a GQA group
@@ -8,17 +8,24 @@
 // 64-key tiles so that every CTA streams the same number of bytes whatever the
 // per-sequence lengths are:
 //
-//   plan    : prefix sum of ceil(len_b / 64) over the batch (lengths stay on the device)
+//   plan    : every CTA scans ceil(len_b / 64) over the batch into shared memory (the
+//             lengths stay on the device; batch <= 1024)
 //   stream  : CTA c owns tile units [c*upc, (c+1)*upc) of the (batch, kv head) pairs laid
-//             end to end; per pair segment it produces an unnormalised partial
-//             (O, m, l) in fp32 scratch. K/V rows arrive by 16-byte cp.async into a
-//             swizzled ring of stages, one private pipeline per warp (16 keys per tile
-//             each), scores and P.V on warp MMA, running max / sum in fp32.
-//   combine : per pair, merge its partials with the usual max / rescale rule, divide by
-//             the sum, write bf16.
+//             end to end. K/V rows arrive by 16-byte cp.async into a swizzled ring of
+//             stages, one private pipeline per warp (16 keys per tile each), scores and
+//             P.V on warp MMA, running max / sum in fp32.
+//   finish  : a pair that lies inside one CTA is normalised and written at once. Otherwise
+//             each CTA stores its unnormalised partial (O, m, l) in fp32 scratch and takes
+//             a ticket on the pair's counter; the CTA that draws the last ticket merges the
+//             pair's partials (fixed order: deterministic), writes bf16 and puts the
+//             counter back to zero.
+//
+// Scratch: int32 counters [pairs] that must be zero before the first call (the kernel
+// leaves them zero), then per slot 16 maxima, 16 sums and 16 x D partial outputs.
 //
 // Semantics are kohakutt.sdpa(q, k, v, key_lengths=) (attention.py:10-23): keys at or past
 // a length contribute nothing, whatever they hold; lengths are clamped to [1, Sk].
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -35,10 +42,10 @@ struct DecodeParams {
     float* lse;
     int64_t qs[3], ks[3], vs[3], os[3];
     const int32_t* key_lengths;
-    int32_t* prefix;  // [batch + 1] tiles before each batch entry (one kv head)
-    float* part_m;    // [slots][16]
-    float* part_l;    // [slots][16]
-    float* part_o;    // [slots][16][d]
+    int32_t* counters;  // [batch * kv_heads] tickets, zero between calls
+    float* part_m;      // [slots][16]
+    float* part_l;      // [slots][16]
+    float* part_o;      // [slots][16][d]
     int slots;
 };
 
@@ -46,6 +53,8 @@ namespace {
 
 constexpr int kTile = 64;      // keys per tile (16 per warp)
 constexpr int kThreads = 128;
+constexpr int kMaxBatch = 1024;  // prefix sums live in shared memory
+constexpr int kMaxPending = 8;   // stored partials per CTA before their tickets are drawn
 
 __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
     if (!p.key_lengths) return p.sk;
@@ -54,41 +63,35 @@ __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
     return l > p.sk ? p.sk : l;
 }
 
-// prefix[b] = sum_{b' < b} ceil(len_b' / 64); one block, any batch size.
-__global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p) {
-    __shared__ int warp_sums[32];
-    __shared__ int carry;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
+// prefix[b] = sum_{b' < b} ceil(len_b' / 64) for b in [0, batch], by one CTA of 128 threads.
+__device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix, int* warp_sums) {
+    constexpr int kPer = kMaxBatch / kThreads;  // 8 consecutive entries per thread
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int base = 0; base < p.batch; base += 1024) {
-        const int b = base + threadIdx.x;
-        const int tiles = b < p.batch ? (clamp_len(p, b) + kTile - 1) / kTile : 0;
-        int x = tiles;
+    int tiles[kPer], mine = 0;
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int y = __shfl_up_sync(0xffffffffu, x, off);
-            if (lane >= off) x += y;
-        }
-        if (lane == 31) warp_sums[warp] = x;
-        __syncthreads();
-        if (warp == 0) {
-            int w = warp_sums[lane];
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const int y = __shfl_up_sync(0xffffffffu, w, off);
-                if (lane >= off) w += y;
-            }
-            warp_sums[lane] = w;
-        }
-        __syncthreads();
-        const int before = carry + (warp ? warp_sums[warp - 1] : 0) + x - tiles;
-        if (b < p.batch) p.prefix[b] = before;
-        __syncthreads();
-        if (threadIdx.x == 1023) carry = before + tiles;
-        __syncthreads();
+    for (int i = 0; i < kPer; ++i) {
+        const int b = threadIdx.x * kPer + i;
+        tiles[i] = b < p.batch ? (clamp_len(p, b) + kTile - 1) / kTile : 0;
+        mine += tiles[i];
     }
-    if (threadIdx.x == 0) p.prefix[p.batch] = carry;
+    int x = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, off);
+        if (lane >= off) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    int before = x - mine;
+    for (int w = 0; w < warp; ++w) before += warp_sums[w];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+        const int b = threadIdx.x * kPer + i;
+        if (b <= p.batch) prefix[b] = before;
+        before += tiles[i];
+    }
+    if (threadIdx.x == kThreads - 1 && p.batch == kMaxBatch) prefix[kMaxBatch] = before;
+    __syncthreads();
 }
 
 // Position inside the end-to-end sequence of (batch, kv head) pairs.
@@ -96,29 +99,29 @@ struct Cursor {
     int b, hk, tile, ntiles, len;
 };
 
-__device__ __forceinline__ void cursor_seek(const DecodeParams& p, Cursor& c, int unit) {
+__device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* prefix, Cursor& c, int unit) {
     // Largest b with kv_heads * prefix[b] <= unit.
     int lo = 0, hi = p.batch - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
-        if (p.kv_heads * p.prefix[mid] <= unit) lo = mid; else hi = mid - 1;
+        if (p.kv_heads * prefix[mid] <= unit) lo = mid; else hi = mid - 1;
     }
     c.b = lo;
+    c.ntiles = prefix[lo + 1] - prefix[lo];
     c.len = clamp_len(p, lo);
-    c.ntiles = (c.len + kTile - 1) / kTile;
-    const int rem = unit - p.kv_heads * p.prefix[lo];
+    const int rem = unit - p.kv_heads * prefix[lo];
     c.hk = rem / c.ntiles;
     c.tile = rem % c.ntiles;
 }
 
-__device__ __forceinline__ void cursor_next(const DecodeParams& p, Cursor& c) {
+__device__ __forceinline__ void cursor_next(const DecodeParams& p, const int* prefix, Cursor& c) {
     if (++c.tile < c.ntiles) return;
     c.tile = 0;
     if (++c.hk < p.kv_heads) return;
     c.hk = 0;
     if (++c.b < p.batch) {
         c.len = clamp_len(p, c.b);
-        c.ntiles = (c.len + kTile - 1) / kTile;
+        c.ntiles = prefix[c.b + 1] - prefix[c.b];
     }
 }
 
@@ -130,28 +133,101 @@ __device__ __forceinline__ int swz(int row, int col) {
 }
 
 template <int D, int NS>
-__global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const DecodeParams p) {
     constexpr int kStage = 2 * kTile * D * 2;  // K then V, bytes
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
     float* acc = reinterpret_cast<float*>(smem + NS * kStage);  // [16][D]
     float* sm_m = acc + 16 * D;                                 // [4][16]
     float* sm_l = sm_m + 64;                                    // [4][16]
+    float* fin_m = sm_l + 64;                                   // [16] merged maxima of a segment
+    float* fin_l = fin_m + 16;                                  // [16] merged sums
+    int* prefix_s = reinterpret_cast<int*>(fin_l + 16);         // [kMaxBatch + 1]
+    int* misc = prefix_s + kMaxBatch + 1;                       // [8] warp sums, then the pending list
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = p.heads / p.kv_heads;
     const int rows = group * p.sq;  // valid rows of the 16-row MMA tile
 
-    const int total = p.kv_heads * p.prefix[p.batch];
+    scan_lengths(p, prefix_s, misc);
+    const int total = p.kv_heads * prefix_s[p.batch];
     const int upc = (total + gridDim.x - 1) / gridDim.x;
     const int u0 = blockIdx.x * upc;
     const int u1 = min(u0 + upc, total);
     if (u0 >= u1) return;
 
     Cursor prod, cons;
-    cursor_seek(p, cons, u0);
+    cursor_seek(p, prefix_s, cons, u0);
     prod = cons;
+
+    // One normalised output row chunk (4 columns) of (batch b, kv head hk, tile row r).
+    auto write_row = [&](int b, int hk, int r, int c4, float4 sum, float mm, float ll) {
+        const float inv = ll > 0.f ? 1.f / ll : 0.f;
+        const int gi = r / p.sq, tq = r % p.sq;
+        const int h = hk * group + gi;
+        __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + tq * p.os[2] + c4 * 4;
+        uint2 packed;
+        packed.x = pack_bf16(sum.x * inv, sum.y * inv);
+        packed.y = pack_bf16(sum.z * inv, sum.w * inv);
+        *reinterpret_cast<uint2*>(og) = packed;
+        if (p.lse && c4 == 0) {
+            p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.sq + tq] =
+                ll > 0.f ? kLn2 * (mm + log2f(ll)) : -INFINITY;
+        }
+    };
+
+    // Pairs whose partial this CTA has stored and whose ticket it still has to draw.
+    int* pend = misc + 8;            // [kMaxPending][5]: pair, first CTA, last CTA, batch, kv head
+    int* npend_s = pend + 5 * kMaxPending;
+    int* last_s = npend_s + 1;       // [kMaxPending] 1 where this CTA drew the last ticket
+    if (threadIdx.x == 0) npend_s[0] = 0;
+    __syncthreads();
+
+    // Draws a ticket per pending pair; where this CTA is the last holder it merges the pair's
+    // partials (read through L2, fixed order of CTAs: deterministic), writes the rows and
+    // puts the counter back to zero for the next call. Called by the whole CTA.
+    auto draw_tickets = [&]() {
+        __syncthreads();  // every thread's partial stores are ordered before the fence below
+        const int n = npend_s[0];
+        if (threadIdx.x == 0) {
+            __threadfence();
+            for (int i = 0; i < n; ++i) {
+                const int* e = pend + 5 * i;
+                const int parts = e[2] - e[1] + 1;
+                const int ticket = atomicAdd(&p.counters[e[0]], 1);
+                last_s[i] = ticket == parts - 1;
+                if (ticket == parts - 1) p.counters[e[0]] = 0;  // all holders have drawn
+            }
+            __threadfence();
+        }
+        __syncthreads();
+        for (int i = 0; i < n; ++i) {
+            if (!last_s[i]) continue;
+            const int* e = pend + 5 * i;
+            const int pair = e[0], c_first = e[1], c_last = e[2];
+            for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
+                const int r = idx / (D / 4), c4 = idx % (D / 4);
+                float mm = -INFINITY;
+                for (int c = c_first; c <= c_last; ++c) mm = fmaxf(mm, __ldcg(&p.part_m[(c + pair) * 16 + r]));
+                const float base = (mm == -INFINITY) ? 0.f : mm;
+                float ll = 0.f;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int c = c_first; c <= c_last; ++c) {
+                    const int slot = c + pair;
+                    const float w = fast_exp2(__ldcg(&p.part_m[slot * 16 + r]) - base);
+                    ll += __ldcg(&p.part_l[slot * 16 + r]) * w;
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                        p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
+                    sum.x += v.x * w; sum.y += v.y * w; sum.z += v.z * w; sum.w += v.w * w;
+                }
+                write_row(e[3], e[4], r, c4, sum, mm, ll);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) npend_s[0] = 0;
+        __syncthreads();
+    };
 
     // One warp copies its own 16 key rows of K and V for a tile into stage `st`.
     auto issue = [&](const Cursor& c, int st) {
@@ -178,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
     for (int s = 0; s < NS - 1; ++s) {
         if (up < u1) {
             issue(prod, s);
-            cursor_next(p, prod);
+            cursor_next(p, prefix_s, prod);
             ++up;
         }
         cp_async_commit();
@@ -194,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
         // Refill the stage consumed in the previous iteration.
         if (up < u1) {
             issue(prod, (up - u0) % NS);
-            cursor_next(p, prod);
+            cursor_next(p, prefix_s, prod);
             ++up;
         }
         cp_async_commit();
@@ -296,8 +372,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
 
         const bool last_of_pair = cons.tile + 1 == cons.ntiles;
         if (last_of_pair || u + 1 == u1) {
-            // Merge the four warps' states in a fixed order (deterministic) and store the
-            // pair segment's partial.
+            // Merge the four warps' states in a fixed order (deterministic).
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
@@ -310,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
                 sm_l[warp * 16 + g + 8] = l_run[1];
             }
             __syncthreads();
-            float f[2], m_all[2], l_all[2];
+            float f[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const int row = g + r * 8;
@@ -321,8 +396,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
                 float ll = 0.f;
 #pragma unroll
                 for (int w = 0; w < 4; ++w) ll += sm_l[w * 16 + row] * fast_exp2(sm_m[w * 16 + row] - base);
-                m_all[r] = mm;
-                l_all[r] = ll;
+                if (warp == 0 && t == 0) {
+                    fin_m[row] = mm;
+                    fin_l[row] = ll;
+                }
                 f[r] = fast_exp2(m_run[r] - base);
             }
 #pragma unroll
@@ -345,67 +422,50 @@ __global__ void __launch_bounds__(kThreads, 2) decode_stream_kernel(const Decode
                 }
                 __syncthreads();
             }
+
+            // Which CTAs hold a piece of this pair?
             const int pair = cons.b * p.kv_heads + cons.hk;
-            const int slot = blockIdx.x + pair;
-            float4* dst = reinterpret_cast<float4*>(p.part_o + static_cast<int64_t>(slot) * 16 * D);
-            const float4* src = reinterpret_cast<const float4*>(acc);
-            for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = src[idx];
-            if (warp == 0 && t == 0) {
-                p.part_m[slot * 16 + g] = m_all[0];
-                p.part_m[slot * 16 + g + 8] = m_all[1];
-                p.part_l[slot * 16 + g] = l_all[0];
-                p.part_l[slot * 16 + g + 8] = l_all[1];
+            const int t0 = p.kv_heads * prefix_s[cons.b] + cons.hk * cons.ntiles;
+            const int c_first = t0 / upc, c_last = (t0 + cons.ntiles - 1) / upc;
+            if (c_first == c_last) {
+                // The whole pair lies in this CTA: normalise and write it now.
+                for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
+                    const int r = idx / (D / 4), c4 = idx % (D / 4);
+                    const float4 sum = *reinterpret_cast<const float4*>(&acc[r * D + c4 * 4]);
+                    write_row(cons.b, cons.hk, r, c4, sum, fin_m[r], fin_l[r]);
+                }
+            } else {
+                // Store the partial; the ticket is drawn at the end of the CTA so that the
+                // stream is not held up by a device-wide fence in the middle.
+                const int slot = blockIdx.x + pair;
+                float4* dst = reinterpret_cast<float4*>(p.part_o + static_cast<int64_t>(slot) * 16 * D);
+                const float4* src = reinterpret_cast<const float4*>(acc);
+                for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = src[idx];
+                if (threadIdx.x < 16) {
+                    p.part_m[slot * 16 + threadIdx.x] = fin_m[threadIdx.x];
+                    p.part_l[slot * 16 + threadIdx.x] = fin_l[threadIdx.x];
+                }
+                if (threadIdx.x == 0) {
+                    int* e = pend + 5 * npend_s[0];
+                    e[0] = pair; e[1] = c_first; e[2] = c_last; e[3] = cons.b; e[4] = cons.hk;
+                    npend_s[0] += 1;
+                }
+                __syncthreads();
+                if (npend_s[0] == kMaxPending) draw_tickets();
             }
             __syncthreads();
             fresh = true;
         }
-        cursor_next(p, cons);
+        cursor_next(p, prefix_s, cons);
     }
     cp_async_wait<0>();
+    __syncthreads();
+    if (npend_s[0] > 0) draw_tickets();
 }
 
-// One CTA per (batch, kv head) pair: merge its partials and write bf16 rows.
-template <int D>
-__global__ void __launch_bounds__(kThreads) decode_combine_kernel(const DecodeParams p, int stream_ctas) {
-    const int pair = blockIdx.x;
-    const int b = pair / p.kv_heads, hk = pair % p.kv_heads;
-    const int group = p.heads / p.kv_heads;
-    const int rows = group * p.sq;
-    const int len = clamp_len(p, b);
-    const int ntiles = (len + kTile - 1) / kTile;
-    const int total = p.kv_heads * p.prefix[p.batch];
-    const int upc = (total + stream_ctas - 1) / stream_ctas;
-    const int t0 = p.kv_heads * p.prefix[b] + hk * ntiles;
-    const int c_first = t0 / upc, c_last = (t0 + ntiles - 1) / upc;
-
-    for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
-        const int r = idx / (D / 4), c4 = idx % (D / 4);
-        float mm = -INFINITY;
-        for (int c = c_first; c <= c_last; ++c) mm = fmaxf(mm, p.part_m[(c + pair) * 16 + r]);
-        const float base = (mm == -INFINITY) ? 0.f : mm;
-        float ll = 0.f;
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = c_first; c <= c_last; ++c) {
-            const int slot = c + pair;
-            const float f = fast_exp2(p.part_m[slot * 16 + r] - base);
-            ll += p.part_l[slot * 16 + r] * f;
-            const float4 v = *reinterpret_cast<const float4*>(
-                p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4);
-            sum.x += v.x * f; sum.y += v.y * f; sum.z += v.z * f; sum.w += v.w * f;
-        }
-        const float inv = ll > 0.f ? 1.f / ll : 0.f;
-        const int gi = r / p.sq, tq = r % p.sq;
-        const int h = hk * group + gi;
-        __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + tq * p.os[2] + c4 * 4;
-        uint2 packed;
-        packed.x = pack_bf16(sum.x * inv, sum.y * inv);
-        packed.y = pack_bf16(sum.z * inv, sum.w * inv);
-        *reinterpret_cast<uint2*>(og) = packed;
-        if (p.lse && c4 == 0) {
-            p.lse[(static_cast<int64_t>(b) * p.heads + h) * p.sq + tq] =
-                ll > 0.f ? kLn2 * (mm + log2f(ll)) : -INFINITY;
-        }
-    }
+int ctas_per_sm() {
+    static const int v = [] { const char* e = getenv("KTT_B200_DECODE_CTAS_PER_SM"); return e ? atoi(e) : 2; }();
+    return v;
 }
 
 int stream_ctas_for_device() {
@@ -413,24 +473,20 @@ int stream_ctas_for_device() {
     if (cudaGetDevice(&dev) == cudaSuccess) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    return 2 * sms;
+    return ctas_per_sm() * sms;
 }
 
 template <int D, int NS>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
-    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + 2 * 64 * 4;
-    if (int rc = ensure_smem(decode_stream_kernel<D, NS>, smem, "cudaFuncSetAttribute(decode_stream)")) return rc;
-    decode_plan_kernel<<<1, 1024, 0, stream>>>(p);
-    if (int rc = check_cuda(cudaGetLastError(), "decode_plan launch")) return rc;
-    decode_stream_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);
-    if (int rc = check_cuda(cudaGetLastError(), "decode_stream launch")) return rc;
-    decode_combine_kernel<D><<<p.batch * p.kv_heads, kThreads, 0, stream>>>(p, ctas);
-    return check_cuda(cudaGetLastError(), "decode_combine launch");
+    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
+    if (int rc = ensure_smem(decode_kernel<D, NS>, smem, "cudaFuncSetAttribute(decode)")) return rc;
+    decode_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "decode launch");
 }
 
-// Scratch layout: prefix (int32, padded to 256 B), then m, l, O partials.
+// Scratch layout: ticket counters (int32, padded to 256 B), then m, l, O partials.
 struct ScratchLayout {
-    int64_t prefix_bytes, m_bytes, l_bytes, o_bytes, total;
+    int64_t counter_bytes, m_bytes, l_bytes, o_bytes, total;
     int slots;
 };
 
@@ -438,11 +494,11 @@ ScratchLayout scratch_layout(int batch, int kv_heads, int d, int ctas) {
     ScratchLayout s;
     s.slots = ctas + batch * kv_heads;
     auto up = [](int64_t x) { return (x + 255) / 256 * 256; };
-    s.prefix_bytes = up(static_cast<int64_t>(batch + 1) * 4);
+    s.counter_bytes = up(static_cast<int64_t>(batch) * kv_heads * 4);
     s.m_bytes = up(static_cast<int64_t>(s.slots) * 16 * 4);
     s.l_bytes = s.m_bytes;
     s.o_bytes = up(static_cast<int64_t>(s.slots) * 16 * d * 4);
-    s.total = s.prefix_bytes + s.m_bytes + s.l_bytes + s.o_bytes;
+    s.total = s.counter_bytes + s.m_bytes + s.l_bytes + s.o_bytes;
     return s;
 }
 
@@ -459,6 +515,7 @@ int decode_ctas(const ktt_b200_decode_args* a) {
 const char* decode_refusal(const ktt_b200_decode_args* a) {
     if (!a) return "null arguments";
     if (a->batch < 1 || a->heads < 1 || a->kv_heads < 1 || a->sq < 1 || a->sk < 1) return "sizes must be positive";
+    if (a->batch > kMaxBatch) return "decode takes at most 1024 sequences per call";
     if (a->heads % a->kv_heads) return "K / V heads must divide Q heads";
     if (a->d != a->dv || (a->d != 64 && a->d != 128)) return "decode takes head dim 64 or 128 (D == Dv)";
     if ((a->heads / a->kv_heads) * a->sq > 16) return "decode takes at most 16 query rows per K / V head";
@@ -467,6 +524,41 @@ const char* decode_refusal(const ktt_b200_decode_args* a) {
         if (a->q_strides[i] % 2 || a->out_strides[i] % 4) return "q strides must be even and out strides multiples of 4";
     }
     return nullptr;
+}
+
+// Checks, parameter block and launch shared by both entry points; `base` is the scratch.
+int run_decode(const ktt_b200_decode_args* a, unsigned char* base, const ScratchLayout& lay, int ctas,
+               void* stream, const char* what) {
+    if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(base)) & 15) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "%s: k, v and scratch must be 16-byte aligned", what);
+    }
+    if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (reinterpret_cast<uintptr_t>(a->out) & 7)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "%s: q must be 4-byte and out 8-byte aligned", what);
+    }
+    DecodeParams p;
+    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
+    p.sq = a->sq; p.sk = a->sk; p.d = a->d;
+    p.scale_log2 = a->scale * kLog2e;
+    p.q = static_cast<const __nv_bfloat16*>(a->q);
+    p.k = static_cast<const __nv_bfloat16*>(a->k);
+    p.v = static_cast<const __nv_bfloat16*>(a->v);
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.lse = a->lse;
+    for (int i = 0; i < 3; ++i) {
+        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i];
+        p.vs[i] = a->v_strides[i]; p.os[i] = a->out_strides[i];
+    }
+    p.key_lengths = a->key_lengths;
+    p.counters = reinterpret_cast<int32_t*>(base);
+    p.part_m = reinterpret_cast<float*>(base + lay.counter_bytes);
+    p.part_l = reinterpret_cast<float*>(base + lay.counter_bytes + lay.m_bytes);
+    p.part_o = reinterpret_cast<float*>(base + lay.counter_bytes + lay.m_bytes + lay.l_bytes);
+    p.slots = lay.slots;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    note_call(3);
+    if (a->d == 64) return launch<64, 6>(p, ctas, st);
+    if (ctas_per_sm() == 3) return launch<128, 2>(p, ctas, st);
+    return launch<128, 3>(p, ctas, st);
 }
 
 }  // namespace
@@ -488,42 +580,13 @@ extern "C" int ktt_b200_decode(const ktt_b200_decode_args* a, void* stream) {
     if (!a->q || !a->k || !a->v || !a->out || !a->scratch) {
         return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode: null tensor or scratch pointer");
     }
-    const uintptr_t align = reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) |
-        reinterpret_cast<uintptr_t>(a->scratch);
-    if (align & 15) return fail(KTT_B200_ERR_UNSUPPORTED, "decode: k, v and scratch must be 16-byte aligned");
-    if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (reinterpret_cast<uintptr_t>(a->out) & 7)) {
-        return fail(KTT_B200_ERR_UNSUPPORTED, "decode: q must be 4-byte and out 8-byte aligned");
-    }
     const int ctas = decode_ctas(a);
     const ScratchLayout lay = scratch_layout(a->batch, a->kv_heads, a->d, ctas);
     if (a->scratch_bytes < lay.total) {
         return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode: scratch holds %lld bytes, %lld needed",
                     static_cast<long long>(a->scratch_bytes), static_cast<long long>(lay.total));
     }
-    DecodeParams p;
-    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
-    p.sq = a->sq; p.sk = a->sk; p.d = a->d;
-    p.scale_log2 = a->scale * kLog2e;
-    p.q = static_cast<const __nv_bfloat16*>(a->q);
-    p.k = static_cast<const __nv_bfloat16*>(a->k);
-    p.v = static_cast<const __nv_bfloat16*>(a->v);
-    p.out = static_cast<__nv_bfloat16*>(a->out);
-    p.lse = a->lse;
-    for (int i = 0; i < 3; ++i) {
-        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i];
-        p.vs[i] = a->v_strides[i]; p.os[i] = a->out_strides[i];
-    }
-    p.key_lengths = a->key_lengths;
-    unsigned char* base = static_cast<unsigned char*>(a->scratch);
-    p.prefix = reinterpret_cast<int32_t*>(base);
-    p.part_m = reinterpret_cast<float*>(base + lay.prefix_bytes);
-    p.part_l = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes);
-    p.part_o = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes + lay.l_bytes);
-    p.slots = lay.slots;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    note_call(3);
-    if (a->d == 64) return launch<64, 6>(p, ctas, st);
-    return launch<128, 3>(p, ctas, st);
+    return run_decode(a, static_cast<unsigned char*>(a->scratch), lay, ctas, stream, "decode");
 }
 
 // ---- decode without any allocation ---------------------------------------------------------
@@ -579,19 +642,14 @@ int static_scratch_address(unsigned char** out) {
 //  - The first call on each device looks up the array's device address and raises the
 //    kernel's shared-memory limit. Make that first call outside of any stream capture.
 //  - All calls on a device share the one array. Nothing in it has to be cleared between
-//    calls (every word a call reads, it has written first), but two calls whose kernels
+//    calls (the array starts zeroed with the module, the ticket counters are put back to
+//    zero by the kernel, every other word is written before it is read), but two calls whose kernels
 //    overlap on the GPU, for example on different streams, overwrite each other's
 //    partials. Keep calls to this entry point on one stream, or order them with events.
 extern "C" int ktt_b200_decode_static(const ktt_b200_decode_args* a, void* stream) {
     if (const char* why = decode_refusal(a)) return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: %s", why);
     if (!a->q || !a->k || !a->v || !a->out) {
         return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_static: null tensor pointer");
-    }
-    if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v)) & 15) {
-        return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: k and v must be 16-byte aligned");
-    }
-    if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (reinterpret_cast<uintptr_t>(a->out) & 7)) {
-        return fail(KTT_B200_ERR_UNSUPPORTED, "decode_static: q must be 4-byte and out 8-byte aligned");
     }
     const int ctas = decode_ctas(a);
     const ScratchLayout lay = scratch_layout(a->batch, a->kv_heads, a->d, ctas);
@@ -603,27 +661,5 @@ extern "C" int ktt_b200_decode_static(const ktt_b200_decode_args* a, void* strea
     }
     unsigned char* base = nullptr;
     if (int rc = static_scratch_address(&base)) return rc;
-    DecodeParams p;
-    p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
-    p.sq = a->sq; p.sk = a->sk; p.d = a->d;
-    p.scale_log2 = a->scale * kLog2e;
-    p.q = static_cast<const __nv_bfloat16*>(a->q);
-    p.k = static_cast<const __nv_bfloat16*>(a->k);
-    p.v = static_cast<const __nv_bfloat16*>(a->v);
-    p.out = static_cast<__nv_bfloat16*>(a->out);
-    p.lse = a->lse;
-    for (int i = 0; i < 3; ++i) {
-        p.qs[i] = a->q_strides[i]; p.ks[i] = a->k_strides[i];
-        p.vs[i] = a->v_strides[i]; p.os[i] = a->out_strides[i];
-    }
-    p.key_lengths = a->key_lengths;
-    p.prefix = reinterpret_cast<int32_t*>(base);
-    p.part_m = reinterpret_cast<float*>(base + lay.prefix_bytes);
-    p.part_l = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes);
-    p.part_o = reinterpret_cast<float*>(base + lay.prefix_bytes + lay.m_bytes + lay.l_bytes);
-    p.slots = lay.slots;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    note_call(3);
-    if (a->d == 64) return launch<64, 6>(p, ctas, st);
-    return launch<128, 3>(p, ctas, st);
+    return run_decode(a, base, lay, ctas, stream, "decode_static");
 }

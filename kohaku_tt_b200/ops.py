@@ -325,7 +325,7 @@ def decode_takes(q, k, v):
         return False
     b, h, sq, d = q.shape
     hk = k.shape[1]
-    if hk == 0 or h % hk or v.shape[3] != d or d not in (64, 128) or (h // hk) * sq > 16:
+    if hk == 0 or h % hk or v.shape[3] != d or d not in (64, 128) or (h // hk) * sq > 16 or b > 1024:
         return False
     if any(t.stride(-1) != 1 for t in (q, k, v)):
         return False
@@ -342,10 +342,13 @@ def decode_scratch(args, device):
     need = _lib.lib().ktt_b200_decode_scratch_bytes(ctypes.byref(args))
     if need <= 0:
         _lib.check(_lib.ERR_UNSUPPORTED, "decode")
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    # One buffer per device: concurrent decode calls on several streams of one device must
+    # pass their own `scratch` (calls sharing a buffer must not overlap on the GPU).
+    key = device.index
     buf = _DECODE_SCRATCH.get(key)
     if buf is None or buf.numel() < need:
-        buf = torch.empty((need,), dtype=torch.uint8, device=device)
+        # Zero-filled: the kernel's ticket counters must start at zero (it leaves them so).
+        buf = torch.zeros((need,), dtype=torch.uint8, device=device)
         _DECODE_SCRATCH[key] = buf
     return buf, need
 
@@ -353,6 +356,7 @@ def decode_scratch(args, device):
 def decode(q, k, v, key_lengths=None, scale=None, need_lse=False, splits=0, scratch=None):
     """Decode attention of q [B, H, Sq, D] (H / Hk * Sq <= 16) against a static cache
     k / v [B, Hk, Smax, D]; key_lengths int32 [B] on the device (clamped to [1, Smax]).
+    `scratch`, when given, must have been zero-filled once before its first use.
     Returns (out [B, H, Sq, D] bf16, lse or None). The decode route of
     ktt::_sdpa_lengths (aten_lengths.cpp:69-99, aten_attention.cpp:578-604)."""
     _require_cuda(q, k, v, key_lengths)
