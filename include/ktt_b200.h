@@ -149,7 +149,7 @@ KTT_B200_API const char* ktt_b200_last_error(void);
 
 /* ktt_counters (ktt_capi.h:24-26) reduced to this path: out[8] = forward calls on the
  * tcgen05 kernel, forward calls on the warp-MMA kernel, backward calls, decode calls,
- * refused calls, device-wait timeouts, reserved, reserved. */
+ * refused calls, device-wait timeouts, backward calls on the tcgen05 kernels, reserved. */
 KTT_B200_API int ktt_b200_counters(int64_t* out8);
 KTT_B200_API int ktt_b200_reset_counters(void);
 

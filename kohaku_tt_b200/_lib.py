@@ -236,6 +236,7 @@ COUNTER_NAMES = (
     "attention_decode",
     "attention_refused",
     "device_wait_timeouts",
+    "attention_backward_flash",
 )
 
 

@@ -333,12 +333,14 @@ int launch_dkv(const AttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
+int launch_backward_delta(const AttnParams& p, cudaStream_t stream) {
+    dim3 grid((p.sq + 3) / 4, p.heads, p.batch);
+    bwd_delta_kernel<<<grid, kThreads, 0, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "bwd_delta launch");
+}
+
 int launch_backward_mma(const AttnParams& p, cudaStream_t stream) {
-    {
-        dim3 grid((p.sq + 3) / 4, p.heads, p.batch);
-        bwd_delta_kernel<<<grid, kThreads, 0, stream>>>(p);
-        if (int rc = check_cuda(cudaGetLastError(), "bwd_delta launch")) return rc;
-    }
+    if (int rc = launch_backward_delta(p, stream)) return rc;
     const int dmax = p.d > p.dv ? p.d : p.dv;
     int rc;
     if (dmax <= 32) {

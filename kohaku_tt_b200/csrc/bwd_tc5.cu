@@ -1,0 +1,630 @@
+// Backward on the Blackwell tensor path: a dK/dV kernel and a dQ kernel, both TMA loads +
+// tcgen05.mma with accumulators in tensor memory.
+//
+// Same split and same arithmetic as the reference's backward (ktt_flash/program.cpp:
+// 1587-2006; bw_dq_compute.cpp, bw_dkv_compute.cpp): every gradient has one owner, nothing
+// is accumulated with atomics, so results are deterministic and a packed sequence's
+// gradients do not depend on its neighbours. With delta_i = sum_d dO_id O_id from the
+// preprocess kernel and lse from the forward:
+//
+//   P = 2^(S scale log2e - lse log2e),  dP = dO V^T,  dS = P o (dP - delta)
+//
+//   dK/dV kernel  one CTA = 128 keys of one K/V head; it streams the query blocks of every
+//                 query head of the group. Everything is computed transposed so that the CTA's
+//                 keys are the TMEM lanes:  S^T = K Q^T,  dP^T = V dO^T  (both operands from
+//                 shared memory), then P^T and dS^T are written back over S^T and dP^T as
+//                 packed bf16 and feed  dV += P^T dO,  dK += dS^T Q  as the A operand from
+//                 tensor memory (dO and Q are the MN-major B operands). dV and dK stay in
+//                 TMEM for the whole loop: there is no running maximum to rescale by.
+//   dQ kernel     one CTA = 128 query rows of one head; it streams key blocks:
+//                 S = Q K^T,  dP = dO V^T,  dS over dP in place,  dQ += dS K  (K is read as
+//                 the K-major B operand of the first MMA and as the MN-major B operand of
+//                 the last one, from the same tile).
+//
+// Ten warps per CTA: warps 0-7 are two groups of 128 threads (one thread per TMEM lane, each
+// group owning 64 of the block's 128 score columns), warp 8 issues MMAs, warp 9 issues TMA.
+// Every mbarrier wait is bounded as in the forward kernel.
+#include "tc5.cuh"
+
+namespace ktt {
+using namespace tc5;
+namespace {
+
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+
+struct BwdParams {
+    AttnParams a;
+    int* status;
+    int dim_of[4][3];  // q, k, v, dout: tensor-map coordinate slot of row, head, batch
+};
+
+__device__ __forceinline__ void named_barrier_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Shared-memory plan: a resident pair of tiles (A0, A1), a ring of streamed pairs (B0, B1),
+// two double-buffered vectors of 128 floats, barriers.
+template <int D>
+struct BwdPlan {
+    static constexpr int kSub = D / 64;
+    static constexpr int kTile = 128 * 128;              // one [128][64] bf16 sub-tile
+    static constexpr int kStages = D == 64 ? 4 : 2;
+    static constexpr int kA0 = 0;
+    static constexpr int kA1 = kA0 + kSub * kTile;
+    static constexpr int kB0 = kA1 + kSub * kTile;
+    static constexpr int kB1 = kB0 + kStages * kSub * kTile;
+    static constexpr int kVec = kB1 + kStages * kSub * kTile;  // float [2 buffers][2 vectors][128]
+    static constexpr int kBars = kVec + 2 * 2 * 128 * 4;
+    static constexpr int kBytes = kBars + 256;
+    static constexpr int bAFull = 0;
+    static constexpr int bBFull = 1;                  // + stage
+    static constexpr int bBEmpty = bBFull + kStages;  // + stage
+    static constexpr int bSFull = bBEmpty + kStages;
+    static constexpr int bPFull = bSFull + 1;         // + half
+    static constexpr int bDone = bPFull + 2;
+    static constexpr int bCount = bDone + 1;
+    static_assert(bCount * 8 + 16 <= 256, "barrier area");
+};
+
+template <int D>
+__device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort_flag) {
+    using P = BwdPlan<D>;
+    mbar_init(bars + 8 * P::bAFull, 1);
+    for (int s = 0; s < P::kStages; ++s) {
+        mbar_init(bars + 8 * (P::bBFull + s), 1);
+        mbar_init(bars + 8 * (P::bBEmpty + s), 1);
+    }
+    mbar_init(bars + 8 * P::bSFull, 1);
+    mbar_init(bars + 8 * (P::bPFull + 0), 128);
+    mbar_init(bars + 8 * (P::bPFull + 1), 128);
+    mbar_init(bars + 8 * P::bDone, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+}
+
+// ---- dK / dV ----------------------------------------------------------------------------
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+    const BwdParams tp) {
+    using P = BwdPlan<D>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {
+        if (threadIdx.x == 0) atomicCAS_system(tp.status, 0, 901);
+        return;
+    }
+    const uint32_t bars = sbase + P::kBars;
+    auto bar = [&](int i) { return bars + 8u * i; };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
+    float* vec = reinterpret_cast<float*>(smem + P::kVec);  // [buf][0: lse2, 1: delta][128]
+
+    const AttnParams& p = tp.a;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hk = blockIdx.x, kb = blockIdx.y, b = blockIdx.z;
+    const SeqInfo si = seq_info(p, b);
+    const int k0 = kb * kBM;
+    if (k0 >= si.lk) return;
+    const int group = p.heads / p.kv_heads;
+    const int nq = (si.lq + kBN - 1) / kBN;
+    int qstart = 0;
+    if (p.causal) {
+        const int first = k0 - si.shift;  // first query row that can see key k0
+        qstart = first > 0 ? first / kBN : 0;
+    }
+    const bool any_key = k0 < si.klen;
+    const int per_head = (any_key && nq > qstart) ? nq - qstart : 0;
+    const int nitems = per_head * group;
+
+    if (threadIdx.x == 0) init_barriers<D>(bars, abort_flag);
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 256 + D;
+
+    auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
+        c[tp.dim_of[operand][0]] = row;
+        c[tp.dim_of[operand][1]] = head;
+        c[tp.dim_of[operand][2]] = batch;
+    };
+    const int batch_c = p.cu_q ? 0 : b;
+
+    if (warp == 9) {
+        // ---------------- producer ----------------
+        if (nitems > 0) {
+            int c[4], c2[4];
+            c[0] = c2[0] = 0;
+            coords(1, si.k_off + k0, hk, batch_c, c);
+            coords(2, si.k_off + k0, hk, batch_c, c2);
+            mbar_expect_tx(bar(P::bAFull), 2 * P::kSub * P::kTile);
+            for (int s = 0; s < P::kSub; ++s) {
+                tma_load_4d(sbase + P::kA0 + s * P::kTile, &map_k, bar(P::bAFull), s * 64, c[1], c[2], c[3]);
+                tma_load_4d(sbase + P::kA1 + s * P::kTile, &map_v, bar(P::bAFull), s * 64, c2[1], c2[2], c2[3]);
+            }
+            int issued = 0;
+            for (int it = 0; it < nitems; ++it) {
+                const int st = it % P::kStages;
+                if (it >= P::kStages) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((it / P::kStages) - 1) & 1, abort_flag, 400 + st, tp.status))) break;
+                }
+                const int h = hk * group + it / per_head;
+                const int q0 = (qstart + it % per_head) * kBN;
+                coords(0, si.q_off + q0, h, batch_c, c);
+                coords(3, si.q_off + q0, h, batch_c, c2);
+                mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
+                for (int s = 0; s < P::kSub; ++s) {
+                    tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_q, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
+                    tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_do, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
+                }
+                ++issued;
+            }
+            if (*abort_flag) {
+                for (int it = max(0, issued - P::kStages); it < issued; ++it) {
+                    const int st = it % P::kStages;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar(P::bBFull + st), (it / P::kStages) & 1) && clock64() - t0 < kWaitCycles / 8) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ---------------- MMA issuer ----------------
+        if (nitems > 0) {
+            constexpr uint32_t idesc_s = instr_desc(kBN, false);  // 128 x 128, both K-major
+            constexpr uint32_t idesc_g = instr_desc(D, true);     // 128 x D, B MN-major
+            const uint64_t k_desc = smem_desc(sbase + P::kA0, 16, 1024);
+            const uint64_t v_desc = smem_desc(sbase + P::kA1, 16, 1024);
+            const uint64_t q_desc = smem_desc(sbase + P::kB0, 16, 1024);
+            const uint64_t do_desc = smem_desc(sbase + P::kB1, 16, 1024);
+            const uint64_t q_mn = smem_desc(sbase + P::kB0, P::kTile, 1024);
+            const uint64_t do_mn = smem_desc(sbase + P::kB1, P::kTile, 1024);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bAFull), 0, abort_flag, 500, tp.status));
+            for (int it = 0; ok && it < nitems; ++it) {
+                const int st = it % P::kStages;
+                const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (it / P::kStages) & 1, abort_flag, 510 + st, tp.status));
+                if (!ok) break;
+                tc_fence_after();
+                // S^T = K Q^T and dP^T = V dO^T. The previous item's P^T / dS^T reads were issued
+                // before these and MMAs run in issue order.
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                    tc_mma(tmem_s, k_desc + off, q_desc + soff + off, idesc_s, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                    tc_mma(tmem_dp, v_desc + off, do_desc + soff + off, idesc_s, ks > 0);
+                }
+                tc_commit(bar(P::bSFull));
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), it & 1, abort_flag, 520 + g, tp.status));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        // 16 query rows of this half per step: A = P^T / dS^T (8 TMEM columns),
+                        // B = dO / Q rows as the MN-major operand (16 rows of 128 bytes).
+                        const uint32_t boff = soff + (((g * 4 + ks) * 2048) >> 4);
+                        const uint32_t acc = (it > 0 || g > 0 || ks > 0) ? 1u : 0u;
+                        tc_mma_ts(tmem_dv, tmem_s + g * 64 + ks * 8, do_mn + boff, idesc_g, acc);
+                        tc_mma_ts(tmem_dk, tmem_dp + g * 64 + ks * 8, q_mn + boff, idesc_g, acc);
+                    }
+                }
+                if (!ok) break;
+                tc_commit(bar(P::bBEmpty + st));
+                if (it + 1 == nitems) tc_commit(bar(P::bDone));
+            }
+        }
+    } else {
+        // ---------------- score threads: (key row, half of the query columns) ----------------
+        const int g = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;      // key inside the tile = TMEM lane
+        const int kk = k0 + row;                     // key inside the sequence
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool key_ok = kk < si.klen;
+        bool ok = true;
+
+        // Row terms of one item: group 0 threads fetch lse (as base-2, +inf for rows that do
+        // not exist or saw no key), group 1 threads fetch delta.
+        auto fetch = [&](int it) -> float {
+            const int h = hk * group + it / per_head;
+            const int qi = (qstart + it % per_head) * kBN + row;
+            if (qi >= si.lq) return g == 0 ? INFINITY : 0.f;
+            if (g == 0) {
+                const float l = p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] * kLog2e;
+                return l == -INFINITY ? INFINITY : l;
+            }
+            return p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + qi];
+        };
+        float pre = nitems > 0 ? fetch(0) : 0.f;
+
+        for (int it = 0; it < nitems; ++it) {
+            float* lse2 = vec + (it & 1) * 256;
+            float* delta = lse2 + 128;
+            (g == 0 ? lse2 : delta)[row] = pre;
+            named_barrier_256();
+            if (it + 1 < nitems) pre = fetch(it + 1);
+            const int q0 = (qstart + it % per_head) * kBN;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), it & 1, abort_flag, 600 + g, tp.status));
+            if (!ok) break;
+            tc_fence_after();
+            // Column c of this half is query q0 + g * 64 + c; key kk sees it when
+            // kk <= q + shift, i.e. c >= first_col.
+            const int first_col = p.causal ? kk - si.shift - q0 - g * 64 : -1;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float s[32], dp[32];
+                tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, s);
+                tmem_ld32(tmem_dp + lane_addr + g * 64 + c * 32, dp);
+                tmem_wait_ld();
+                uint32_t wp[16], wd[16];
+                const float4* l4 = reinterpret_cast<const float4*>(lse2 + g * 64 + c * 32);
+                const float4* d4 = reinterpret_cast<const float4*>(delta + g * 64 + c * 32);
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 lv = l4[e4], dv = d4[e4];
+                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w}, ds_[4] = {dv.x, dv.y, dv.z, dv.w};
+                    float pv[4], dsv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int col = c * 32 + e4 * 4 + e;
+                        const bool vis = key_ok && col >= first_col;
+                        const float x = vis ? fmaf(s[e4 * 4 + e], p.scale_log2, -ls[e]) : -INFINITY;
+                        pv[e] = fast_exp2(x);
+                        dsv[e] = pv[e] * (dp[e4 * 4 + e] - ds_[e]);
+                    }
+                    wp[e4 * 2] = pack_bf16(pv[0], pv[1]);
+                    wp[e4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
+                    wd[e4 * 2] = pack_bf16(dsv[0], dsv[1]);
+                    wd[e4 * 2 + 1] = pack_bf16(dsv[2], dsv[3]);
+                }
+                // Packed results go over columns this thread has already consumed.
+                tmem_st16(tmem_s + lane_addr + g * 64 + c * 16, wp);
+                tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(P::bPFull + g));
+        }
+
+        // Epilogue: group 0 writes dV, group 1 writes dK (scaled); rows past the end of the
+        // sequence are not stored. Every lane takes part in the TMEM reads.
+        if (ok && nitems > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 610, tp.status));
+        if (ok) {
+            const bool real = kk < si.lk;
+            const float mul = g == 0 ? 1.f : p.scale;
+            __nv_bfloat16* dst = g == 0
+                ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + static_cast<int64_t>(si.k_off + kk) * p.dvs[2]
+                : p.dk + b * p.dks[0] + hk * p.dks[1] + static_cast<int64_t>(si.k_off + kk) * p.dks[2];
+            if (nitems > 0) tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                if (nitems > 0) {
+                    tmem_ld32((g == 0 ? tmem_dv : tmem_dk) + lane_addr + c * 32, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                }
+                if (real) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = pack_bf16(o[e * 8 + 0] * mul, o[e * 8 + 1] * mul);
+                        v.y = pack_bf16(o[e * 8 + 2] * mul, o[e * 8 + 3] * mul);
+                        v.z = pack_bf16(o[e * 8 + 4] * mul, o[e * 8 + 5] * mul);
+                        v.w = pack_bf16(o[e * 8 + 6] * mul, o[e * 8 + 7] * mul);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ---- dQ ---------------------------------------------------------------------------------
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+    const BwdParams tp) {
+    using P = BwdPlan<D>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {
+        if (threadIdx.x == 0) atomicCAS_system(tp.status, 0, 902);
+        return;
+    }
+    const uint32_t bars = sbase + P::kBars;
+    auto bar = [&](int i) { return bars + 8u * i; };
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
+
+    const AttnParams& p = tp.a;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x, b = blockIdx.z;
+    const int qb = gridDim.y - 1 - blockIdx.y;
+    const SeqInfo si = seq_info(p, b);
+    const int q0 = qb * kBM;
+    if (q0 >= si.lq) return;
+    const int hk = h / (p.heads / p.kv_heads);
+    int kend = si.klen;
+    if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
+    const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
+
+    if (threadIdx.x == 0) init_barriers<D>(bars, abort_flag);
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+
+    auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
+        c[tp.dim_of[operand][0]] = row;
+        c[tp.dim_of[operand][1]] = head;
+        c[tp.dim_of[operand][2]] = batch;
+    };
+    const int batch_c = p.cu_q ? 0 : b;
+
+    if (warp == 9) {
+        if (nblocks > 0) {
+            int c[4], c2[4];
+            c[0] = c2[0] = 0;
+            coords(0, si.q_off + q0, h, batch_c, c);
+            coords(3, si.q_off + q0, h, batch_c, c2);
+            mbar_expect_tx(bar(P::bAFull), 2 * P::kSub * P::kTile);
+            for (int s = 0; s < P::kSub; ++s) {
+                tma_load_4d(sbase + P::kA0 + s * P::kTile, &map_q, bar(P::bAFull), s * 64, c[1], c[2], c[3]);
+                tma_load_4d(sbase + P::kA1 + s * P::kTile, &map_do, bar(P::bAFull), s * 64, c2[1], c2[2], c2[3]);
+            }
+            int issued = 0;
+            for (int j = 0; j < nblocks; ++j) {
+                const int st = j % P::kStages;
+                if (j >= P::kStages) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 700 + st, tp.status))) break;
+                }
+                coords(1, si.k_off + j * kBN, hk, batch_c, c);
+                coords(2, si.k_off + j * kBN, hk, batch_c, c2);
+                mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
+                for (int s = 0; s < P::kSub; ++s) {
+                    tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
+                    tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
+                }
+                ++issued;
+            }
+            if (*abort_flag) {
+                for (int j = max(0, issued - P::kStages); j < issued; ++j) {
+                    const int st = j % P::kStages;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(bar(P::bBFull + st), (j / P::kStages) & 1) && clock64() - t0 < kWaitCycles / 8) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 8) {
+        if (nblocks > 0) {
+            constexpr uint32_t idesc_s = instr_desc(kBN, false);
+            constexpr uint32_t idesc_g = instr_desc(D, true);
+            const uint64_t q_desc = smem_desc(sbase + P::kA0, 16, 1024);
+            const uint64_t do_desc = smem_desc(sbase + P::kA1, 16, 1024);
+            const uint64_t k_desc = smem_desc(sbase + P::kB0, 16, 1024);
+            const uint64_t v_desc = smem_desc(sbase + P::kB1, 16, 1024);
+            const uint64_t k_mn = smem_desc(sbase + P::kB0, P::kTile, 1024);
+            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bAFull), 0, abort_flag, 800, tp.status));
+            for (int j = 0; ok && j < nblocks; ++j) {
+                const int st = j % P::kStages;
+                const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (j / P::kStages) & 1, abort_flag, 810 + st, tp.status));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                    tc_mma(tmem_s, q_desc + off, k_desc + soff + off, idesc_s, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                    tc_mma(tmem_dp, do_desc + off, v_desc + soff + off, idesc_s, ks > 0);
+                }
+                tc_commit(bar(P::bSFull));
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), j & 1, abort_flag, 820 + g, tp.status));
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        tc_mma_ts(tmem_dq, tmem_dp + g * 64 + ks * 8,
+                                  k_mn + soff + (((g * 4 + ks) * 2048) >> 4), idesc_g, (j > 0 || g > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                if (!ok) break;
+                tc_commit(bar(P::bBEmpty + st));
+                if (j + 1 == nblocks) tc_commit(bar(P::bDone));
+            }
+        }
+    } else {
+        // ---------------- score threads: (query row, half of the key columns) ----------------
+        const int g = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        const int qi = q0 + row;
+        const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        bool ok = true;
+        float lse2 = INFINITY, delta = 0.f;
+        if (qi < si.lq) {
+            lse2 = p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] * kLog2e;
+            if (lse2 == -INFINITY) lse2 = INFINITY;  // a row without keys: P exactly 0
+            delta = p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + qi];
+        }
+        int row_limit = si.klen;
+        if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
+
+        for (int j = 0; j < nblocks; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), j & 1, abort_flag, 900 + g, tp.status));
+            if (!ok) break;
+            tc_fence_after();
+            const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float s[32], dp[32];
+                tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, s);
+                tmem_ld32(tmem_dp + lane_addr + g * 64 + c * 32, dp);
+                tmem_wait_ld();
+                uint32_t wd[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float x0 = c * 32 + 2 * e < limit ? fmaf(s[2 * e], p.scale_log2, -lse2) : -INFINITY;
+                    const float x1 = c * 32 + 2 * e + 1 < limit ? fmaf(s[2 * e + 1], p.scale_log2, -lse2) : -INFINITY;
+                    const float d0 = fast_exp2(x0) * (dp[2 * e] - delta);
+                    const float d1 = fast_exp2(x1) * (dp[2 * e + 1] - delta);
+                    wd[e] = pack_bf16(d0, d1);
+                }
+                tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(P::bPFull + g));
+        }
+
+        if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 910, tp.status));
+        if (ok) {
+            // Group g writes dQ columns [g * D / 2, (g + 1) * D / 2), scaled.
+            const bool real = qi < si.lq;
+            __nv_bfloat16* dst = p.dq + b * p.dqs[0] + h * p.dqs[1] + static_cast<int64_t>(si.q_off + qi) * p.dqs[2] + g * (D / 2);
+            if (nblocks > 0) tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                float o[32];
+                if (nblocks > 0) {
+                    tmem_ld32(tmem_dq + lane_addr + g * (D / 2) + c * 32, o);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[e] = 0.f;
+                }
+                if (real) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = pack_bf16(o[e * 8 + 0] * p.scale, o[e * 8 + 1] * p.scale);
+                        v.y = pack_bf16(o[e * 8 + 2] * p.scale, o[e * 8 + 3] * p.scale);
+                        v.z = pack_bf16(o[e * 8 + 4] * p.scale, o[e * 8 + 5] * p.scale);
+                        v.w = pack_bf16(o[e * 8 + 6] * p.scale, o[e * 8 + 7] * p.scale);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000) {
+            }
+        }
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+bool aligned16(const void* ptr, const int64_t strides[3]) {
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
+    for (int i = 0; i < 3; ++i) {
+        if (strides[i] % 8) return false;
+    }
+    return true;
+}
+
+template <int D>
+int launch_bwd(const AttnParams& p, cudaStream_t stream) {
+    using P = BwdPlan<D>;
+    const char* why = "";
+    const int64_t tq = p.cu_q ? p.total_q : p.sq, tk = p.cu_q ? p.total_k : p.sk;
+    const int64_t bq = p.cu_q ? 1 : p.batch;
+    int64_t s[4][3];
+    if (!operand_layout(p.q, tq, p.heads, bq, p.qs, s[0], &why) ||
+        !operand_layout(p.k, tk, p.kv_heads, bq, p.ks, s[1], &why) ||
+        !operand_layout(p.v, tk, p.kv_heads, bq, p.vs, s[2], &why) ||
+        !operand_layout(p.dout, tq, p.heads, bq, p.dos, s[3], &why)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: %s", why);
+    }
+    DimOrder orders[4];
+    for (int i = 0; i < 4; ++i) orders[i] = order_of(s[i]);
+    CUtensorMap mq, mk, mv, mdo;
+    if (!encode_map(&mq, p.q, D, tq, p.heads, bq, s[0], orders[0], kBM, &why) ||
+        !encode_map(&mk, p.k, D, tk, p.kv_heads, bq, s[1], orders[1], kBM, &why) ||
+        !encode_map(&mv, p.v, D, tk, p.kv_heads, bq, s[2], orders[2], kBM, &why) ||
+        !encode_map(&mdo, p.dout, D, tq, p.heads, bq, s[3], orders[3], kBM, &why)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: %s", why);
+    }
+    BwdParams tp;
+    tp.a = p;
+    int* dev_status = nullptr;
+    int* host_status = status_word(&dev_status);
+    if (!host_status || !dev_status) return fail(KTT_B200_ERR_LAUNCH, "tcgen05 backward: no status word");
+    if (*host_status != 0) {
+        const int code = *host_status;
+        *host_status = 0;
+        note_call(5);
+        return fail(KTT_B200_ERR_DEVICE_WAIT, "an earlier tcgen05 launch gave up waiting (code %d)", code);
+    }
+    tp.status = dev_status;
+    for (int o = 0; o < 4; ++o) {
+        for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
+    }
+    constexpr int smem = P::kBytes;
+    if (int rc = ensure_smem(bwd_dkv_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dkv_tc5)")) return rc;
+    if (int rc = ensure_smem(bwd_dq_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dq_tc5)")) return rc;
+    dim3 grid_kv(p.kv_heads, (p.sk + kBM - 1) / kBM, p.batch);
+    bwd_dkv_tc5_kernel<D><<<grid_kv, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
+    if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_tc5 launch")) return rc;
+    dim3 grid_q(p.heads, (p.sq + kBM - 1) / kBM, p.batch);
+    bwd_dq_tc5_kernel<D><<<grid_q, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
+    return check_cuda(cudaGetLastError(), "bwd_dq_tc5 launch");
+}
+
+}  // namespace
+
+bool backward_tc5_takes(const AttnParams& p, const char** why) {
+    if (!forward_tc5_takes(p, why)) return false;
+    if (!aligned16(p.dout, p.dos) || !aligned16(p.dq, p.dqs) || !aligned16(p.dk, p.dks) || !aligned16(p.dv_out, p.dvs)) {
+        *why = "dout, dq, dk and dv must be 16-byte aligned with strides that are multiples of 8";
+        return false;
+    }
+    return true;
+}
+
+int launch_backward_tc5(const AttnParams& p, cudaStream_t stream) {
+    if (int rc = launch_backward_delta(p, stream)) return rc;
+    if (p.d == 64) return launch_bwd<64>(p, stream);
+    return launch_bwd<128>(p, stream);
+}
+
+}  // namespace ktt

@@ -261,6 +261,16 @@ extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream)
     p.delta_bs = bs;
     p.delta_hs = hs;
     note_call(2);
+    const char* why = nullptr;
+    const bool tc5 = backward_tc5_takes(p, &why);
+    if (a->kernel == KTT_B200_KERNEL_TC5 && !tc5) {
+        note_call(4);
+        return fail(KTT_B200_ERR_UNSUPPORTED, "sdpa_backward: tcgen05 kernel: %s", why);
+    }
+    if (tc5 && a->kernel != KTT_B200_KERNEL_MMA) {
+        note_call(6);
+        return launch_backward_tc5(p, static_cast<cudaStream_t>(stream));
+    }
     return launch_backward_mma(p, static_cast<cudaStream_t>(stream));
 }
 

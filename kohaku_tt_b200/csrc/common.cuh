@@ -152,7 +152,7 @@ __device__ __forceinline__ void cp_async_wait() {
 int fail(int code, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 // Counter slots: 0 tcgen05 forward, 1 warp-MMA forward, 2 backward, 3 decode,
-// 4 refused, 5 device-wait timeouts.
+// 4 refused, 5 device-wait timeouts, 6 tcgen05 backward.
 void note_call(int which);
 
 // Raises a kernel's dynamic shared-memory limit once per (kernel, device): the attribute
@@ -178,6 +178,9 @@ int ensure_smem(K kernel, int bytes, const char* what) {
 // Launchers (one per kernel family).
 int launch_forward_mma(const AttnParams& p, cudaStream_t stream);
 int launch_backward_mma(const AttnParams& p, cudaStream_t stream);
+int launch_backward_delta(const AttnParams& p, cudaStream_t stream);  // delta = rowsum(dO o O)
+int launch_backward_tc5(const AttnParams& p, cudaStream_t stream);
+bool backward_tc5_takes(const AttnParams& p, const char** why);
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).

@@ -182,14 +182,14 @@ def sdpa_forward(q, k, v, mask=None, key_lengths=None, causal=False, scale=None,
 
 
 def sdpa_backward(dout, q, k, v, out, lse, mask=None, key_lengths=None, causal=False,
-                  scale=None):
+                  scale=None, kernel="auto"):
     """dq, dk, dv of sdpa_forward from its output and log-sum-exp; dk / dv are summed
     over each GQA group. Stands where bridge::sdpa_train_backward and
     sdpa_lengths_backward stand (device_attention.cpp:909-959,1208-1281)."""
     _require_cuda(dout, q, k, v, out, lse, mask, key_lengths)
     q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
     dout, out = _rows_contiguous(dout), _rows_contiguous(out)
-    args, keep = _dense_args(q, k, v, mask, key_lengths, causal, scale, "mma")
+    args, keep = _dense_args(q, k, v, mask, key_lengths, causal, scale, kernel)
     if lse.dtype != torch.float32 or lse.dim() != 3 or lse.stride(2) != 1:
         raise ValueError("kohaku_tt_b200: lse must be fp32 [B, H, rows] with unit row stride")
     with torch.cuda.device(q.device):
@@ -283,13 +283,13 @@ def varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal=False, scale=None,
 
 
 def varlen_backward(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal=False,
-                    scale=None, key_mask=None):
+                    scale=None, key_mask=None, kernel="auto"):
     """dq, dk, dv of varlen_forward, packed like q, k, v (bridge::sdpa_varlen_backward,
     device_attention.cpp:763-834)."""
     _require_cuda(dout, q, k, v, out, lse, cu_q, cu_k, key_mask)
     q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
     dout, out = _rows_contiguous(dout), _rows_contiguous(out)
-    args, keep = _packed_args(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, key_mask, "mma")
+    args, keep = _packed_args(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, key_mask, kernel)
     if lse.dtype != torch.float32 or tuple(lse.shape) != (q.shape[1], q.shape[0]) or lse.stride(1) != 1:
         raise ValueError("kohaku_tt_b200: packed lse must be fp32 [H, Tq]")
     with torch.cuda.device(q.device):
