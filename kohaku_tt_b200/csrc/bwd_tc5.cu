@@ -104,11 +104,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hk = blockIdx.x, kb = blockIdx.y, b = blockIdx.z;
+    // blockIdx.x = kv head * gsplit + part: this CTA handles query heads [g0, g0 + group) of
+    // the kv head's GQA group.
+    const int hk = blockIdx.x / p.gsplit, part = blockIdx.x % p.gsplit, kb = blockIdx.y, b = blockIdx.z;
     const SeqInfo si = seq_info(p, b);
     const int k0 = kb * kBM;
     if (k0 >= si.lk) return;
-    const int group = p.heads / p.kv_heads;
+    const int full_group = p.heads / p.kv_heads;
+    const int g0 = part * full_group / p.gsplit;
+    const int group = (part + 1) * full_group / p.gsplit - g0;
     const int nq = (si.lq + kBN - 1) / kBN;
     int qstart = 0;
     if (p.causal) {
@@ -152,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
                 if (it >= P::kStages) {
                     if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((it / P::kStages) - 1) & 1, abort_flag, 400 + st, tp.status))) break;
                 }
-                const int h = hk * group + it / per_head;
+                const int h = hk * full_group + g0 + it / per_head;
                 const int q0 = (qstart + it % per_head) * kBN;
                 coords(0, si.q_off + q0, h, batch_c, c);
                 coords(3, si.q_off + q0, h, batch_c, c2);
@@ -235,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
         // Row terms of one item: group 0 threads fetch lse (as base-2, +inf for rows that do
         // not exist or saw no key), group 1 threads fetch delta.
         auto fetch = [&](int it) -> float {
-            const int h = hk * group + it / per_head;
+            const int h = hk * full_group + g0 + it / per_head;
             const int qi = (qstart + it % per_head) * kBN + row;
             if (qi >= si.lq) return g == 0 ? INFINITY : 0.f;
             if (g == 0) {
@@ -296,7 +300,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
         }
 
         // Epilogue: group 0 writes dV, group 1 writes dK (scaled); rows past the end of the
-        // sequence are not stored. Every lane takes part in the TMEM reads.
+        // sequence are not stored. Every lane takes part in the TMEM reads. With the GQA
+        // group split over several CTAs the fp32 sums go to the partial buffer instead.
         if (ok && nitems > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 610, tp.status));
         if (ok) {
             const bool real = kk < si.lk;
@@ -304,6 +309,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
             __nv_bfloat16* dst = g == 0
                 ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + static_cast<int64_t>(si.k_off + kk) * p.dvs[2]
                 : p.dk + b * p.dks[0] + hk * p.dks[1] + static_cast<int64_t>(si.k_off + kk) * p.dks[2];
+            const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
+            const int64_t planes = static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * p.gsplit;
+            float* pdst = p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit + part) * key_rows * D +
+                          static_cast<int64_t>(si.k_off + kk) * D;
             if (nitems > 0) tc_fence_after();
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -315,7 +324,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
 #pragma unroll
                     for (int e = 0; e < 32; ++e) o[e] = 0.f;
                 }
-                if (real) {
+                if (real && p.gsplit > 1) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        *reinterpret_cast<float4*>(pdst + c * 32 + e * 4) =
+                            make_float4(o[e * 4], o[e * 4 + 1], o[e * 4 + 2], o[e * 4 + 3]);
+                    }
+                } else if (real) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         uint4 v;
@@ -554,6 +569,43 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
     }
 }
 
+// Sums the gsplit fp32 partials of every key row in a fixed order and writes bf16 dV and
+// (scaled) dK. One thread per 8 output columns.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_dkv_reduce_kernel(const AttnParams p) {
+    const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
+    const int nb = p.cu_q ? 1 : p.batch;
+    const int64_t planes = static_cast<int64_t>(nb) * p.kv_heads * p.gsplit;
+    const int64_t per_tensor = static_cast<int64_t>(nb) * p.kv_heads * key_rows * (D / 8);
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= 2 * per_tensor) return;
+    const int which = idx >= per_tensor;  // 0: dV, 1: dK
+    int64_t r = idx - which * per_tensor;
+    const int c8 = r % (D / 8);
+    r /= D / 8;
+    const int64_t row = r % key_rows;
+    r /= key_rows;
+    const int hk = r % p.kv_heads;
+    const int b = r / p.kv_heads;
+    const float* src = p.dkv_partial + (which * planes + (static_cast<int64_t>(b) * p.kv_heads + hk) * p.gsplit) * key_rows * D + row * D + c8 * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.gsplit; ++s) {
+        const float4 x = *reinterpret_cast<const float4*>(src + s * key_rows * D);
+        const float4 y = *reinterpret_cast<const float4*>(src + s * key_rows * D + 4);
+        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+    }
+    const float mul = which ? p.scale : 1.f;
+    __nv_bfloat16* dst = which ? p.dk + b * p.dks[0] + hk * p.dks[1] + row * p.dks[2]
+                               : p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + row * p.dvs[2];
+    uint4 v;
+    v.x = pack_bf16(acc[0] * mul, acc[1] * mul);
+    v.y = pack_bf16(acc[2] * mul, acc[3] * mul);
+    v.z = pack_bf16(acc[4] * mul, acc[5] * mul);
+    v.w = pack_bf16(acc[6] * mul, acc[7] * mul);
+    *reinterpret_cast<uint4*>(dst + c8 * 8) = v;
+}
+
 bool aligned16(const void* ptr, const int64_t strides[3]) {
     if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
     for (int i = 0; i < 3; ++i) {
@@ -602,9 +654,15 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
     constexpr int smem = P::kBytes;
     if (int rc = ensure_smem(bwd_dkv_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dkv_tc5)")) return rc;
     if (int rc = ensure_smem(bwd_dq_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dq_tc5)")) return rc;
-    dim3 grid_kv(p.kv_heads, (p.sk + kBM - 1) / kBM, p.batch);
+    dim3 grid_kv(p.kv_heads * p.gsplit, (p.sk + kBM - 1) / kBM, p.batch);
     bwd_dkv_tc5_kernel<D><<<grid_kv, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
     if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_tc5 launch")) return rc;
+    if (p.gsplit > 1) {
+        const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
+        const int64_t threads = 2 * static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * key_rows * (D / 8);
+        bwd_dkv_reduce_kernel<D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p);
+        if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_reduce launch")) return rc;
+    }
     dim3 grid_q(p.heads, (p.sq + kBM - 1) / kBM, p.batch);
     bwd_dq_tc5_kernel<D><<<grid_q, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
     return check_cuda(cudaGetLastError(), "bwd_dq_tc5 launch");
@@ -619,6 +677,23 @@ bool backward_tc5_takes(const AttnParams& p, const char** why) {
         return false;
     }
     return true;
+}
+
+int backward_group_split(const AttnParams& p) {
+    const int group = p.heads / p.kv_heads;
+    if (group <= 1 || p.d != p.dv || (p.d != 64 && p.d != 128)) return 1;
+    // Aim for about 256 CTAs: the dK/dV kernel has one CTA per (batch, kv head, 128 keys).
+    const int64_t ctas = static_cast<int64_t>(p.batch) * p.kv_heads * ((p.sk + kBM - 1) / kBM);
+    const int64_t want = ctas > 0 ? 256 / ctas : 1;
+    if (want <= 1) return 1;
+    return static_cast<int>(want < group ? want : group);
+}
+
+int64_t backward_partial_bytes(const AttnParams& p, int gsplit) {
+    if (gsplit <= 1) return 0;
+    const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
+    const int64_t nb = p.cu_q ? 1 : p.batch;
+    return 2 * nb * p.kv_heads * gsplit * key_rows * p.d * 4;
 }
 
 int launch_backward_tc5(const AttnParams& p, cudaStream_t stream) {

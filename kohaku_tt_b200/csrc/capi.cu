@@ -238,7 +238,9 @@ extern "C" int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* a)
     }
     int64_t bs, hs, total;
     delta_layout(a, bs, hs, total);
-    return (total * 4 + 255) / 256 * 256;
+    AttnParams p;
+    to_params(a, p);
+    return (total * 4 + 255) / 256 * 256 + backward_partial_bytes(p, backward_group_split(p));
 }
 
 extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream) {
@@ -251,15 +253,19 @@ extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream)
     }
     int64_t bs, hs, total;
     delta_layout(a, bs, hs, total);
-    if (!a->workspace || a->workspace_bytes < total * 4) {
-        return fail(KTT_B200_ERR_BAD_ARGUMENT, "sdpa_backward: workspace holds %lld bytes, %lld needed",
-                    static_cast<long long>(a->workspace_bytes), static_cast<long long>(total * 4));
-    }
     AttnParams p;
     to_params(a, p);
+    const int64_t delta_bytes = (total * 4 + 255) / 256 * 256;
+    p.gsplit = backward_group_split(p);
+    const int64_t need = delta_bytes + backward_partial_bytes(p, p.gsplit);
+    if (!a->workspace || a->workspace_bytes < need) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "sdpa_backward: workspace holds %lld bytes, %lld needed",
+                    static_cast<long long>(a->workspace_bytes), static_cast<long long>(need));
+    }
     p.delta = static_cast<float*>(a->workspace);
     p.delta_bs = bs;
     p.delta_hs = hs;
+    p.dkv_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(a->workspace) + delta_bytes);
     note_call(2);
     const char* why = nullptr;
     const bool tc5 = backward_tc5_takes(p, &why);

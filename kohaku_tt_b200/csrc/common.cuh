@@ -41,6 +41,10 @@ struct AttnParams {
     int64_t dos[3], dqs[3], dks[3], dvs[3];
     float* delta;  // [batch, heads, sq_pad] (packed: [heads, total_q_pad])
     int64_t delta_bs, delta_hs;
+    // tcgen05 backward with grouped heads: the query heads of a group are split over
+    // `gsplit` CTAs per key block, which leave fp32 partial dV / dK here for a reduction.
+    int gsplit;
+    float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows][d]
 };
 
 // One sequence's extent inside the operands.
@@ -181,6 +185,10 @@ int launch_backward_mma(const AttnParams& p, cudaStream_t stream);
 int launch_backward_delta(const AttnParams& p, cudaStream_t stream);  // delta = rowsum(dO o O)
 int launch_backward_tc5(const AttnParams& p, cudaStream_t stream);
 bool backward_tc5_takes(const AttnParams& p, const char** why);
+// Number of CTAs the query heads of a GQA group are split over in the tcgen05 dK/dV kernel
+// (1 when there are enough key blocks to fill the GPU), and the fp32 bytes that needs.
+int backward_group_split(const AttnParams& p);
+int64_t backward_partial_bytes(const AttnParams& p, int gsplit);
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).
