@@ -9,7 +9,7 @@
 // per-sequence lengths are:
 //
 //   plan    : every CTA scans ceil(len_b / 64) over the batch into shared memory (the
-//             lengths stay on the device; batch <= 1024)
+//             lengths stay on the device; batch <= 512)
 //   stream  : CTA c owns tile units [c*upc, (c+1)*upc) of the (batch, kv head) pairs laid
 //             end to end. K/V rows arrive by 16-byte cp.async into a swizzled ring of
 //             stages, one private pipeline per warp (16 keys per tile each), scores and
@@ -25,7 +25,6 @@
 //
 // Semantics are kohakutt.sdpa(q, k, v, key_lengths=) (attention.py:10-23): keys at or past
 // a length contribute nothing, whatever they hold; lengths are clamped to [1, Sk].
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -53,7 +52,7 @@ namespace {
 
 constexpr int kTile = 64;      // keys per tile (16 per warp)
 constexpr int kThreads = 128;
-constexpr int kMaxBatch = 1024;  // prefix sums live in shared memory
+constexpr int kMaxBatch = 512;   // clamped lengths and their prefix sums live in shared memory
 constexpr int kMaxPending = 8;   // stored partials per CTA before their tickets are drawn
 
 __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
@@ -64,14 +63,16 @@ __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
 }
 
 // prefix[b] = sum_{b' < b} ceil(len_b' / 64) for b in [0, batch], by one CTA of 128 threads.
-__device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix, int* warp_sums) {
-    constexpr int kPer = kMaxBatch / kThreads;  // 8 consecutive entries per thread
+__device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix, int* lens, int* warp_sums) {
+    constexpr int kPer = kMaxBatch / kThreads;  // consecutive entries per thread
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int tiles[kPer], mine = 0;
 #pragma unroll
     for (int i = 0; i < kPer; ++i) {
         const int b = threadIdx.x * kPer + i;
-        tiles[i] = b < p.batch ? (clamp_len(p, b) + kTile - 1) / kTile : 0;
+        const int len = b < p.batch ? clamp_len(p, b) : 0;
+        if (b < p.batch) lens[b] = len;
+        tiles[i] = (len + kTile - 1) / kTile;
         mine += tiles[i];
     }
     int x = mine;
@@ -99,7 +100,7 @@ struct Cursor {
     int b, hk, tile, ntiles, len;
 };
 
-__device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* prefix, Cursor& c, int unit) {
+__device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* prefix, const int* lens, Cursor& c, int unit) {
     // Largest b with kv_heads * prefix[b] <= unit.
     int lo = 0, hi = p.batch - 1;
     while (lo < hi) {
@@ -108,19 +109,19 @@ __device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* pr
     }
     c.b = lo;
     c.ntiles = prefix[lo + 1] - prefix[lo];
-    c.len = clamp_len(p, lo);
+    c.len = lens[lo];
     const int rem = unit - p.kv_heads * prefix[lo];
     c.hk = rem / c.ntiles;
     c.tile = rem % c.ntiles;
 }
 
-__device__ __forceinline__ void cursor_next(const DecodeParams& p, const int* prefix, Cursor& c) {
+__device__ __forceinline__ void cursor_next(const DecodeParams& p, const int* prefix, const int* lens, Cursor& c) {
     if (++c.tile < c.ntiles) return;
     c.tile = 0;
     if (++c.hk < p.kv_heads) return;
     c.hk = 0;
     if (++c.b < p.batch) {
-        c.len = clamp_len(p, c.b);
+        c.len = lens[c.b];
         c.ntiles = prefix[c.b + 1] - prefix[c.b];
     }
 }
@@ -133,7 +134,7 @@ __device__ __forceinline__ int swz(int row, int col) {
 }
 
 template <int D, int NS>
-__global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
     constexpr int kStage = 2 * kTile * D * 2;  // K then V, bytes
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
@@ -143,14 +144,15 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
     float* fin_m = sm_l + 64;                                   // [16] merged maxima of a segment
     float* fin_l = fin_m + 16;                                  // [16] merged sums
     int* prefix_s = reinterpret_cast<int*>(fin_l + 16);         // [kMaxBatch + 1]
-    int* misc = prefix_s + kMaxBatch + 1;                       // [8] warp sums, then the pending list
+    int* lens_s = prefix_s + kMaxBatch + 1;                     // [kMaxBatch] clamped lengths
+    int* misc = lens_s + kMaxBatch;                       // [8] warp sums, then the pending list
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = p.heads / p.kv_heads;
     const int rows = group * p.sq;  // valid rows of the 16-row MMA tile
 
-    scan_lengths(p, prefix_s, misc);
+    scan_lengths(p, prefix_s, lens_s, misc);
     const int total = p.kv_heads * prefix_s[p.batch];
     const int upc = (total + gridDim.x - 1) / gridDim.x;
     const int u0 = blockIdx.x * upc;
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
     if (u0 >= u1) return;
 
     Cursor prod, cons;
-    cursor_seek(p, prefix_s, cons, u0);
+    cursor_seek(p, prefix_s, lens_s, cons, u0);
     prod = cons;
 
     // One normalised output row chunk (4 columns) of (batch b, kv head hk, tile row r).
@@ -188,41 +190,50 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
     // partials (read through L2, fixed order of CTAs: deterministic), writes the rows and
     // puts the counter back to zero for the next call. Called by the whole CTA.
     auto draw_tickets = [&]() {
-        __syncthreads();  // every thread's partial stores are ordered before the fence below
+        __syncthreads();  // every thread's partial stores happen before thread 0's release
         const int n = npend_s[0];
-        if (threadIdx.x == 0) {
-            __threadfence();
-            for (int i = 0; i < n; ++i) {
-                const int* e = pend + 5 * i;
-                const int parts = e[2] - e[1] + 1;
-                const int ticket = atomicAdd(&p.counters[e[0]], 1);
-                last_s[i] = ticket == parts - 1;
-                if (ticket == parts - 1) p.counters[e[0]] = 0;  // all holders have drawn
-            }
-            __threadfence();
+        if (threadIdx.x < n) {
+            // One thread per pending pair, so the round trips overlap. An acquire-release RMW
+            // at GPU scope publishes this CTA's partials (the barrier above makes the release
+            // cumulative over the CTA) and, for the last holder, makes the other holders'
+            // partials visible.
+            const int* e = pend + 5 * threadIdx.x;
+            const int parts = e[2] - e[1] + 1;
+            int ticket;
+            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + e[0]) : "memory");
+            last_s[threadIdx.x] = ticket == parts - 1;
+            if (ticket == parts - 1) p.counters[e[0]] = 0;  // all holders have drawn
         }
         __syncthreads();
-        for (int i = 0; i < n; ++i) {
+        // All pairs this CTA finishes, flattened so that their loads are in flight together.
+        const int per_pair = rows * (D / 4);
+        for (int idx = threadIdx.x; idx < n * per_pair; idx += kThreads) {
+            const int i = idx / per_pair;
             if (!last_s[i]) continue;
             const int* e = pend + 5 * i;
             const int pair = e[0], c_first = e[1], c_last = e[2];
-            for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
-                const int r = idx / (D / 4), c4 = idx % (D / 4);
-                float mm = -INFINITY;
-                for (int c = c_first; c <= c_last; ++c) mm = fmaxf(mm, __ldcg(&p.part_m[(c + pair) * 16 + r]));
-                const float base = (mm == -INFINITY) ? 0.f : mm;
-                float ll = 0.f;
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int c = c_first; c <= c_last; ++c) {
-                    const int slot = c + pair;
-                    const float w = fast_exp2(__ldcg(&p.part_m[slot * 16 + r]) - base);
-                    ll += __ldcg(&p.part_l[slot * 16 + r]) * w;
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                        p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
-                    sum.x += v.x * w; sum.y += v.y * w; sum.z += v.z * w; sum.w += v.w * w;
-                }
-                write_row(e[3], e[4], r, c4, sum, mm, ll);
+            const int r = (idx % per_pair) / (D / 4), c4 = idx % (D / 4);
+            // Running merge in CTA order (deterministic); the loads do not depend on it.
+            float mm = -INFINITY, ll = 0.f;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int c = c_first; c <= c_last; ++c) {
+                const int slot = c + pair;
+                const float ms = __ldcg(&p.part_m[slot * 16 + r]);
+                const float ls = __ldcg(&p.part_l[slot * 16 + r]);
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                    p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
+                const float m_new = fmaxf(mm, ms);
+                const float base = (m_new == -INFINITY) ? 0.f : m_new;
+                const float fa = fast_exp2(mm - base), fb = fast_exp2(ms - base);
+                ll = ll * fa + ls * fb;
+                sum.x = sum.x * fa + v.x * fb;
+                sum.y = sum.y * fa + v.y * fb;
+                sum.z = sum.z * fa + v.z * fb;
+                sum.w = sum.w * fa + v.w * fb;
+                mm = m_new;
             }
+            write_row(e[3], e[4], r, c4, sum, mm, ll);
         }
         __syncthreads();
         if (threadIdx.x == 0) npend_s[0] = 0;
@@ -254,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
     for (int s = 0; s < NS - 1; ++s) {
         if (up < u1) {
             issue(prod, s);
-            cursor_next(p, prefix_s, prod);
+            cursor_next(p, prefix_s, lens_s, prod);
             ++up;
         }
         cp_async_commit();
@@ -270,12 +281,10 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
         // Refill the stage consumed in the previous iteration.
         if (up < u1) {
             issue(prod, (up - u0) % NS);
-            cursor_next(p, prefix_s, prod);
+            cursor_next(p, prefix_s, lens_s, prod);
             ++up;
         }
         cp_async_commit();
-        cp_async_wait<NS - 1>();
-        __syncwarp();
 
         if (fresh) {
             fresh = false;
@@ -298,6 +307,9 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
             m_run[0] = m_run[1] = -INFINITY;
             l_run[0] = l_run[1] = 0.f;
         }
+        // (The query loads above are in flight while this waits for the tile.)
+        cp_async_wait<NS - 1>();
+        __syncwarp();
 
         const int j0 = cons.tile * kTile + warp * 16;
         if (j0 < cons.len) {
@@ -456,16 +468,11 @@ __global__ void __launch_bounds__(kThreads, NS == 2 ? 3 : 2) decode_kernel(const
             __syncthreads();
             fresh = true;
         }
-        cursor_next(p, prefix_s, cons);
+        cursor_next(p, prefix_s, lens_s, cons);
     }
     cp_async_wait<0>();
     __syncthreads();
     if (npend_s[0] > 0) draw_tickets();
-}
-
-int ctas_per_sm() {
-    static const int v = [] { const char* e = getenv("KTT_B200_DECODE_CTAS_PER_SM"); return e ? atoi(e) : 2; }();
-    return v;
 }
 
 int stream_ctas_for_device() {
@@ -473,12 +480,12 @@ int stream_ctas_for_device() {
     if (cudaGetDevice(&dev) == cudaSuccess) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    return ctas_per_sm() * sms;
+    return 2 * sms;
 }
 
 template <int D, int NS>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
-    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
+    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (2 * kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
     if (int rc = ensure_smem(decode_kernel<D, NS>, smem, "cudaFuncSetAttribute(decode)")) return rc;
     decode_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode launch");
@@ -515,7 +522,7 @@ int decode_ctas(const ktt_b200_decode_args* a) {
 const char* decode_refusal(const ktt_b200_decode_args* a) {
     if (!a) return "null arguments";
     if (a->batch < 1 || a->heads < 1 || a->kv_heads < 1 || a->sq < 1 || a->sk < 1) return "sizes must be positive";
-    if (a->batch > kMaxBatch) return "decode takes at most 1024 sequences per call";
+    if (a->batch > kMaxBatch) return "decode takes at most 512 sequences per call";
     if (a->heads % a->kv_heads) return "K / V heads must divide Q heads";
     if (a->d != a->dv || (a->d != 64 && a->d != 128)) return "decode takes head dim 64 or 128 (D == Dv)";
     if ((a->heads / a->kv_heads) * a->sq > 16) return "decode takes at most 16 query rows per K / V head";
@@ -557,7 +564,6 @@ int run_decode(const ktt_b200_decode_args* a, unsigned char* base, const Scratch
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     note_call(3);
     if (a->d == 64) return launch<64, 6>(p, ctas, st);
-    if (ctas_per_sm() == 3) return launch<128, 2>(p, ctas, st);
     return launch<128, 3>(p, ctas, st);
 }
 

@@ -325,7 +325,7 @@ def decode_takes(q, k, v):
         return False
     b, h, sq, d = q.shape
     hk = k.shape[1]
-    if hk == 0 or h % hk or v.shape[3] != d or d not in (64, 128) or (h // hk) * sq > 16 or b > 1024:
+    if hk == 0 or h % hk or v.shape[3] != d or d not in (64, 128) or (h // hk) * sq > 16 or b > 512:
         return False
     if any(t.stride(-1) != 1 for t in (q, k, v)):
         return False
