@@ -36,12 +36,16 @@ constexpr float kRescaleGap = 8.f;  // in log2 units
 
 // ---- shared-memory plan -----------------------------------------------------------------
 
-// One CTA per SM: 128 query rows, 128-key blocks, ten warps.
-//   warps 0-3  softmax group a: thread r owns row r and the block's keys [0, 64)
-//   warps 4-7  softmax group b: thread r owns row r and the block's keys [64, 128)
+// Persistent kernel: one CTA per SM walks a list of work items (128 query rows of one
+// (batch, head) each), ten warps:
+//   warps 0-3  softmax group a: thread r owns row r and each block's keys [0, 64)
+//   warps 4-7  softmax group b: thread r owns row r and each block's keys [64, 128)
 //   warp 8     MMA issuer, warp 9 TMA producer
 // Each group keeps its own running maximum, sum and output accumulator (O_a, O_b), so the
-// two threads of a row never talk inside the loop; the halves are merged once at the end.
+// two threads of a row never talk inside the loop; the halves are merged once per item.
+// While the softmax groups write an item's output, the producer already loads the next
+// item's Q / K / V and the MMA warp issues its first two Q K^T: barriers, the K/V ring and
+// tensor memory live across items.
 // Tensor memory (512 columns): S / P buffers [0, 128) and [128, 256) (P overwrites the S
 // columns it came from as packed bf16), O_a [256, 256 + D), O_b [256 + D, 256 + 2 D).
 template <int D>
@@ -52,18 +56,20 @@ struct Plan {
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + kSub * kTile;
     static constexpr int kV = kK + kStages * kSub * kTile;
-    static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [2][128]: (m, l) per half
+    static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [2 halves][128]: (m, l)
     static constexpr int kBars = kML + 2 * 128 * 8;
     static constexpr int kBytes = kBars + 256;
     // barrier indices (8 bytes each)
     static constexpr int bQFull = 0;
-    static constexpr int bKVFull = 1;                 // + stage
+    static constexpr int bQFree = 1;
+    static constexpr int bOFree = 2;
+    static constexpr int bKVFull = 3;                 // + stage
     static constexpr int bKVEmpty = bKVFull + kStages;
     static constexpr int bSFull = bKVEmpty + kStages;  // + buffer
     static constexpr int bPFull = bSFull + 2;          // + half
     static constexpr int bPVDone = bPFull + 2;         // + half
     static constexpr int bCount = bPVDone + 2;
-    static_assert(bCount * 8 + 16 <= 256, "barrier area");
+    static_assert(bCount * 8 + 16 + 64 <= 256, "barrier area");
 };
 
 struct Tc5Params {
@@ -71,16 +77,50 @@ struct Tc5Params {
     int* status;        // host-visible: first wait that ran out, or 0
     int dim_of[3][3];   // per operand (q, k, v): tensor-map coordinate slot (1..3) of the
                         // row, head and batch dims
-    long long* trace;   // optional [64][8] clock64 stamps of CTA (0, 0, 0), else null
+    long long* trace;   // optional clock stamps (see ktt_b200_set_trace), else null
+    int q_tiles;        // query tiles per batch entry (ceil(sq / 128))
+    int work;           // work items = heads * batch * q_tiles
 };
 
 // Profiling zones (the counterpart of the reference's FLASH_PROFILE device zones,
-// ktt_flash/compute.cpp:25-30): CTA (0, 0, 0) stamps clock64 per key block.
-//   slots 0-3: softmax row 0 of group a after S ready / S in registers and maximum known /
-//              exponentials done / P published;  slot 4: group b row 0 after P published;
+// ktt_flash/compute.cpp:25-30): CTA 0 stamps clock64 per key block of its first item.
+//   slots 0-3: softmax row 0 of group a after S ready / maximum known / exponentials done /
+//              P published;  slot 4: MMA lane before the next-but-one Q K^T;
 //   slots 5-7: MMA lane after issuing P V of half a / of half b / the next-but-one Q K^T.
 __device__ __forceinline__ void zone(const Tc5Params& tp, bool who, int j, int slot) {
     if (tp.trace && who && j < 64) tp.trace[j * 8 + slot] = clock64();
+}
+
+// One work item: 128 query rows of (batch b, head h).
+struct Work {
+    int b, h, q0, nblocks;
+    SeqInfo si;
+    bool valid;  // false: the tile lies past the end of its sequence
+};
+
+// Items are ordered so that consecutive ones are the heads of one (tile, batch) and the
+// longest causal tiles come first: with items dealt round-robin, every CTA gets a similar
+// mix of long and short tiles, and the heads of a GQA group stream the same K/V together.
+__device__ __forceinline__ Work decode_work(const Tc5Params& tp, int w) {
+    const AttnParams& p = tp.a;
+    Work k;
+    k.h = w % p.heads;
+    const int t = w / p.heads;
+    k.b = t % p.batch;
+    const int qb = tp.q_tiles - 1 - t / p.batch;
+    k.si = seq_info(p, k.b);
+    k.q0 = qb * kBM;
+    k.valid = k.q0 < k.si.lq;
+    int kend = k.si.klen;
+    if (p.causal) kend = min(kend, min(k.q0 + kBM, k.si.lq) - 1 + k.si.shift + 1);
+    k.nblocks = (k.valid && kend > 0) ? (kend + kBN - 1) / kBN : 0;
+    return k;
+}
+
+// Items are dealt to the CTAs in snake order (0 .. G-1, then G-1 .. 0, ...): on a list
+// sorted by decreasing work that pairs each CTA's long items with short ones.
+__device__ __forceinline__ int work_of(int round, int cta, int ctas) {
+    return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
 }
 
 // ---- the kernel ------------------------------------------------------------------------
@@ -99,32 +139,24 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         return;
     }
     // Second profiling zone set: rows 64.. of the trace buffer hold, per CTA, its start and
-    // end on the global nanosecond timer, its SM and its key-block count.
+    // end on the global nanosecond timer, its SM and the key blocks it processed.
     long long cta_t0 = 0;
-    if (tp.trace && threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
+    if (tp.trace && threadIdx.x == 256) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
     const uint32_t bars = sbase + P::kBars;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
+    // Per item and softmax warp: "every wait of mine succeeded" (two items alternate).
+    volatile int* ok_flags = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8 + 16);
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Heads vary fastest and query tiles run from the last (longest under a causal mask) to
-    // the first, so the CTAs the scheduler hands out first are the longest ones of every
-    // head, and the heads of one GQA group stream the same K/V tiles at the same time.
-    const int b = blockIdx.z, h = blockIdx.x;
-    const int qb = gridDim.y - 1 - blockIdx.y;
-    const SeqInfo si = seq_info(p, b);
-    const int q0 = qb * kBM;
-    if (q0 >= si.lq) return;  // whole CTA, before any barrier or allocation
-    const int hk = h / (p.heads / p.kv_heads);
-
-    int kend = si.klen;
-    if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
-    const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
+    const int group_size = p.heads / p.kv_heads;
 
     if (threadIdx.x == 0) {
         mbar_init(bar(P::bQFull), 1);
+        mbar_init(bar(P::bQFree), 1);
+        mbar_init(bar(P::bOFree), 256);
         for (int s = 0; s < P::kStages; ++s) {
             mbar_init(bar(P::bKVFull + s), 1);
             mbar_init(bar(P::bKVEmpty + s), 1);
@@ -153,78 +185,112 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         c[tp.dim_of[operand][2]] = batch;
     };
 
+    // Every role walks the same items and keeps the same two counters: `item` counts the
+    // items with at least one key block, `blk` the key blocks of all items so far. Ring
+    // stages, S buffers and barrier parities are functions of those.
+    int blocks_done = 0;
+
     if (warp == 9) {
         // ---------------- producer (whole warp, converged) ----------------
-        if (nblocks > 0) {
+        int item = 0, blk = 0;
+        bool ok = true;
+        for (int round = 0; ok && round * gridDim.x < tp.work; ++round) {
+            const int w = work_of(round, blockIdx.x, gridDim.x);
+            if (w >= tp.work) continue;
+            const Work k = decode_work(tp, w);
+            if (k.nblocks == 0) continue;
+            const int hk = k.h / group_size;
             int c[4], cv[4];
-            const int batch = p.cu_q ? 0 : b;
+            const int batch = p.cu_q ? 0 : k.b;
             c[0] = cv[0] = 0;
-            coords(0, si.q_off + q0, h, batch, c);
+            // Q may be replaced once the last Q K^T of the previous item has run.
+            if (item > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bQFree), (item - 1) & 1, abort_flag, 110, tp.status));
+                if (!ok) break;
+            }
+            coords(0, k.si.q_off + k.q0, k.h, batch, c);
             mbar_expect_tx(bar(P::bQFull), P::kSub * P::kTile);
             for (int s = 0; s < P::kSub; ++s) {
                 tma_load_4d(sbase + P::kQ + s * P::kTile, &map_q, bar(P::bQFull), s * 64, c[1], c[2], c[3]);
             }
-            int issued = 0;
-            for (int j = 0; j < nblocks; ++j) {
-                const int st = j % P::kStages;
-                if (j >= P::kStages) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bKVEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status))) break;
+            for (int j = 0; j < k.nblocks; ++j) {
+                const int gb = blk + j, st = gb % P::kStages;
+                if (gb >= P::kStages) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVEmpty + st), ((gb / P::kStages) - 1) & 1, abort_flag, 100 + st, tp.status));
+                    if (!ok) break;
                 }
-                coords(1, si.k_off + j * kBN, hk, batch, c);
-                coords(2, si.k_off + j * kBN, hk, batch, cv);
+                coords(1, k.si.k_off + j * kBN, hk, batch, c);
+                coords(2, k.si.k_off + j * kBN, hk, batch, cv);
                 mbar_expect_tx(bar(P::bKVFull + st), 2 * P::kSub * P::kTile);
                 for (int s = 0; s < P::kSub; ++s) {
                     tma_load_4d(sbase + P::kK + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bKVFull + st), s * 64, c[1], c[2], c[3]);
                     tma_load_4d(sbase + P::kV + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bKVFull + st), s * 64, cv[1], cv[2], cv[3]);
                 }
-                ++issued;
             }
-            if (*abort_flag) {
-                // Let copies already in flight land before the CTA's memory goes away.
-                for (int j = max(0, issued - P::kStages); j < issued; ++j) {
-                    const int st = j % P::kStages;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(bar(P::bKVFull + st), (j / P::kStages) & 1) && clock64() - t0 < kWaitCycles / 8) {
-                    }
-                }
+            blk += k.nblocks;
+            ++item;
+        }
+        if (*abort_flag) {
+            // Let copies already in flight land before the CTA's memory goes away.
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000) {
             }
         }
     } else if (warp == 8) {
         // ---------------- MMA issuer (whole warp, converged) ----------------
-        if (nblocks > 0) {
-            constexpr uint32_t idesc_s = instr_desc(kBN, false);
-            constexpr uint32_t idesc_o = instr_desc(D, true);
-            const bool mtracer = lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-            // Descriptors differ only in their 14-bit start-address field (bytes / 16):
-            // build each base once and add constants per MMA.
-            const uint64_t q_desc = smem_desc(sbase + P::kQ, 16, 1024);
-            const uint64_t k_desc = smem_desc(sbase + P::kK, 16, 1024);
-            const uint64_t v_desc = smem_desc(sbase + P::kV, P::kTile, 1024);
-            auto issue_s = [&](int j) {
-                const uint64_t kd = k_desc + static_cast<uint64_t>(((j % P::kStages) * P::kSub * P::kTile) >> 4);
-                const uint32_t d_s = tmem + (j & 1) * 128;
+        constexpr uint32_t idesc_s = instr_desc(kBN, false);
+        constexpr uint32_t idesc_o = instr_desc(D, true);
+        // Descriptors differ only in their 14-bit start-address field (bytes / 16):
+        // build each base once and add constants per MMA.
+        const uint64_t q_desc = smem_desc(sbase + P::kQ, 16, 1024);
+        const uint64_t k_desc = smem_desc(sbase + P::kK, 16, 1024);
+        const uint64_t v_desc = smem_desc(sbase + P::kV, P::kTile, 1024);
+        int item = 0, blk = 0;
+        bool ok = true;
+        bool first_item = true;
+        // Q K^T of global block gb into S buffer gb & 1; `last` marks the item's last one,
+        // after which Q is free.
+        auto issue_s = [&](int gb, bool last) {
+            const uint64_t kd = k_desc + static_cast<uint64_t>(((gb % P::kStages) * P::kSub * P::kTile) >> 4);
+            const uint32_t d_s = tmem + (gb & 1) * 128;
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
-                    tc_mma(d_s, q_desc + off, kd + off, idesc_s, ks > 0);
-                }
-                tc_commit(bar(P::bSFull + (j & 1)));
-            };
-            bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bQFull), 0, abort_flag, 200, tp.status));
-            for (int j = 0; ok && j < 2 && j < nblocks; ++j) {
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + j), 0, abort_flag, 210 + j, tp.status));
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
+                tc_mma(d_s, q_desc + off, kd + off, idesc_s, ks > 0);
+            }
+            tc_commit(bar(P::bSFull + (gb & 1)));
+            if (last) tc_commit(bar(P::bQFree));
+        };
+        for (int round = 0; ok && round * gridDim.x < tp.work; ++round) {
+            const int w = work_of(round, blockIdx.x, gridDim.x);
+            if (w >= tp.work) continue;
+            const Work k = decode_work(tp, w);
+            if (k.nblocks == 0) continue;
+            const bool mtracer = first_item && lane == 0 && blockIdx.x == 0;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bQFull), item & 1, abort_flag, 200, tp.status));
+            // The first two Q K^T of the item run while the previous item's output is
+            // still being written: they only need the S buffers, which are free once the
+            // previous item's P V MMAs have been issued.
+            for (int j = 0; ok && j < 2 && j < k.nblocks; ++j) {
+                const int gb = blk + j;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + gb % P::kStages), (gb / P::kStages) & 1, abort_flag, 210 + j, tp.status));
                 if (ok) {
                     tc_fence_after();
-                    issue_s(j);
+                    issue_s(gb, j + 1 == k.nblocks);
                 }
             }
-            for (int j = 0; ok && j < nblocks; ++j) {
-                const int st = j % P::kStages;
+            for (int j = 0; ok && j < k.nblocks; ++j) {
+                const int gb = blk + j, st = gb % P::kStages;
                 const uint64_t vd = v_desc + static_cast<uint64_t>((st * P::kSub * P::kTile) >> 4);
-                const uint32_t p_tmem = tmem + (j & 1) * 128;
+                const uint32_t p_tmem = tmem + (gb & 1) * 128;
+                if (j == 0 && item > 0) {
+                    // The accumulators are free once the previous item's epilogue has read them.
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bOFree), (item - 1) & 1, abort_flag, 250, tp.status));
+                    if (!ok) break;
+                }
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), j & 1, abort_flag, 240 + g, tp.status));
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), gb & 1, abort_flag, 240 + g, tp.status));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
@@ -240,177 +306,212 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                 }
                 if (!ok) break;
                 tc_commit(bar(P::bKVEmpty + st));
-                if (j + 2 < nblocks) {
+                if (j + 2 < k.nblocks) {
                     // Both groups have published P of block j, so they are done with this S
                     // buffer; MMAs run in issue order, so the P V reads above precede the
                     // overwrite.
-                    const int st2 = (j + 2) % P::kStages;
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + st2), ((j + 2) / P::kStages) & 1, abort_flag, 220 + st2, tp.status));
+                    const int gb2 = gb + 2;
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + gb2 % P::kStages), (gb2 / P::kStages) & 1, abort_flag, 220, tp.status));
                     if (!ok) break;
                     tc_fence_after();
                     zone(tp, mtracer, j, 4);
-                    issue_s(j + 2);
+                    issue_s(gb2, j + 3 == k.nblocks);
                     zone(tp, mtracer, j, 7);
                 }
             }
+            blk += k.nblocks;
+            ++item;
+            first_item = false;
         }
+        blocks_done = blk;
     } else {
-        // ---------------- softmax: thread = (query row, half of the block's keys) ----------------
+        // ---------------- softmax: thread = (query row, half of each block's keys) ----------------
         const int g = warp >> 2;                        // 0: keys [0, 64), 1: keys [64, 128)
         const int row = (warp & 3) * 32 + lane;         // row inside the tile = TMEM lane
-        const int qi = q0 + row;                        // row inside the sequence
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const bool tracer = row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-        float m_ref = -INFINITY;  // this half's reference maximum (base-2 logits), moved lazily
-        float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // running sums, 4 lanes
+        int item = 0, blk = 0;
         bool ok = true;
-        // Keys this row may see: [0, row_limit).
-        int row_limit = si.klen;
-        if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
+        bool first_item = true;
+        float2* ml_base = reinterpret_cast<float2*>(smem + P::kML);
 
-        for (int j = 0; j < nblocks; ++j) {
-            const uint32_t s_addr = tmem + (j & 1) * 128 + g * 64 + lane_addr;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull + (j & 1)), (j >> 1) & 1, abort_flag, 300 + g, tp.status));
-            if (!ok) break;
-            tc_fence_after();
-            zone(tp, tracer && g == 0, j, 0);
-            float s[64];
-            tmem_ld32(s_addr, s);
-            tmem_ld32(s_addr + 32, s + 32);
-            tmem_wait_ld();
-            const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            const bool whole = limit >= 64;
-            if (whole) {
-#pragma unroll
-                for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 64; ++e) {
-                    s[e] = e < limit ? s[e] : -INFINITY;
-                    mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
-                }
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            zone(tp, tracer && g == 0, j, 1);
-
-            // Lazy rescale: move the reference only when this block exceeds it by 2^8.
-            const bool move = mx > m_ref + kRescaleGap;
-            if (__any_sync(0xffffffffu, move)) {
-                float f = 1.f;
-                if (move) {
-                    f = fast_exp2(m_ref - mx);  // 0 on the first block
-                    m_ref = mx;
-                    l2[0] = __fmul2_rn(l2[0], make_float2(f, f));
-                    l2[1] = __fmul2_rn(l2[1], make_float2(f, f));
-                }
-                if (j > 0) {
-                    // O of this half holds blocks [0, j): wait for block j - 1's P V.
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + g), (j - 1) & 1, abort_flag, 310 + g, tp.status));
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        float o[32];
-                        tmem_ld32(tmem_o + g * D + lane_addr + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) o[e] *= f;
-                        tmem_st32(tmem_o + g * D + lane_addr + c * 32, o);
-                    }
-                    tmem_wait_st();
-                }
-            }
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-
-            // P = 2^(s * scale - m) as packed bf16 pairs, two values per instruction where
-            // the packed fp32 pipe allows.
-            uint32_t w[32];
-            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
-            if (whole) {
-                // Every column visible: every other pair of exponentials runs on the FMA pipe
-                // as a polynomial (MUFU is the narrowest pipe of this loop).
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
-                    float2 pr;
-                    if (e & 1) {
-                        pr = exp2_poly2(x);
-                    } else {
-                        pr.x = fast_exp2(x.x);
-                        pr.y = fast_exp2(x.y);
-                    }
-                    l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
-                    w[e] = pack_bf16(pr.x, pr.y);
-                }
-            } else {
-                // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
-                    const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-                    l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
-                    w[e] = pack_bf16(pr.x, pr.y);
-                }
-            }
-            zone(tp, tracer && g == 0, j, 2);
-            // P overwrites the first 32 of the 64 S columns this thread has just read.
-            tmem_st32(s_addr, reinterpret_cast<const float*>(w));
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(P::bPFull + g));
-            zone(tp, tracer && g == 0, j, 3);
-        }
-
-        // Epilogue: merge the two halves of each row and normalise. Every lane takes part in
-        // the TMEM reads and in the 256-thread barrier whatever happened above.
-        if (ok && nblocks > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 0), (nblocks - 1) & 1, abort_flag, 330, tp.status));
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 1), (nblocks - 1) & 1, abort_flag, 331, tp.status));
-        }
-        float2* ml = reinterpret_cast<float2*>(smem + P::kML);
-        const float l_mine = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
-        ml[g * 128 + row] = make_float2(m_ref, l_mine);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ok) {
-            const float2 other = ml[(g ^ 1) * 128 + row];
-            const float m_all = fmaxf(m_ref, other.x);
-            const float base = (m_all == -INFINITY) ? 0.f : m_all;
-            const float f_mine = fast_exp2(m_ref - base), f_other = fast_exp2(other.x - base);
-            const float l_sum = l_mine * f_mine + other.y * f_other;
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            const float fa = (g == 0 ? f_mine : f_other) * inv, fb = (g == 0 ? f_other : f_mine) * inv;
+        for (int round = 0; round * gridDim.x < tp.work; ++round) {
+            const int w = work_of(round, blockIdx.x, gridDim.x);
+            if (w >= tp.work) continue;
+            const Work k = decode_work(tp, w);
+            if (!k.valid) continue;
+            const SeqInfo& si = k.si;
+            const int qi = k.q0 + row;                  // row inside the sequence
             const bool real = qi < si.lq;
-            // Group a writes output columns [0, D / 2), group b the rest.
-            __nv_bfloat16* og = p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2] + g * (D / 2);
-            if (nblocks > 0) tc_fence_after();
+            __nv_bfloat16* og = p.out + k.b * p.os[0] + k.h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2] + g * (D / 2);
+            if (k.nblocks == 0) {
+                // No key is visible to this tile: zeros, lse = -inf. No barrier is involved.
+                if (real) {
 #pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
-                float oa[32], ob[32];
-                if (nblocks > 0) {
+                    for (int c = 0; c < D / 16; ++c) *reinterpret_cast<uint4*>(og + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    if (g == 0 && p.lse) p.lse[k.b * p.ls[0] + k.h * p.ls[1] + (si.q_off + qi) * p.ls[2]] = -INFINITY;
+                }
+                continue;
+            }
+            const bool tracer = first_item && row == 0 && blockIdx.x == 0;
+            float m_ref = -INFINITY;  // this half's reference maximum (base-2 logits), moved lazily
+            float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // running sums, 4 lanes
+            // Keys this row may see: [0, row_limit).
+            int row_limit = si.klen;
+            if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
+
+            for (int j = 0; ok && j < k.nblocks; ++j) {
+                const int gb = blk + j;
+                const uint32_t s_addr = tmem + (gb & 1) * 128 + g * 64 + lane_addr;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull + (gb & 1)), (gb >> 1) & 1, abort_flag, 300 + g, tp.status));
+                if (!ok) break;
+                tc_fence_after();
+                zone(tp, tracer && g == 0, j, 0);
+                float s[64];
+                tmem_ld32(s_addr, s);
+                tmem_ld32(s_addr + 32, s + 32);
+                tmem_wait_ld();
+                const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                const bool whole = limit >= 64;
+                if (whole) {
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) {
+                        s[e] = e < limit ? s[e] : -INFINITY;
+                        mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                    }
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                zone(tp, tracer && g == 0, j, 1);
+
+                // Lazy rescale: move the reference only when this block exceeds it by 2^8.
+                const bool move = mx > m_ref + kRescaleGap;
+                if (__any_sync(0xffffffffu, move)) {
+                    float f = 1.f;
+                    if (move) {
+                        f = fast_exp2(m_ref - mx);  // 0 on the first block
+                        m_ref = mx;
+                        l2[0] = __fmul2_rn(l2[0], make_float2(f, f));
+                        l2[1] = __fmul2_rn(l2[1], make_float2(f, f));
+                    }
+                    if (j > 0) {
+                        // O of this half holds blocks [0, j): wait for block j - 1's P V.
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + g), (gb - 1) & 1, abort_flag, 310 + g, tp.status));
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+                            float o[32];
+                            tmem_ld32(tmem_o + g * D + lane_addr + c * 32, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) o[e] *= f;
+                            tmem_st32(tmem_o + g * D + lane_addr + c * 32, o);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+
+                // P = 2^(s * scale - m) as packed bf16 pairs, two values per instruction where
+                // the packed fp32 pipe allows.
+                uint32_t wv[32];
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
+                if (whole) {
+                    // Every column visible: every other pair of exponentials runs on the FMA pipe
+                    // as a polynomial (MUFU is the narrowest pipe of this loop).
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
+                        float2 pr;
+                        if (e & 1) {
+                            pr = exp2_poly2(x);
+                        } else {
+                            pr.x = fast_exp2(x.x);
+                            pr.y = fast_exp2(x.y);
+                        }
+                        l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
+                        wv[e] = pack_bf16(pr.x, pr.y);
+                    }
+                } else {
+                    // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
+                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
+                        wv[e] = pack_bf16(pr.x, pr.y);
+                    }
+                }
+                zone(tp, tracer && g == 0, j, 2);
+                // P overwrites the first 32 of the 64 S columns this thread has just read.
+                tmem_st32(s_addr, reinterpret_cast<const float*>(wv));
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(P::bPFull + g));
+                zone(tp, tracer && g == 0, j, 3);
+            }
+
+            // Epilogue of the item: merge the two halves of each row and normalise. Every lane
+            // takes part in the TMEM reads and in the 256-thread barrier whatever happened.
+            const int last = blk + k.nblocks - 1;
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 0), last & 1, abort_flag, 330, tp.status));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 1), last & 1, abort_flag, 331, tp.status));
+            // One buffer is enough: nobody reaches the next item's write before every thread has
+            // passed this item's accumulator hand-over (bOFree), which comes after its reads here.
+            float2* ml = ml_base;
+            const float l_mine = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
+            ml[g * 128 + row] = make_float2(m_ref, l_mine);
+            if (lane == 0) ok_flags[warp] = ok;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            // All eight warps take the same decision, so none is left alone at this barrier.
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ok = ok && ok_flags[i] != 0;
+            if (ok) {
+                const float2 other = ml[(g ^ 1) * 128 + row];
+                const float m_all = fmaxf(m_ref, other.x);
+                const float base = (m_all == -INFINITY) ? 0.f : m_all;
+                const float f_mine = fast_exp2(m_ref - base), f_other = fast_exp2(other.x - base);
+                const float l_sum = l_mine * f_mine + other.y * f_other;
+                const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+                const float fa = (g == 0 ? f_mine : f_other) * inv, fb = (g == 0 ? f_other : f_mine) * inv;
+                // Group a writes output columns [0, D / 2), group b the rest.
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 64; ++c) {
+                    float oa[32], ob[32];
                     tmem_ld32(tmem_o + lane_addr + g * (D / 2) + c * 32, oa);
                     tmem_ld32(tmem_o + D + lane_addr + g * (D / 2) + c * 32, ob);
                     tmem_wait_ld();
-                } else {
+                    if (c + 1 == D / 64) {
+                        // The accumulators are in registers: the next item's P V may overwrite them.
+                        tc_fence_before();
+                        mbar_arrive(bar(P::bOFree));
+                    }
+                    if (real) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) oa[e] = ob[e] = 0.f;
-                }
-                if (real) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 v;
-                        v.x = pack_bf16(oa[e * 8 + 0] * fa + ob[e * 8 + 0] * fb, oa[e * 8 + 1] * fa + ob[e * 8 + 1] * fb);
-                        v.y = pack_bf16(oa[e * 8 + 2] * fa + ob[e * 8 + 2] * fb, oa[e * 8 + 3] * fa + ob[e * 8 + 3] * fb);
-                        v.z = pack_bf16(oa[e * 8 + 4] * fa + ob[e * 8 + 4] * fb, oa[e * 8 + 5] * fa + ob[e * 8 + 5] * fb);
-                        v.w = pack_bf16(oa[e * 8 + 6] * fa + ob[e * 8 + 6] * fb, oa[e * 8 + 7] * fa + ob[e * 8 + 7] * fb);
-                        *reinterpret_cast<uint4*>(og + c * 32 + e * 8) = v;
+                        for (int e = 0; e < 4; ++e) {
+                            uint4 v;
+                            v.x = pack_bf16(oa[e * 8 + 0] * fa + ob[e * 8 + 0] * fb, oa[e * 8 + 1] * fa + ob[e * 8 + 1] * fb);
+                            v.y = pack_bf16(oa[e * 8 + 2] * fa + ob[e * 8 + 2] * fb, oa[e * 8 + 3] * fa + ob[e * 8 + 3] * fb);
+                            v.z = pack_bf16(oa[e * 8 + 4] * fa + ob[e * 8 + 4] * fb, oa[e * 8 + 5] * fa + ob[e * 8 + 5] * fb);
+                            v.w = pack_bf16(oa[e * 8 + 6] * fa + ob[e * 8 + 6] * fb, oa[e * 8 + 7] * fa + ob[e * 8 + 7] * fb);
+                            *reinterpret_cast<uint4*>(og + c * 32 + e * 8) = v;
+                        }
                     }
                 }
+                if (real && g == 0 && p.lse) {
+                    p.lse[k.b * p.ls[0] + k.h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =
+                        l_sum > 0.f ? kLn2 * (m_all + log2f(l_sum)) : -INFINITY;
+                }
+            } else {
+                break;
             }
-            if (real && g == 0 && p.lse) {
-                p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =
-                    l_sum > 0.f ? kLn2 * (m_all + log2f(l_sum)) : -INFINITY;
-            }
+            blk += k.nblocks;
+            ++item;
+            first_item = false;
         }
     }
 
@@ -427,8 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    if (tp.trace && threadIdx.x == 0) {
-        const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (tp.trace && threadIdx.x == 256) {  // lane 0 of the MMA warp knows the block count
+        const int cta = blockIdx.x;
         if (cta < 1024) {
             long long t1;
             unsigned smid;
@@ -438,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             row[0] = cta_t0;
             row[1] = t1;
             row[2] = smid;
-            row[3] = nblocks;
+            row[3] = blocks_done;
         }
     }
 }
@@ -640,7 +741,13 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
     }
     constexpr int smem = P::kBytes;
     if (int rc = ensure_smem(fwd_tc5_kernel<D>, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
-    dim3 grid(p.heads, (p.sq + kBM - 1) / kBM, p.batch);
+    tp.q_tiles = (p.sq + kBM - 1) / kBM;
+    const int64_t work = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;
+    if (work > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: too many query tiles");
+    tp.work = static_cast<int>(work);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = tp.work < sms ? tp.work : sms;  // persistent: one CTA per SM
     fwd_tc5_kernel<D><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
     return check_cuda(cudaGetLastError(), "fwd_tc5 launch");
 }
