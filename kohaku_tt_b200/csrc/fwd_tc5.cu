@@ -26,12 +26,13 @@
 
 #include "tc5.cuh"
 
+#include <type_traits>
+
 namespace ktt {
 using namespace tc5;
 namespace {
 
-constexpr int kThreads = 320;     // 8 softmax warps + MMA warp + producer warp
-constexpr int kTmemCols = 512;    // two S / P buffers, O_a, O_b
+constexpr int kTmemCols = 512;    // two S / P buffers, one O accumulator per softmax group
 constexpr float kRescaleGap = 8.f;  // in log2 units
 
 // ---- shared-memory plan -----------------------------------------------------------------
@@ -50,15 +51,26 @@ constexpr float kRescaleGap = 8.f;  // in log2 units
 // columns it came from as packed bf16), O_a [256, 256 + D), O_b [256 + D, 256 + 2 D).
 template <int D>
 struct Plan {
+    // Softmax groups: each owns 128 / kGroups of a block's keys and its own accumulator.
+    // (Four groups were tried at D 64 with the registers re-divided by setmaxnreg: the
+    // softmax loop is bound by the SM's MUFU / FMA / issue rates, not by latency, and
+    // sixteen warps ran no faster than eight.)
+    static constexpr int kGroups = 2;
+    // Pairs of exponentials per thread and block that take the FMA-pipe polynomial instead
+    // of MUFU. Measured: 4 of 32 is best by ~2 %; more loses to the extra instructions.
+    static constexpr int kPolyPairs = 4;
+    static constexpr int kCols = 128 / kGroups;          // score columns per softmax thread
+    static constexpr int kThreads = 128 * kGroups + 64;  // softmax warps + MMA warp + producer warp
+    static constexpr int kMmaWarp = 4 * kGroups;
     static constexpr int kSub = D / 64;                  // 64-column sub-tiles of Q, K, V
     static constexpr int kTile = 128 * 128;              // one [128][64] bf16 sub-tile
     static constexpr int kStages = D == 64 ? 4 : 3;      // K/V ring depth
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + kSub * kTile;
     static constexpr int kV = kK + kStages * kSub * kTile;
-    static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [2 halves][128]: (m, l)
-    static constexpr int kBars = kML + 2 * 128 * 8;
-    static constexpr int kBytes = kBars + 256;
+    static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [groups][128]: (m, l)
+    static constexpr int kBars = kML + kGroups * 128 * 8;
+    static constexpr int kBytes = kBars + 512;
     // barrier indices (8 bytes each)
     static constexpr int bQFull = 0;
     static constexpr int bQFree = 1;
@@ -66,10 +78,16 @@ struct Plan {
     static constexpr int bKVFull = 3;                 // + stage
     static constexpr int bKVEmpty = bKVFull + kStages;
     static constexpr int bSFull = bKVEmpty + kStages;  // + buffer
-    static constexpr int bPFull = bSFull + 2;          // + half
-    static constexpr int bPVDone = bPFull + 2;         // + half
-    static constexpr int bCount = bPVDone + 2;
-    static_assert(bCount * 8 + 16 + 64 <= 256, "barrier area");
+    // P published / P V complete: one barrier per (group, S buffer). A parity wait tells
+    // phases apart only one step deep, and a group may run two blocks ahead of the MMA warp
+    // (or the MMA warp two P V ahead of a group's next look); alternating barriers keeps
+    // every one of them within one phase of its waiters.
+    static constexpr int bPFull = bSFull + 2;              // + 2 * group + buffer
+    static constexpr int bPVDone = bPFull + 2 * kGroups;   // + 2 * group + buffer
+    static constexpr int bCount = bPVDone + 2 * kGroups;
+    static constexpr int kBarBytes = 512;
+    static_assert(bCount * 8 + 16 + 4 * kMmaWarp <= kBarBytes, "barrier area");
+    static_assert(256 + kGroups * D <= 512, "tensor memory columns");
 };
 
 struct Tc5Params {
@@ -87,8 +105,13 @@ struct Tc5Params {
 //   slots 0-3: softmax row 0 of group a after S ready / maximum known / exponentials done /
 //              P published;  slot 4: MMA lane before the next-but-one Q K^T;
 //   slots 5-7: MMA lane after issuing P V of half a / of half b / the next-but-one Q K^T.
+// The stamps cost a few percent even when nobody listens, so the traced kernel is an
+// instantiation of its own, launched only while a trace buffer is set.
+template <bool kTrace>
 __device__ __forceinline__ void zone(const Tc5Params& tp, bool who, int j, int slot) {
-    if (tp.trace && who && j < 64) tp.trace[j * 8 + slot] = clock64();
+    if constexpr (kTrace) {
+        if (who && j < 64) tp.trace[j * 8 + slot] = clock64();
+    }
 }
 
 // One work item: 128 query rows of (batch b, head h).
@@ -125,11 +148,13 @@ __device__ __forceinline__ int work_of(int round, int cta, int ctas) {
 
 // ---- the kernel ------------------------------------------------------------------------
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
+template <int D, bool kTrace>
+__global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const Tc5Params tp) {
     using P = Plan<D>;
+    constexpr int G = P::kGroups, CG = P::kCols;
+    constexpr int kSoftmaxThreads = 128 * G;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
     // Swizzled tiles need a 1024-byte aligned base. The dynamic window starts there on
@@ -141,7 +166,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     // Second profiling zone set: rows 64.. of the trace buffer hold, per CTA, its start and
     // end on the global nanosecond timer, its SM and the key blocks it processed.
     long long cta_t0 = 0;
-    if (tp.trace && threadIdx.x == 256) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
+    long long cta_c0 = 0;
+    if (kTrace && threadIdx.x == kSoftmaxThreads) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cta_t0));
+        cta_c0 = clock64();
+    }
     const uint32_t bars = sbase + P::kBars;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
@@ -153,29 +182,40 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group_size = p.heads / p.kv_heads;
 
-    if (threadIdx.x == 0) {
+    // The producer warp sets the barriers up itself and goes straight to its first loads;
+    // it only arrives at the start-up barrier, the others wait there for it and for the
+    // tensor-memory allocation.
+    if (warp == P::kMmaWarp + 1) {
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
         mbar_init(bar(P::bQFull), 1);
         mbar_init(bar(P::bQFree), 1);
-        mbar_init(bar(P::bOFree), 256);
+        mbar_init(bar(P::bOFree), kSoftmaxThreads);
         for (int s = 0; s < P::kStages; ++s) {
             mbar_init(bar(P::bKVFull + s), 1);
             mbar_init(bar(P::bKVEmpty + s), 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(P::bSFull + i), 1);
+        for (int i = 0; i < 2; ++i) mbar_init(bar(P::bSFull + i), 1);
+        for (int i = 0; i < 2 * G; ++i) {
             mbar_init(bar(P::bPFull + i), 128);
             mbar_init(bar(P::bPVDone + i), 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
+      }
+      __syncwarp();
+      asm volatile("barrier.cta.arrive 0, %0;" ::"n"(P::kThreads) : "memory");
+    } else {
+      if (warp == P::kMmaWarp) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+      tc_fence_before();
+      asm volatile("barrier.cta.sync 0, %0;" ::"n"(P::kThreads) : "memory");
+      tc_fence_after();
     }
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_o = tmem + 256;    // O_a, then O_b
+    const uint32_t tmem_o = tmem + 256;    // one accumulator of D columns per group
 
     // Tensor-map coordinates: slot 0 is the head dim; rows, head and batch sit in the
     // slots the host sorted them into by stride.
@@ -190,7 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     // stages, S buffers and barrier parities are functions of those.
     int blocks_done = 0;
 
-    if (warp == 9) {
+    if (warp == P::kMmaWarp + 1) {
         // ---------------- producer (whole warp, converged) ----------------
         int item = 0, blk = 0;
         bool ok = true;
@@ -236,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             while (clock64() - t0 < 4000000) {
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == P::kMmaWarp) {
         // ---------------- MMA issuer (whole warp, converged) ----------------
         constexpr uint32_t idesc_s = instr_desc(kBN, false);
         constexpr uint32_t idesc_o = instr_desc(D, true);
@@ -267,7 +307,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             const Work k = decode_work(tp, w);
             if (k.nblocks == 0) continue;
             const bool mtracer = first_item && lane == 0 && blockIdx.x == 0;
+            zone<kTrace>(tp, mtracer, 61, 0);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bQFull), item & 1, abort_flag, 200, tp.status));
+            zone<kTrace>(tp, mtracer, 61, 1);
             // The first two Q K^T of the item run while the previous item's output is
             // still being written: they only need the S buffers, which are free once the
             // previous item's P V MMAs have been issued.
@@ -276,6 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + gb % P::kStages), (gb / P::kStages) & 1, abort_flag, 210 + j, tp.status));
                 if (ok) {
                     tc_fence_after();
+                    zone<kTrace>(tp, mtracer, 61, 2 + j);
                     issue_s(gb, j + 1 == k.nblocks);
                 }
             }
@@ -289,20 +332,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                     if (!ok) break;
                 }
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), gb & 1, abort_flag, 240 + g, tp.status));
+                for (int g = 0; g < G; ++g) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + 2 * g + (gb & 1)), (gb >> 1) & 1, abort_flag, 240 + g, tp.status));
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        // A: this half's P, 8 TMEM columns per 16 keys. B: V is MN-major, 16
+                    for (int ks = 0; ks < CG / 16; ++ks) {
+                        // A: this group's P, 8 TMEM columns per 16 keys. B: V is MN-major, 16
                         // keys down = 16 rows of 128 bytes; the second 64 columns of D are
                         // one sub-tile further (LBO).
-                        tc_mma_ts(tmem_o + g * D, p_tmem + g * 64 + ks * 8,
-                                  vd + (((g * 4 + ks) * 2048) >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_ts(tmem_o + g * D, p_tmem + g * CG + ks * 8,
+                                  vd + (((g * (CG / 16) + ks) * 2048) >> 4), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
                     }
-                    tc_commit(bar(P::bPVDone + g));
-                    zone(tp, mtracer, j, 5 + g);
+                    tc_commit(bar(P::bPVDone + 2 * g + (gb & 1)));
+                    if (g < 2) zone<kTrace>(tp, mtracer, j, 5 + g);
                 }
                 if (!ok) break;
                 tc_commit(bar(P::bKVEmpty + st));
@@ -314,9 +357,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bKVFull + gb2 % P::kStages), (gb2 / P::kStages) & 1, abort_flag, 220, tp.status));
                     if (!ok) break;
                     tc_fence_after();
-                    zone(tp, mtracer, j, 4);
+                    zone<kTrace>(tp, mtracer, j, 4);
                     issue_s(gb2, j + 3 == k.nblocks);
-                    zone(tp, mtracer, j, 7);
+                    zone<kTrace>(tp, mtracer, j, 7);
                 }
             }
             blk += k.nblocks;
@@ -326,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         blocks_done = blk;
     } else {
         // ---------------- softmax: thread = (query row, half of each block's keys) ----------------
-        const int g = warp >> 2;                        // 0: keys [0, 64), 1: keys [64, 128)
+        const int g = warp >> 2;                        // group: keys [g * CG, (g + 1) * CG) of each block
         const int row = (warp & 3) * 32 + lane;         // row inside the tile = TMEM lane
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         int item = 0, blk = 0;
@@ -342,12 +385,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             const SeqInfo& si = k.si;
             const int qi = k.q0 + row;                  // row inside the sequence
             const bool real = qi < si.lq;
-            __nv_bfloat16* og = p.out + k.b * p.os[0] + k.h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2] + g * (D / 2);
+            __nv_bfloat16* og = p.out + k.b * p.os[0] + k.h * p.os[1] + static_cast<int64_t>(si.q_off + qi) * p.os[2] + g * (D / G);
             if (k.nblocks == 0) {
                 // No key is visible to this tile: zeros, lse = -inf. No barrier is involved.
                 if (real) {
 #pragma unroll
-                    for (int c = 0; c < D / 16; ++c) *reinterpret_cast<uint4*>(og + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c = 0; c < D / G / 8; ++c) *reinterpret_cast<uint4*>(og + c * 8) = make_uint4(0u, 0u, 0u, 0u);
                     if (g == 0 && p.lse) p.lse[k.b * p.ls[0] + k.h * p.ls[1] + (si.q_off + qi) * p.ls[2]] = -INFINITY;
                 }
                 continue;
@@ -361,30 +404,37 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
 
             for (int j = 0; ok && j < k.nblocks; ++j) {
                 const int gb = blk + j;
-                const uint32_t s_addr = tmem + (gb & 1) * 128 + g * 64 + lane_addr;
+                const uint32_t s_addr = tmem + (gb & 1) * 128 + g * CG + lane_addr;
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull + (gb & 1)), (gb >> 1) & 1, abort_flag, 300 + g, tp.status));
                 if (!ok) break;
                 tc_fence_after();
-                zone(tp, tracer && g == 0, j, 0);
-                float s[64];
-                tmem_ld32(s_addr, s);
-                tmem_ld32(s_addr + 32, s + 32);
-                tmem_wait_ld();
-                const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
+                zone<kTrace>(tp, tracer && g == 0, j, 0);
+                float s[CG];
+                const int limit = row_limit - j * kBN - g * CG;  // this group's columns [0, limit) are visible
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                const bool whole = limit >= 64;
+                const bool whole = limit >= CG;
+                // The second half of the columns is still on its way while the maximum of
+                // the first is taken.
+                tmem_ld32(s_addr, s);
+                tmem_wait_ld();
+                tmem_ld32(s_addr + 32, s + 32);
                 if (whole) {
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                    for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                }
+                tmem_wait_ld();
+                if (whole) {
+#pragma unroll
+                    for (int e = 32; e < CG; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) {
+                    for (int e = 0; e < CG; ++e) {
                         s[e] = e < limit ? s[e] : -INFINITY;
                         mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
                     }
                 }
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-                zone(tp, tracer && g == 0, j, 1);
+                zone<kTrace>(tp, tracer && g == 0, j, 1);
 
                 // Lazy rescale: move the reference only when this block exceeds it by 2^8.
                 const bool move = mx > m_ref + kRescaleGap;
@@ -398,17 +448,28 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
                     }
                     if (j > 0) {
                         // O of this half holds blocks [0, j): wait for block j - 1's P V.
-                        ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + g), (gb - 1) & 1, abort_flag, 310 + g, tp.status));
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 2 * g + ((gb - 1) & 1)), ((gb - 1) >> 1) & 1, abort_flag, 310 + g, tp.status));
                         if (!ok) break;
                         tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < D / 32; ++c) {
-                            float o[32];
-                            tmem_ld32(tmem_o + g * D + lane_addr + c * 32, o);
+                        // One chunk at a time keeps this rare path from claiming registers.
+                        constexpr int kR = 32;
+#pragma unroll 1
+                        for (int c = 0; c < D / kR; ++c) {
+                            float o[kR];
+                            const uint32_t addr = tmem_o + g * D + lane_addr + c * kR;
+                            if constexpr (kR == 32) {
+                                tmem_ld32(addr, o);
+                            } else {
+                                tmem_ld16(addr, o);
+                            }
                             tmem_wait_ld();
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) o[e] *= f;
-                            tmem_st32(tmem_o + g * D + lane_addr + c * 32, o);
+                            for (int e = 0; e < kR; ++e) o[e] *= f;
+                            if constexpr (kR == 32) {
+                                tmem_st32(addr, o);
+                            } else {
+                                tmem_st16(addr, reinterpret_cast<const uint32_t*>(o));
+                            }
                         }
                         tmem_wait_st();
                     }
@@ -417,91 +478,137 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
 
                 // P = 2^(s * scale - m) as packed bf16 pairs, two values per instruction where
                 // the packed fp32 pipe allows.
-                uint32_t wv[32];
+                uint32_t wv[CG / 2];
                 const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
                 if (whole) {
-                    // Every column visible: every other pair of exponentials runs on the FMA pipe
-                    // as a polynomial (MUFU is the narrowest pipe of this loop).
+                    // Every column visible. kPolyPairs of this thread's pairs take the polynomial
+                    // on the FMA pipe, the rest MUFU; odd groups start with the polynomial and
+                    // even ones end with it, so that the warps sharing a scheduler are on
+                    // different pipes at the same time.
+                    auto exps = [&](auto poly_first) {
+                        constexpr bool kFirst = decltype(poly_first)::value;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
-                        float2 pr;
-                        if (e & 1) {
-                            pr = exp2_poly2(x);
-                        } else {
-                            pr.x = fast_exp2(x.x);
-                            pr.y = fast_exp2(x.y);
+                        for (int e = 0; e < CG / 2; ++e) {
+                            const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
+                            float2 pr;
+                            if (kFirst ? (e < P::kPolyPairs) : (e >= CG / 2 - P::kPolyPairs)) {
+                                pr = exp2_poly2(x);
+                            } else {
+                                pr.x = fast_exp2(x.x);
+                                pr.y = fast_exp2(x.y);
+                            }
+                            l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
+                            wv[e] = pack_bf16(pr.x, pr.y);
                         }
-                        l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
-                        wv[e] = pack_bf16(pr.x, pr.y);
+                    };
+                    if (g & 1) {
+                        exps(std::true_type{});
+                    } else {
+                        exps(std::false_type{});
                     }
                 } else {
                     // Masked columns take the MUFU path, whose 2^-inf is exactly 0.
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
+                    for (int e = 0; e < CG / 2; ++e) {
                         const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
                         const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                         l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
                         wv[e] = pack_bf16(pr.x, pr.y);
                     }
                 }
-                zone(tp, tracer && g == 0, j, 2);
-                // P overwrites the first 32 of the 64 S columns this thread has just read.
-                tmem_st32(s_addr, reinterpret_cast<const float*>(wv));
+                zone<kTrace>(tp, tracer && g == 0, j, 2);
+                // P overwrites the first half of the S columns this thread has just read.
+                if constexpr (CG == 64) {
+                    tmem_st32(s_addr, reinterpret_cast<const float*>(wv));
+                } else {
+                    tmem_st16(s_addr, wv);
+                }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(bar(P::bPFull + g));
-                zone(tp, tracer && g == 0, j, 3);
+                mbar_arrive(bar(P::bPFull + 2 * g + (gb & 1)));
+                zone<kTrace>(tp, tracer && g == 0, j, 3);
             }
 
             // Epilogue of the item: merge the two halves of each row and normalise. Every lane
             // takes part in the TMEM reads and in the 256-thread barrier whatever happened.
             const int last = blk + k.nblocks - 1;
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 0), last & 1, abort_flag, 330, tp.status));
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 1), last & 1, abort_flag, 331, tp.status));
+            // Each group waits for its own last P V; the barrier below then covers all of them.
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPVDone + 2 * g + (last & 1)), (last >> 1) & 1, abort_flag, 330 + g, tp.status));
             // One buffer is enough: nobody reaches the next item's write before every thread has
             // passed this item's accumulator hand-over (bOFree), which comes after its reads here.
+            zone<kTrace>(tp, tracer && g == 0, 60, 0);
             float2* ml = ml_base;
             const float l_mine = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
             ml[g * 128 + row] = make_float2(m_ref, l_mine);
             if (lane == 0) ok_flags[warp] = ok;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            // All eight warps take the same decision, so none is left alone at this barrier.
+            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            zone<kTrace>(tp, tracer && g == 0, 60, 1);
+            // All softmax warps take the same decision, so none is left alone at this barrier.
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ok = ok && ok_flags[i] != 0;
+            for (int i = 0; i < 4 * G; ++i) ok = ok && ok_flags[i] != 0;
             if (ok) {
-                const float2 other = ml[(g ^ 1) * 128 + row];
-                const float m_all = fmaxf(m_ref, other.x);
+                // Merge the groups' (m, l) of this row; f[i] rescales group i's accumulator.
+                float m_all = -INFINITY;
+                float2 mls[G];
+#pragma unroll
+                for (int i = 0; i < G; ++i) {
+                    mls[i] = ml[i * 128 + row];
+                    m_all = fmaxf(m_all, mls[i].x);
+                }
                 const float base = (m_all == -INFINITY) ? 0.f : m_all;
-                const float f_mine = fast_exp2(m_ref - base), f_other = fast_exp2(other.x - base);
-                const float l_sum = l_mine * f_mine + other.y * f_other;
+                float f[G], l_sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < G; ++i) {
+                    f[i] = fast_exp2(mls[i].x - base);
+                    l_sum += mls[i].y * f[i];
+                }
                 const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-                const float fa = (g == 0 ? f_mine : f_other) * inv, fb = (g == 0 ? f_other : f_mine) * inv;
-                // Group a writes output columns [0, D / 2), group b the rest.
+                // Group g writes output columns [g * D / G, (g + 1) * D / G).
+                constexpr int kOut = D / G;                  // columns per thread
+                constexpr int kChunk = kOut < 32 ? kOut : 32;
                 tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < D / 64; ++c) {
-                    float oa[32], ob[32];
-                    tmem_ld32(tmem_o + lane_addr + g * (D / 2) + c * 32, oa);
-                    tmem_ld32(tmem_o + D + lane_addr + g * (D / 2) + c * 32, ob);
+                for (int c = 0; c < kOut / kChunk; ++c) {
+                    // All groups' chunks are requested before the one wait.
+                    float o[G][kChunk];
+#pragma unroll
+                    for (int i = 0; i < G; ++i) {
+                        const uint32_t addr = tmem_o + i * D + lane_addr + g * kOut + c * kChunk;
+                        if constexpr (kChunk == 32) {
+                            tmem_ld32(addr, o[i]);
+                        } else {
+                            tmem_ld16(addr, o[i]);
+                        }
+                    }
                     tmem_wait_ld();
-                    if (c + 1 == D / 64) {
+                    float acc[kChunk];
+#pragma unroll
+                    for (int e = 0; e < kChunk; ++e) acc[e] = o[0][e] * (f[0] * inv);
+#pragma unroll
+                    for (int i = 1; i < G; ++i) {
+                        const float fi = f[i] * inv;
+#pragma unroll
+                        for (int e = 0; e < kChunk; ++e) acc[e] = fmaf(o[i][e], fi, acc[e]);
+                    }
+                    zone<kTrace>(tp, tracer && g == 0, 60, 2);
+                    if (c + 1 == kOut / kChunk) {
                         // The accumulators are in registers: the next item's P V may overwrite them.
                         tc_fence_before();
                         mbar_arrive(bar(P::bOFree));
                     }
                     if (real) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
+                        for (int e = 0; e < kChunk / 8; ++e) {
                             uint4 v;
-                            v.x = pack_bf16(oa[e * 8 + 0] * fa + ob[e * 8 + 0] * fb, oa[e * 8 + 1] * fa + ob[e * 8 + 1] * fb);
-                            v.y = pack_bf16(oa[e * 8 + 2] * fa + ob[e * 8 + 2] * fb, oa[e * 8 + 3] * fa + ob[e * 8 + 3] * fb);
-                            v.z = pack_bf16(oa[e * 8 + 4] * fa + ob[e * 8 + 4] * fb, oa[e * 8 + 5] * fa + ob[e * 8 + 5] * fb);
-                            v.w = pack_bf16(oa[e * 8 + 6] * fa + ob[e * 8 + 6] * fb, oa[e * 8 + 7] * fa + ob[e * 8 + 7] * fb);
-                            *reinterpret_cast<uint4*>(og + c * 32 + e * 8) = v;
+                            v.x = pack_bf16(acc[e * 8 + 0], acc[e * 8 + 1]);
+                            v.y = pack_bf16(acc[e * 8 + 2], acc[e * 8 + 3]);
+                            v.z = pack_bf16(acc[e * 8 + 4], acc[e * 8 + 5]);
+                            v.w = pack_bf16(acc[e * 8 + 6], acc[e * 8 + 7]);
+                            *reinterpret_cast<uint4*>(og + c * kChunk + e * 8) = v;
                         }
                     }
                 }
+                zone<kTrace>(tp, tracer && g == 0, 60, 3);
                 if (real && g == 0 && p.lse) {
                     p.lse[k.b * p.ls[0] + k.h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =
                         l_sum > 0.f ? kLn2 * (m_all + log2f(l_sum)) : -INFINITY;
@@ -519,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
     // frees tensor memory.
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == P::kMmaWarp) {
         if (*abort_flag) {
             const long long t0 = clock64();
             while (clock64() - t0 < 2000000) {
@@ -528,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    if (tp.trace && threadIdx.x == 256) {  // lane 0 of the MMA warp knows the block count
+    if (kTrace && threadIdx.x == kSoftmaxThreads) {  // lane 0 of the MMA warp knows the block count
         const int cta = blockIdx.x;
         if (cta < 1024) {
             long long t1;
@@ -540,6 +647,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_tc5_kernel(
             row[1] = t1;
             row[2] = smid;
             row[3] = blocks_done;
+            row[4] = cta_c0;
+            row[5] = clock64();
         }
     }
 }
@@ -740,7 +849,8 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     constexpr int smem = P::kBytes;
-    if (int rc = ensure_smem(fwd_tc5_kernel<D>, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
+    auto kernel = tp.trace ? fwd_tc5_kernel<D, true> : fwd_tc5_kernel<D, false>;
+    if (int rc = ensure_smem(kernel, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
     tp.q_tiles = (p.sq + kBM - 1) / kBM;
     const int64_t work = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;
     if (work > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: too many query tiles");
@@ -748,7 +858,7 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = tp.work < sms ? tp.work : sms;  // persistent: one CTA per SM
-    fwd_tc5_kernel<D><<<grid, kThreads, smem, stream>>>(mq, mk, mv, tp);
+    kernel<<<grid, P::kThreads, smem, stream>>>(mq, mk, mv, tp);
     return check_cuda(cudaGetLastError(), "fwd_tc5 launch");
 }
 
