@@ -276,3 +276,28 @@ def test_large_logits_stay_finite(cuda):
     out, lse = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda))
     assert torch.isfinite(out).all() and torch.isfinite(lse).all()
     assert rel(out, ao.ruler_dense(q, k, v)) <= 2e-2
+
+
+# Long causal work lists: many key blocks per item and several items per CTA let the two
+# softmax groups and the MMA warp drift apart by more than one block, which is what the
+# per-buffer barriers of the tcgen05 kernel are for. The full float64 score matrix is too
+# large here: whole output against the warp-MMA kernel, sampled rows against float64.
+@pytest.mark.parametrize("b,h,hk,s,d", [(2, 16, 16, 4096, 128), (2, 14, 2, 4096, 64)])
+def test_long_causal_work_lists(cuda, b, h, hk, s, d):
+    q, k, v = qkv(b, h, hk, s, s, d, b + h + s + d)
+    qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
+    for _ in range(3):  # repeated: the drift differs from launch to launch
+        out, lse = ops.sdpa_forward(qc, kc, vc, causal=True, kernel="flash")
+    torch.cuda.synchronize()
+    _lib.device_status()
+    ref, ref_lse = ops.sdpa_forward(qc, kc, vc, causal=True, kernel="mma")
+    assert rel(out.float(), ref.float()) <= 4e-3
+    assert (lse - ref_lse).abs().max().item() <= 2e-3
+    rows = torch.tensor([0, 1, 127, 128, 1000, 2047, 2048, 3000, s - 1])
+    group = h // hk
+    for bi, hi in ((0, 0), (b - 1, h - 1)):
+        kk, vv = k[bi, hi // group].double(), v[bi, hi // group].double()
+        scores = (q[bi, hi, rows].double() @ kk.T) / math.sqrt(d)
+        scores = scores.masked_fill(torch.arange(s)[None, :] > rows[:, None], float("-inf"))
+        ruler = torch.softmax(scores, dim=-1) @ vv
+        assert rel(out[bi, hi, rows.to(cuda)].cpu(), ruler) <= FWD_BOUND
