@@ -243,8 +243,9 @@ def _overrideable_backward(grad_out, q, k, v, attn_bias, grad_input_mask, out, l
 def _sdpa_lengths(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lengths: torch.Tensor,
                   is_causal: bool, scale: float | None, stats: bool) -> tuple[torch.Tensor, torch.Tensor]:
     if not stats and not is_causal and ops.decode_takes(q, k, v):
-        out, _ = ops.decode(q, k, v, key_lengths=lengths, scale=scale)
-        return out, torch.empty((0,), dtype=torch.float32, device=q.device)
+        # lse always has its full shape, so that the fake kernel below (which cannot ask
+        # about pointers) describes every route.
+        return ops.decode(q, k, v, key_lengths=lengths, scale=scale, need_lse=True)
     out, lse = ops.sdpa_forward(q, k, v, key_lengths=lengths, causal=is_causal, scale=scale,
                                 need_lse=True)
     return out, lse

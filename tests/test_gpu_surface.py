@@ -126,3 +126,67 @@ def test_merge_partials_equals_attention_over_the_union(cuda):
     ops.merge_partials(acc, l1, o2.float().contiguous(), l2)
     assert rel(acc, ao.ruler_dense(q, k, v)) <= FWD_BOUND
     assert (l1.cpu().double() - ao.ruler_lse(q, k, v)).abs().max() <= 3e-2
+
+
+# ---- torch.compile (tests/hardware/ops/test_sdpa_kernel.py:215-224) ----------------------
+
+def test_scope_reaches_compiled_code(cuda):
+    """The kernel scope is read when the compiled function runs, not when it was traced."""
+    q, k, v = (t.to(cuda) for t in qkv(1, 4, 4, 128, 128, 64, 10))
+    fn = torch.compile(lambda a, b, c: F.scaled_dot_product_attention(a, b, c),
+                       backend="aot_eager", fullgraph=True)
+    want = F.scaled_dot_product_attention(q, k, v)
+    before = ktt.counters()
+    with ktt.sdpa_kernel("mma"):
+        first = fn(q, k, v)
+    second = fn(q, k, v)
+    assert _delta(before) == {"attention_mma": 1, "attention_flash": 1}
+    assert torch.equal(second, want)
+    assert rel(first, want.float()) <= 4e-3
+
+
+def test_compiled_training_step_uses_these_kernels(cuda):
+    q, k, v, do = qkv(2, 4, 2, 256, 256, 64, 12, extra=1)
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, causal=True)
+    qc, kc, vc = (t.to(cuda).requires_grad_(True) for t in (q, k, v))
+
+    def step(a, b, c):
+        return F.scaled_dot_product_attention(a, b, c, is_causal=True, enable_gqa=True)
+
+    fn = torch.compile(step, backend="aot_eager", fullgraph=True)
+    before = ktt.counters()
+    out = fn(qc, kc, vc)
+    out.backward(do.to(cuda))
+    d = _delta(before)
+    assert d.get("attention_backward") == 1
+    assert d.get("attention_flash", 0) + d.get("attention_mma", 0) == 1
+    assert rel(out, ruler) <= FWD_BOUND
+    for got, want in ((qc.grad, dq), (kc.grad, dk), (vc.grad, dv)):
+        assert rel(got, want) <= GRAD_BOUND
+
+
+def test_key_lengths_op_compiles_whole(cuda):
+    """The custom ops carry fake kernels: decode and the training route trace without a
+    graph break and match eager bit for bit."""
+    q, k, v = (t.to(cuda) for t in qkv(4, 8, 2, 1, 512, 128, 14))
+    lengths = torch.tensor([100, 512, 1, 383], dtype=torch.int32, device=cuda)
+    fn = torch.compile(lambda a, b, c, n: ktt.sdpa(a, b, c, key_lengths=n), backend="aot_eager", fullgraph=True)
+    before = ktt.counters()
+    got = fn(q, k, v, lengths)
+    assert _delta(before) == {"attention_decode": 1}
+    assert torch.equal(got, ktt.sdpa(q, k, v, key_lengths=lengths))
+
+    q2, k2, v2, do = qkv(2, 4, 2, 96, 96, 64, 15, extra=1)
+    n2 = torch.tensor([96, 40], dtype=torch.int32, device=cuda)
+    a, b, c = (t.to(cuda).requires_grad_(True) for t in (q2, k2, v2))
+    fn2 = torch.compile(lambda x, y, z, n: ktt.sdpa(x, y, z, key_lengths=n, is_causal=True),
+                        backend="aot_eager", fullgraph=True)
+    out = fn2(a, b, c, n2)
+    out.backward(do.to(cuda))
+    a2, b2, c2 = (t.to(cuda).requires_grad_(True) for t in (q2, k2, v2))
+    eager = ktt.sdpa(a2, b2, c2, key_lengths=n2, is_causal=True)
+    eager.backward(do.to(cuda))
+    assert torch.equal(out, eager)
+    for got_g, want_g in ((a.grad, a2.grad), (b.grad, b2.grad), (c.grad, c2.grad)):
+        assert torch.equal(got_g, want_g)
+    assert torch.count_nonzero(b.grad[1, :, 40:]) == 0
