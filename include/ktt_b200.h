@@ -197,8 +197,8 @@ KTT_B200_API int ktt_b200_decode(const ktt_b200_decode_args* args, void* stream)
  * cause). It has no counterpart in the reference. The split-K partials go to a fixed
  * 4 MiB array inside the library, so args->scratch and args->scratch_bytes are ignored
  * and the call makes no allocation of any kind.
- *  - A call whose partials exceed 4 MiB (more than 216 (batch, kv head) pairs at head dim
- *    128 on a 148-SM GPU, 728 at head dim 64) is refused with KTT_B200_ERR_UNSUPPORTED.
+ *  - A call whose partials exceed 4 MiB (more than 207 (batch, kv head) pairs at head dim
+ *    128 on a 148-SM GPU, 696 at head dim 64) is refused with KTT_B200_ERR_UNSUPPORTED.
  *  - The first call on a device does a one-time set-up (address of the array, kernel
  *    attributes); make it before any stream capture.
  *  - Every call on a device uses the same array. It needs no clearing between calls, but
@@ -206,6 +206,37 @@ KTT_B200_API int ktt_b200_decode(const ktt_b200_decode_args* args, void* stream)
  *    keep them on one stream or order them with events.
  *  - Every GPU that loads the library holds the 4 MiB until the process ends. */
 KTT_B200_API int ktt_b200_decode_static(const ktt_b200_decode_args* args, void* stream);
+
+/* One decode step with its neighbours fused in: the rotate-half rotary embedding of the
+ * new query and key (ktt.rotary: csrc/aten/nn/aten_fused.cpp:30-43, bridge::rotary,
+ * device_attention.cpp:1340-1356), the write of the new key / value row into the static
+ * cache (the `index_copy_` that is 20 % of a decode token in the reference's profile,
+ * docs/reference/results.md:296) and attention over the old keys plus the new one.
+ *
+ * base: as for ktt_b200_decode with sq == 1; base.q is the query BEFORE rotary; base.k /
+ * base.v are the caches and are written: row lengths[b] of each (b, kv head) receives the
+ * rotated key / the value. base.key_lengths[b] is the number of keys already cached,
+ * clamped to [0, sk - 1]; attention sees lengths[b] + 1 keys. The lengths themselves are
+ * not changed; lengths_out, when set (a different buffer), receives lengths[b] + 1.
+ * k_new [B, Hk, D], v_new [B, Hk, D] bf16 with (batch, head) element strides, rows dense.
+ * cos / sin: bf16 rows of D values, rope_row_stride elements apart; row lengths[b] when
+ * rope_by_position is non-zero (a [positions, D] table), else row b (one row per batch).
+ * y = x * cos + cat(-x[D/2:], x[:D/2]) * sin, products and sum rounded separately in fp32,
+ * result rounded to bf16 before it is used or stored. */
+typedef struct ktt_b200_decode_append_args {
+    ktt_b200_decode_args base;
+    const void* k_new;
+    const void* v_new;
+    int64_t k_new_strides[2];
+    int64_t v_new_strides[2];
+    const void* cos;
+    const void* sin;
+    int64_t rope_row_stride;
+    int32_t rope_by_position;
+    int32_t* lengths_out; /* optional int32 [B] */
+} ktt_b200_decode_append_args;
+
+KTT_B200_API int ktt_b200_decode_append(const ktt_b200_decode_append_args* args, void* stream);
 
 /* Merge of two partial attention results over disjoint key sets (ring attention steps):
  * out / lse [rows] are updated in place with (out2, lse2). fp32 lse, bf16 or fp32 out.

@@ -12,7 +12,7 @@ include/ktt_b200.h); there is no CPU or PyTorch-math fallback.
 
 from ._lib import UnsupportedAttention, build, counters, reset_counters
 from .aten import fused_sdp_choice, install, installed
-from .attention import sdpa, sdpa_varlen
+from .attention import decode_step, sdpa, sdpa_varlen
 from .numerics import KERNELS, sdpa_kernel
 from .stats import diff_stats, format_stats, rel_rms
 
@@ -24,6 +24,7 @@ __all__ = [
     "UnsupportedAttention",
     "build",
     "counters",
+    "decode_step",
     "diff_stats",
     "format_stats",
     "fused_sdp_choice",

@@ -51,6 +51,7 @@ EXPORTS = (
     "ktt_b200_decode_scratch_bytes",
     "ktt_b200_decode",
     "ktt_b200_decode_static",
+    "ktt_b200_decode_append",
     "ktt_b200_merge_partials",
 )
 
@@ -130,6 +131,23 @@ class DecodeArgs(ctypes.Structure):
     ]
 
 
+class DecodeAppendArgs(ctypes.Structure):
+    """struct ktt_b200_decode_append_args."""
+
+    _fields_ = [
+        ("base", DecodeArgs),
+        ("k_new", _ptr),
+        ("v_new", _ptr),
+        ("k_new_strides", _i64 * 2),
+        ("v_new_strides", _i64 * 2),
+        ("cos", _ptr),
+        ("sin", _ptr),
+        ("rope_row_stride", _i64),
+        ("rope_by_position", _i32),
+        ("lengths_out", _ptr),
+    ]
+
+
 def sources():
     return sorted(
         os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu")
@@ -200,6 +218,7 @@ def lib():
     handle.ktt_b200_decode_scratch_bytes.restype = _i64
     handle.ktt_b200_decode.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
     handle.ktt_b200_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
+    handle.ktt_b200_decode_append.argtypes = [ctypes.POINTER(DecodeAppendArgs), _ptr]
     handle.ktt_b200_set_trace.argtypes = [_ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]
     if handle.ktt_b200_abi_version() != 1:

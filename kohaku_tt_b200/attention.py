@@ -74,6 +74,22 @@ def sdpa(q, k, v, key_lengths=None, is_causal=False, scale=None):
     return out
 
 
+def decode_step(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin, scale=None, lengths_out=None):
+    """One decode token in one kernel: rotate-half rotary on q [B, H, 1, D] and k_new
+    [B, Hk, 1, D], the static cache's row lengths[b] <- (rotated key, v_new), attention over
+    the lengths[b] + 1 keys. In the reference these are three ops (ktt.rotary twice,
+    StaticCache's index_copy_, sdpa with key_lengths), the cache write alone a fifth of a
+    decode token. lengths: int32 [B] on the device, keys already cached; cos / sin: bf16
+    [B, D] rows for this step, or a [positions, D] table looked up at lengths[b]. No
+    gradients. Returns out [B, H, 1, D]; k_cache / v_cache are updated in place and
+    lengths_out (optional, another buffer) receives lengths + 1."""
+    from . import ops
+
+    with torch.no_grad():
+        return ops.decode_append(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin,
+                                 scale=scale, lengths_out=lengths_out)
+
+
 def offsets(cu_seq):
     """Cumulative sequence offsets as a tuple of ints (a list or an int tensor; a device
     tensor is downloaded) (varlen.py:23-28)."""

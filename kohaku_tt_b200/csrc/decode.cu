@@ -20,8 +20,11 @@
 //             pair's partials (fixed order: deterministic), writes bf16 and puts the
 //             counter back to zero.
 //
-// Scratch: int32 counters [pairs] that must be zero before the first call (the kernel
-// leaves them zero), then per slot 16 maxima, 16 sums and 16 x D partial outputs.
+// Scratch: 1024 int32 ticket counters that must be zero before the first call (the kernel
+// leaves them zero), then per slot 16 maxima, 16 sums and 16 x D partial outputs. A pair
+// that spans several CTAs is the last pair of the first of them, so that CTA's index names
+// its counter: the counter area has one size whatever the batch, and calls of different
+// shapes can share one scratch buffer without a partial ever landing on a counter.
 //
 // Semantics are kohakutt.sdpa(q, k, v, key_lengths=) (attention.py:10-23): keys at or past
 // a length contribute nothing, whatever they hold; lengths are clamped to [1, Sk].
@@ -41,11 +44,21 @@ struct DecodeParams {
     float* lse;
     int64_t qs[3], ks[3], vs[3], os[3];
     const int32_t* key_lengths;
-    int32_t* counters;  // [batch * kv_heads] tickets, zero between calls
+    int32_t* counters;  // [kMaxCtas] tickets, indexed by the first CTA of a pair; zero between calls
     float* part_m;      // [slots][16]
     float* part_l;      // [slots][16]
     float* part_o;      // [slots][16][d]
     int slots;
+    // Append mode (decode_kernel<.., true>): the step's new key / value rows and the rotary
+    // rows; k and v above are then written at each sequence's position.
+    const __nv_bfloat16* k_new;   // [B, Hk, D]
+    const __nv_bfloat16* v_new;
+    int64_t kns[2], vns[2];       // (batch, head) strides
+    const __nv_bfloat16* rope_cos;
+    const __nv_bfloat16* rope_sin;
+    int64_t rope_stride;
+    int rope_by_position;
+    int32_t* lengths_out;
 };
 
 namespace {
@@ -54,15 +67,40 @@ constexpr int kTile = 64;      // keys per tile (16 per warp)
 constexpr int kThreads = 128;
 constexpr int kMaxBatch = 512;   // clamped lengths and their prefix sums live in shared memory
 constexpr int kMaxPending = 8;   // stored partials per CTA before their tickets are drawn
+constexpr int kMaxCtas = 1024;   // ticket counters in the scratch
 
+// Keys batch b attends over. Append mode: the cached count clamped to [0, sk - 1], plus the
+// new key.
+template <bool kAppend>
 __device__ __forceinline__ int clamp_len(const DecodeParams& p, int b) {
+    if (kAppend) {
+        int l = p.key_lengths[b];
+        l = l < 0 ? 0 : l;
+        return (l > p.sk - 1 ? p.sk - 1 : l) + 1;
+    }
     if (!p.key_lengths) return p.sk;
     int l = p.key_lengths[b];
     l = l < 1 ? 1 : l;
     return l > p.sk ? p.sk : l;
 }
 
+// Rotate-half rotary embedding of columns c, c + 1 of a row x (c even): products and sum
+// rounded separately in fp32, as the composite op does.
+template <int D>
+__device__ __forceinline__ uint32_t rope_pair(const __nv_bfloat16* x, const __nv_bfloat16* cs,
+                                              const __nv_bfloat16* sn, int c) {
+    const bool low = c < D / 2;
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + (low ? c + D / 2 : c - D / 2)));
+    const float2 co = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(cs + c));
+    const float2 si = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sn + c));
+    const float r0 = low ? -b.x : b.x, r1 = low ? -b.y : b.y;
+    return pack_bf16(__fadd_rn(__fmul_rn(a.x, co.x), __fmul_rn(r0, si.x)),
+                     __fadd_rn(__fmul_rn(a.y, co.y), __fmul_rn(r1, si.y)));
+}
+
 // prefix[b] = sum_{b' < b} ceil(len_b' / 64) for b in [0, batch], by one CTA of 128 threads.
+template <bool kAppend>
 __device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix, int* lens, int* warp_sums) {
     constexpr int kPer = kMaxBatch / kThreads;  // consecutive entries per thread
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -70,7 +108,7 @@ __device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix,
 #pragma unroll
     for (int i = 0; i < kPer; ++i) {
         const int b = threadIdx.x * kPer + i;
-        const int len = b < p.batch ? clamp_len(p, b) : 0;
+        const int len = b < p.batch ? clamp_len<kAppend>(p, b) : 0;
         if (b < p.batch) lens[b] = len;
         tiles[i] = (len + kTile - 1) / kTile;
         mine += tiles[i];
@@ -133,7 +171,7 @@ __device__ __forceinline__ int swz(int row, int col) {
     return (row * D + ((((col >> 3) ^ (row & 7))) << 3) + (col & 7)) * 2;
 }
 
-template <int D, int NS>
+template <int D, int NS, bool kAppend>
 __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams p) {
     constexpr int kStage = 2 * kTile * D * 2;  // K then V, bytes
     extern __shared__ __align__(128) unsigned char smem[];
@@ -152,7 +190,10 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     const int group = p.heads / p.kv_heads;
     const int rows = group * p.sq;  // valid rows of the 16-row MMA tile
 
-    scan_lengths(p, prefix_s, lens_s, misc);
+    scan_lengths<kAppend>(p, prefix_s, lens_s, misc);
+    if (kAppend && blockIdx.x == 0 && p.lengths_out) {
+        for (int b = threadIdx.x; b < p.batch; b += kThreads) p.lengths_out[b] = lens_s[b];
+    }
     const int total = p.kv_heads * prefix_s[p.batch];
     const int upc = (total + gridDim.x - 1) / gridDim.x;
     const int u0 = blockIdx.x * upc;
@@ -200,9 +241,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             const int* e = pend + 5 * threadIdx.x;
             const int parts = e[2] - e[1] + 1;
             int ticket;
-            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + e[0]) : "memory");
+            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + e[1]) : "memory");
             last_s[threadIdx.x] = ticket == parts - 1;
-            if (ticket == parts - 1) p.counters[e[0]] = 0;  // all holders have drawn
+            if (ticket == parts - 1) p.counters[e[1]] = 0;  // all holders have drawn
         }
         __syncthreads();
         // All pairs this CTA finishes, flattened so that their loads are in flight together.
@@ -296,10 +337,20 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 const int gi = ok ? r / p.sq : 0, tq = ok ? r % p.sq : 0;
                 const __nv_bfloat16* qg = p.q + cons.b * p.qs[0] +
                     (cons.hk * group + gi) * p.qs[1] + tq * p.qs[2];
+                if (kAppend) {
+                    // The query gets the rotary row of the new token's position.
+                    const int64_t rr = (p.rope_by_position ? cons.len - 1 : cons.b) * p.rope_stride;
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        qa[kk][half] = ok ? rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + t * 2) : 0u;
+                        qa[kk][half + 2] = ok ? rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + 8 + t * 2) : 0u;
+                    }
+                } else {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     qa[kk][half] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + t * 2) : 0u;
                     qa[kk][half + 2] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + 8 + t * 2) : 0u;
+                }
                 }
             }
 #pragma unroll
@@ -310,6 +361,32 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         // (The query loads above are in flight while this waits for the tile.)
         cp_async_wait<NS - 1>();
         __syncwarp();
+
+        if (kAppend) {
+            // The warp whose 16 rows hold the new token's slot puts the rotated key and the
+            // value there, in the tile it is about to use and in the cache. Whatever the
+            // copy brought for that row is replaced; no other CTA or warp touches it.
+            const int pos = cons.len - 1;
+            if (pos / kTile == cons.tile && (pos % kTile) / 16 == warp) {
+                const int r = pos % kTile;
+                unsigned char* sK = ring + st * kStage;
+                unsigned char* sV = sK + kTile * D * 2;
+                const __nv_bfloat16* kn = p.k_new + cons.b * p.kns[0] + cons.hk * p.kns[1];
+                const __nv_bfloat16* vn = p.v_new + cons.b * p.vns[0] + cons.hk * p.vns[1];
+                __nv_bfloat16* kc = const_cast<__nv_bfloat16*>(p.k) + cons.b * p.ks[0] + cons.hk * p.ks[1] + static_cast<int64_t>(pos) * p.ks[2];
+                __nv_bfloat16* vc = const_cast<__nv_bfloat16*>(p.v) + cons.b * p.vs[0] + cons.hk * p.vs[1] + static_cast<int64_t>(pos) * p.vs[2];
+                const int64_t rr = (p.rope_by_position ? pos : cons.b) * p.rope_stride;
+                for (int c = lane * 2; c < D; c += 64) {
+                    const uint32_t kr = rope_pair<D>(kn, p.rope_cos + rr, p.rope_sin + rr, c);
+                    const uint32_t vr = *reinterpret_cast<const uint32_t*>(vn + c);
+                    *reinterpret_cast<uint32_t*>(sK + swz<D>(r, c)) = kr;
+                    *reinterpret_cast<uint32_t*>(sV + swz<D>(r, c)) = vr;
+                    *reinterpret_cast<uint32_t*>(kc + c) = kr;
+                    *reinterpret_cast<uint32_t*>(vc + c) = vr;
+                }
+                __syncwarp();
+            }
+        }
 
         const int j0 = cons.tile * kTile + warp * 16;
         if (j0 < cons.len) {
@@ -483,15 +560,15 @@ int stream_ctas_for_device() {
     return 2 * sms;
 }
 
-template <int D, int NS>
+template <int D, int NS, bool kAppend>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
     constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (2 * kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
-    if (int rc = ensure_smem(decode_kernel<D, NS>, smem, "cudaFuncSetAttribute(decode)")) return rc;
-    decode_kernel<D, NS><<<ctas, kThreads, smem, stream>>>(p);
+    if (int rc = ensure_smem(decode_kernel<D, NS, kAppend>, smem, "cudaFuncSetAttribute(decode)")) return rc;
+    decode_kernel<D, NS, kAppend><<<ctas, kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode launch");
 }
 
-// Scratch layout: ticket counters (int32, padded to 256 B), then m, l, O partials.
+// Scratch layout: 1024 ticket counters (int32), then m, l, O partials.
 struct ScratchLayout {
     int64_t counter_bytes, m_bytes, l_bytes, o_bytes, total;
     int slots;
@@ -501,7 +578,7 @@ ScratchLayout scratch_layout(int batch, int kv_heads, int d, int ctas) {
     ScratchLayout s;
     s.slots = ctas + batch * kv_heads;
     auto up = [](int64_t x) { return (x + 255) / 256 * 256; };
-    s.counter_bytes = up(static_cast<int64_t>(batch) * kv_heads * 4);
+    s.counter_bytes = kMaxCtas * 4;
     s.m_bytes = up(static_cast<int64_t>(s.slots) * 16 * 4);
     s.l_bytes = s.m_bytes;
     s.o_bytes = up(static_cast<int64_t>(s.slots) * 16 * d * 4);
@@ -516,6 +593,7 @@ int decode_ctas(const ktt_b200_decode_args* a) {
         const int64_t want = static_cast<int64_t>(a->splits) * a->batch * a->kv_heads;
         if (want < ctas) ctas = static_cast<int>(want);
     }
+    if (ctas > kMaxCtas) ctas = kMaxCtas;
     return ctas < 1 ? 1 : ctas;
 }
 
@@ -535,7 +613,7 @@ const char* decode_refusal(const ktt_b200_decode_args* a) {
 
 // Checks, parameter block and launch shared by both entry points; `base` is the scratch.
 int run_decode(const ktt_b200_decode_args* a, unsigned char* base, const ScratchLayout& lay, int ctas,
-               void* stream, const char* what) {
+               void* stream, const char* what, const ktt_b200_decode_append_args* app = nullptr) {
     if ((reinterpret_cast<uintptr_t>(a->k) | reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(base)) & 15) {
         return fail(KTT_B200_ERR_UNSUPPORTED, "%s: k, v and scratch must be 16-byte aligned", what);
     }
@@ -561,10 +639,27 @@ int run_decode(const ktt_b200_decode_args* a, unsigned char* base, const Scratch
     p.part_l = reinterpret_cast<float*>(base + lay.counter_bytes + lay.m_bytes);
     p.part_o = reinterpret_cast<float*>(base + lay.counter_bytes + lay.m_bytes + lay.l_bytes);
     p.slots = lay.slots;
+    p.k_new = p.v_new = p.rope_cos = p.rope_sin = nullptr;
+    p.lengths_out = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     note_call(3);
-    if (a->d == 64) return launch<64, 6>(p, ctas, st);
-    return launch<128, 3>(p, ctas, st);
+    if (app) {
+        p.k_new = static_cast<const __nv_bfloat16*>(app->k_new);
+        p.v_new = static_cast<const __nv_bfloat16*>(app->v_new);
+        for (int i = 0; i < 2; ++i) {
+            p.kns[i] = app->k_new_strides[i];
+            p.vns[i] = app->v_new_strides[i];
+        }
+        p.rope_cos = static_cast<const __nv_bfloat16*>(app->cos);
+        p.rope_sin = static_cast<const __nv_bfloat16*>(app->sin);
+        p.rope_stride = app->rope_row_stride;
+        p.rope_by_position = app->rope_by_position;
+        p.lengths_out = app->lengths_out;
+        if (a->d == 64) return launch<64, 6, true>(p, ctas, st);
+        return launch<128, 3, true>(p, ctas, st);
+    }
+    if (a->d == 64) return launch<64, 6, false>(p, ctas, st);
+    return launch<128, 3, false>(p, ctas, st);
 }
 
 }  // namespace
@@ -595,6 +690,34 @@ extern "C" int ktt_b200_decode(const ktt_b200_decode_args* a, void* stream) {
     return run_decode(a, static_cast<unsigned char*>(a->scratch), lay, ctas, stream, "decode");
 }
 
+// One decode step with rotary, cache append and attention in the same launch.
+extern "C" int ktt_b200_decode_append(const ktt_b200_decode_append_args* app, void* stream) {
+    if (!app) return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_append: null arguments");
+    const ktt_b200_decode_args* a = &app->base;
+    if (const char* why = decode_refusal(a)) return fail(KTT_B200_ERR_UNSUPPORTED, "decode_append: %s", why);
+    if (a->sq != 1) return fail(KTT_B200_ERR_UNSUPPORTED, "decode_append: one query token per sequence");
+    if (!a->q || !a->k || !a->v || !a->out || !a->scratch || !a->key_lengths || !app->k_new || !app->v_new ||
+        !app->cos || !app->sin) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_append: null tensor, lengths, rotary or scratch pointer");
+    }
+    if (app->lengths_out == a->key_lengths) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_append: lengths_out must not be the lengths themselves");
+    }
+    const uintptr_t small = reinterpret_cast<uintptr_t>(app->k_new) | reinterpret_cast<uintptr_t>(app->v_new) |
+                            reinterpret_cast<uintptr_t>(app->cos) | reinterpret_cast<uintptr_t>(app->sin);
+    if ((small & 3) || (app->rope_row_stride & 1) || ((app->k_new_strides[0] | app->k_new_strides[1] |
+        app->v_new_strides[0] | app->v_new_strides[1]) & 1)) {
+        return fail(KTT_B200_ERR_UNSUPPORTED, "decode_append: new rows and rotary rows must be 4-byte aligned with even strides");
+    }
+    const int ctas = decode_ctas(a);
+    const ScratchLayout lay = scratch_layout(a->batch, a->kv_heads, a->d, ctas);
+    if (a->scratch_bytes < lay.total) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "decode_append: scratch holds %lld bytes, %lld needed",
+                    static_cast<long long>(a->scratch_bytes), static_cast<long long>(lay.total));
+    }
+    return run_decode(a, static_cast<unsigned char*>(a->scratch), lay, ctas, stream, "decode_append", app);
+}
+
 // ---- decode without any allocation ---------------------------------------------------------
 //
 // Some hosts of this library may not allocate device memory once they are running: an
@@ -607,8 +730,8 @@ extern "C" int ktt_b200_decode(const ktt_b200_decode_args* a, void* stream) {
 namespace ktt {
 namespace {
 
-// Room for the partials of 216 (batch, kv head) pairs at head dim 128 on a 148-SM part,
-// or 728 pairs at head dim 64. Each GPU that loads the library holds these 4 MiB until
+// Room for the partials of 207 (batch, kv head) pairs at head dim 128 on a 148-SM part,
+// or 696 pairs at head dim 64. Each GPU that loads the library holds these 4 MiB until
 // the process exits.
 constexpr int64_t kStaticScratchBytes = 4ll << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

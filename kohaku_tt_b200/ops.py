@@ -394,6 +394,71 @@ def decode(q, k, v, key_lengths=None, scale=None, need_lse=False, splits=0, scra
     return out, lse
 
 
+def decode_append(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin, by_position=None,
+                  scale=None, lengths_out=None, scratch=None):
+    """One decode step in one launch: rotate-half rotary of q [B, H, 1, D] and k_new
+    [B, Hk, 1, D] (ktt.rotary, aten_fused.cpp:30-43), k_cache / v_cache [B, Hk, Smax, D]
+    row lengths[b] <- (rotated key, v_new) (the StaticCache `index_copy_`), attention over
+    the lengths[b] + 1 keys. lengths int32 [B] on the device = keys already cached (< Smax);
+    they are not changed, lengths_out (another int32 [B]) receives lengths + 1 when given.
+    cos / sin bf16: [B, D] rows per batch, or a [positions, D] table indexed by lengths[b]
+    (`by_position`; default: a table when the row count differs from B). Returns out
+    [B, H, 1, D]; the caches are updated in place."""
+    _require_cuda(q, k_cache, v_cache, lengths)
+    b, h, sq, d = q.shape
+    if sq != 1 or k_new.shape != (b, k_cache.shape[1], 1, d) or v_new.shape != k_new.shape:
+        raise ValueError("kohaku_tt_b200.decode_append: q [B, H, 1, D], k_new / v_new [B, Hk, 1, D]")
+    if not decode_takes(q, k_cache, v_cache):
+        raise _lib.UnsupportedAttention("kohaku_tt_b200.decode_append: shapes or strides not taken")
+    if lengths.dtype != torch.int32 or lengths.dim() != 1 or lengths.numel() != b:
+        raise ValueError("kohaku_tt_b200: lengths must be int32 [B]")
+    cos2, sin2 = cos.reshape(-1, d), sin.reshape(-1, d)
+    if cos2.dtype != torch.bfloat16 or sin2.dtype != torch.bfloat16 or cos2.shape != sin2.shape:
+        raise ValueError("kohaku_tt_b200.decode_append: cos / sin must be bf16 rows of D values, same shape")
+    if cos2.stride(-1) != 1 or sin2.stride(-1) != 1 or cos2.stride(0) != sin2.stride(0):
+        cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    if by_position is None:
+        by_position = cos2.shape[0] != b
+    if by_position and cos2.shape[0] < k_cache.shape[2]:
+        raise ValueError("kohaku_tt_b200.decode_append: the rotary table must cover every cache position")
+    if not by_position and cos2.shape[0] != b:
+        raise ValueError("kohaku_tt_b200.decode_append: one rotary row per batch entry")
+    if k_new.stride(-1) != 1 or v_new.stride(-1) != 1:
+        k_new, v_new = k_new.contiguous(), v_new.contiguous()
+    app = _lib.DecodeAppendArgs()
+    args = app.base
+    args.batch, args.heads, args.kv_heads = b, h, k_cache.shape[1]
+    args.sq, args.sk, args.d, args.dv = 1, k_cache.shape[2], d, d
+    args.scale = float(scale) if scale is not None else 1.0 / math.sqrt(d)
+    args.q, args.k, args.v = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    _set3(args.q_strides, _bhs_strides(q))
+    _set3(args.k_strides, _bhs_strides(k_cache))
+    _set3(args.v_strides, _bhs_strides(v_cache))
+    lengths = lengths.contiguous()
+    args.key_lengths = lengths.data_ptr()
+    app.k_new, app.v_new = k_new.data_ptr(), v_new.data_ptr()
+    app.k_new_strides[0], app.k_new_strides[1] = k_new.stride(0), k_new.stride(1)
+    app.v_new_strides[0], app.v_new_strides[1] = v_new.stride(0), v_new.stride(1)
+    app.cos, app.sin = cos2.data_ptr(), sin2.data_ptr()
+    app.rope_row_stride = cos2.stride(0)
+    app.rope_by_position = 1 if by_position else 0
+    if lengths_out is not None:
+        if lengths_out.dtype != torch.int32 or lengths_out.shape != lengths.shape or not lengths_out.is_contiguous():
+            raise ValueError("kohaku_tt_b200: lengths_out must be a contiguous int32 [B]")
+        app.lengths_out = lengths_out.data_ptr()
+    with torch.cuda.device(q.device):
+        out = torch.empty((b, h, 1, d), dtype=q.dtype, device=q.device)
+        args.out = out.data_ptr()
+        _set3(args.out_strides, _bhs_strides(out))
+        if scratch is None:
+            scratch, need = decode_scratch(args, q.device)
+        else:
+            need = scratch.numel() * scratch.element_size()
+        args.scratch, args.scratch_bytes = scratch.data_ptr(), need
+        _lib.check(_lib.lib().ktt_b200_decode_append(ctypes.byref(app), _stream(q.device)), "decode_append")
+    return out
+
+
 def merge_partials(out, lse, out2, lse2):
     """In place: (out, lse) <- merge with (out2, lse2), two attention results of the
     same queries over disjoint key sets. out [..., Dv] bf16 or fp32, lse [...] fp32."""

@@ -114,6 +114,33 @@ def grads_dense(q, k, v, dout, mask=None, causal=False, scale=None, lengths=None
     return out.detach(), qd.grad, kd.grad, vd.grad
 
 
+def rotary_composite(x, cos, sin):
+    """ktt.rotary's composite (csrc/aten/nn/aten_fused.cpp:30-43): x * cos + cat(-x2, x1) *
+    sin over the last dim with every product and the sum rounded in fp32, result in x's
+    dtype. cos / sin broadcast against x (rows already chosen by the caller)."""
+    xf = x.float()
+    x1, x2 = xf.chunk(2, -1)
+    rotated = torch.cat([-x2, x1], -1)
+    return (xf * cos.float() + rotated * sin.float()).to(x.dtype)
+
+
+def decode_step(q, k_new, v_new, k_cache, v_cache, lengths, cos_rows, sin_rows, scale=None):
+    """One decode token the way the reference's model code runs it: rotary on q and k_new
+    (rows cos_rows / sin_rows [B, D], one per batch entry), StaticCache `index_copy_` of the
+    new key / value at position lengths[b] (docs/reference/results.md:296), attention over
+    the lengths[b] + 1 keys in float64. Returns (out float64 [B, H, 1, D], updated k cache,
+    updated v cache); the inputs are not modified."""
+    c, s_ = cos_rows[:, None, None, :], sin_rows[:, None, None, :]
+    q_rot = rotary_composite(q, c, s_)
+    k_rot = rotary_composite(k_new, c, s_)
+    k2, v2 = k_cache.clone(), v_cache.clone()
+    for b, n in enumerate(lengths):
+        k2[b, :, n] = k_rot[b, :, 0]
+        v2[b, :, n] = v_new[b, :, 0]
+    out = ruler_lengths(q_rot, k2, v2, [n + 1 for n in lengths], causal=False, scale=scale)
+    return out, k2, v2
+
+
 def _bottom_right(lq, lk):
     """Query r sees its first min(Lk, r + 1 + Lk - Lq) keys (varlen_plan.hpp:69-70)."""
     return torch.arange(lk)[None, :] < (torch.arange(lq)[:, None] + 1 + lk - lq)

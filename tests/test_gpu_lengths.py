@@ -139,3 +139,15 @@ def test_decode_without_lengths_and_strided_cache(cuda):
     assert rel(out, ao.ruler_dense(q, k, v)) <= FWD_BOUND
     with pytest.raises(_lib.UnsupportedAttention):
         ops.decode(q.to(cuda)[..., :32], big_k[..., :32], big_v[..., :32])
+
+
+def test_decode_calls_of_different_shapes_share_one_scratch(cuda):
+    """The cached scratch is reused by calls of any shape: the ticket counters sit in a
+    fixed area that no call's partials reach."""
+    shapes = [(5, 4, 4, 200, 64), (64, 16, 2, 1024, 128), (3, 14, 2, 300, 64), (64, 16, 2, 1024, 128)]
+    for i, (b, h, hk, smax, d) in enumerate(shapes):
+        q, k, v = ao.make_inputs([(b, h, 1, d), (b, hk, smax, d), (b, hk, smax, d)], 40 + i)
+        lengths = torch.randint(1, smax + 1, (b,), generator=torch.Generator().manual_seed(i)).tolist()
+        n = torch.tensor(lengths, dtype=torch.int32, device=cuda)
+        out, _ = ops.decode(q.to(cuda), k.to(cuda), v.to(cuda), key_lengths=n)
+        assert rel(out, ao.ruler_lengths(q, k, v, lengths)) <= FWD_BOUND, (i, b, h)
