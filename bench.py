@@ -461,6 +461,57 @@ def leg_decode(dev, peaks, warmup):
             "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0"}
 
 
+def leg_decode_step(dev, peaks, warmup):
+    """One decode token with its neighbours: rotary on q and the new key, cache append,
+    attention. The fused launch beside the same work as separate ops (rotary by torch
+    elementwise ops twice, index_copy_ twice, then the decode kernel)."""
+    import kohaku_tt_b200 as ktt
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.randint(512, 4096, (64,), generator=g, dtype=torch.int32)
+    caches = []
+    for i in range(2):
+        k = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(i), device=dev, dtype=torch.float32).to(torch.bfloat16)
+        v = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(9 + i), device=dev, dtype=torch.float32).to(torch.bfloat16)
+        caches.append((k, v))
+    q, k_new, v_new = (t.to(dev) for t in ao.make_inputs([(64, 16, 1, 128), (64, 2, 1, 128), (64, 2, 1, 128)], 3))
+    pos = torch.arange(4096, dtype=torch.float32, device=dev)[:, None]
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32, device=dev) / 128))
+    ang = torch.cat([pos * inv, pos * inv], dim=-1)
+    cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+    ln = lengths.to(dev)
+    ln_next = ln + 1
+    idx = ln.long()
+
+    def fused(i):
+        ktt.decode_step(q, k_new, v_new, *caches[i % 2], ln, cos, sin)
+
+    def rotary(x, c, s_):
+        xf = x.float()
+        x1, x2 = xf.chunk(2, -1)
+        return (xf * c + torch.cat([-x2, x1], -1) * s_).to(x.dtype)
+
+    batch = torch.arange(64, device=dev)
+
+    def separate(i):
+        kc, vc = caches[i % 2]
+        c, s_ = cos[idx][:, None, None, :].float(), sin[idx][:, None, None, :].float()
+        q_rot, k_rot = rotary(q, c, s_), rotary(k_new, c, s_)
+        kc[batch, :, idx] = k_rot[:, :, 0]
+        vc[batch, :, idx] = v_new[:, :, 0]
+        ops.decode(q_rot, kc, vc, key_lengths=ln_next)
+
+    ms = _time(fused, 50, warmup)
+    ms_sep = _time(separate, 50, warmup)
+    nbytes = float((lengths + 1).sum()) * 2 * (128 + 128) * 2 + 2 * q.numel() * 2
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"value": gbs, "ms": ms, "separate_ops_ms": ms_sep, "bytes": nbytes,
+            "frac_of_measured_hbm": gbs / peaks["hbm"],
+            "workload": "decode leg's shape; new token at position lengths[b]"}
+
+
 def leg_sdxl_self(dev, peaks, warmup):
     """SDXL self-attention: B 2, 10 heads, S 4096, D 64, head views of [B, S, 640]."""
     from kohaku_tt_b200 import ops
@@ -517,6 +568,7 @@ LEGS = {
     "fwd_bwd_tflops": leg_fwd_bwd,
     "fwd_b8_tflops": leg_fwd_b8,
     "decode_kv_gbs": leg_decode,
+    "decode_step_gbs": leg_decode_step,
     "sdxl_self_tflops": leg_sdxl_self,
     "sdxl_cross_ms": leg_sdxl_cross,
     "varlen_tflops": leg_varlen,

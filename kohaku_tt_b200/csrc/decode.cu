@@ -313,6 +313,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     }
 
     uint32_t qa[D / 16][4];
+    uint32_t k_patch[D / 64], v_patch[D / 64];  // append mode: this lane's share of the new rows
     float o[D / 8][4];
     float m_run[2], l_run[2];
     bool fresh = true;  // start of a pair segment: load Q, reset the running state
@@ -342,8 +343,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                     const int64_t rr = (p.rope_by_position ? cons.len - 1 : cons.b) * p.rope_stride;
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
-                        qa[kk][half] = ok ? rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + t * 2) : 0u;
-                        qa[kk][half + 2] = ok ? rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + 8 + t * 2) : 0u;
+                        // Unconditional loads (a row past the group reads row 0 and is
+                        // zeroed after): all of them are in flight together.
+                        const uint32_t lo = rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + t * 2);
+                        const uint32_t hi = rope_pair<D>(qg, p.rope_cos + rr, p.rope_sin + rr, kk * 16 + 8 + t * 2);
+                        qa[kk][half] = ok ? lo : 0u;
+                        qa[kk][half + 2] = ok ? hi : 0u;
                     }
                 } else {
 #pragma unroll
@@ -351,6 +356,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                     qa[kk][half] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + t * 2) : 0u;
                     qa[kk][half + 2] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + 8 + t * 2) : 0u;
                 }
+                }
+            }
+            if (kAppend) {
+                // The pair's new key (rotated) and value, fetched with the query so that the
+                // warp that later places them does not wait for memory then.
+                const __nv_bfloat16* kn = p.k_new + cons.b * p.kns[0] + cons.hk * p.kns[1];
+                const __nv_bfloat16* vn = p.v_new + cons.b * p.vns[0] + cons.hk * p.vns[1];
+                const int64_t rr = (p.rope_by_position ? cons.len - 1 : cons.b) * p.rope_stride;
+#pragma unroll
+                for (int i = 0; i < D / 64; ++i) {
+                    k_patch[i] = rope_pair<D>(kn, p.rope_cos + rr, p.rope_sin + rr, lane * 2 + i * 64);
+                    v_patch[i] = *reinterpret_cast<const uint32_t*>(vn + lane * 2 + i * 64);
                 }
             }
 #pragma unroll
@@ -371,18 +388,15 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 const int r = pos % kTile;
                 unsigned char* sK = ring + st * kStage;
                 unsigned char* sV = sK + kTile * D * 2;
-                const __nv_bfloat16* kn = p.k_new + cons.b * p.kns[0] + cons.hk * p.kns[1];
-                const __nv_bfloat16* vn = p.v_new + cons.b * p.vns[0] + cons.hk * p.vns[1];
                 __nv_bfloat16* kc = const_cast<__nv_bfloat16*>(p.k) + cons.b * p.ks[0] + cons.hk * p.ks[1] + static_cast<int64_t>(pos) * p.ks[2];
                 __nv_bfloat16* vc = const_cast<__nv_bfloat16*>(p.v) + cons.b * p.vs[0] + cons.hk * p.vs[1] + static_cast<int64_t>(pos) * p.vs[2];
-                const int64_t rr = (p.rope_by_position ? pos : cons.b) * p.rope_stride;
-                for (int c = lane * 2; c < D; c += 64) {
-                    const uint32_t kr = rope_pair<D>(kn, p.rope_cos + rr, p.rope_sin + rr, c);
-                    const uint32_t vr = *reinterpret_cast<const uint32_t*>(vn + c);
-                    *reinterpret_cast<uint32_t*>(sK + swz<D>(r, c)) = kr;
-                    *reinterpret_cast<uint32_t*>(sV + swz<D>(r, c)) = vr;
-                    *reinterpret_cast<uint32_t*>(kc + c) = kr;
-                    *reinterpret_cast<uint32_t*>(vc + c) = vr;
+#pragma unroll
+                for (int i = 0; i < D / 64; ++i) {
+                    const int c = lane * 2 + i * 64;
+                    *reinterpret_cast<uint32_t*>(sK + swz<D>(r, c)) = k_patch[i];
+                    *reinterpret_cast<uint32_t*>(sV + swz<D>(r, c)) = v_patch[i];
+                    *reinterpret_cast<uint32_t*>(kc + c) = k_patch[i];
+                    *reinterpret_cast<uint32_t*>(vc + c) = v_patch[i];
                 }
                 __syncwarp();
             }
