@@ -353,8 +353,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 } else {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    qa[kk][half] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + t * 2) : 0u;
-                    qa[kk][half + 2] = ok ? *reinterpret_cast<const uint32_t*>(qg + kk * 16 + 8 + t * 2) : 0u;
+                    // Unconditional loads (rows past the group read row 0): nothing orders
+                    // them, so they are all in flight together.
+                    const uint32_t lo = *reinterpret_cast<const uint32_t*>(qg + kk * 16 + t * 2);
+                    const uint32_t hi = *reinterpret_cast<const uint32_t*>(qg + kk * 16 + 8 + t * 2);
+                    qa[kk][half] = ok ? lo : 0u;
+                    qa[kk][half + 2] = ok ? hi : 0u;
                 }
                 }
             }
