@@ -24,6 +24,14 @@
 // Ten warps per CTA: warps 0-7 are two groups of 128 threads (one thread per TMEM lane, each
 // group owning 64 of the block's 128 score columns), warp 8 issues MMAs, warp 9 issues TMA.
 // Every mbarrier wait is bounded as in the forward kernel.
+//
+// Overlap: the scores have two buffers in tensor memory wherever 128 columns are left (the dQ
+// kernel at both head dims, the dK/dV kernel at D 64), so the score MMA of item i + 1 runs
+// while the threads still work on item i; dP has one buffer (dS is written over it and read
+// by the last MMA of the item), so dP of item i + 1 is issued behind that MMA and arrives
+// while the threads exponentiate the scores of item i + 1. A thread therefore works in two
+// phases per item: scores -> P (kept in registers, in the dK/dV kernel also stored as the
+// operand of dV), then dP -> dS.
 #include "tc5.cuh"
 
 namespace ktt {
@@ -58,8 +66,9 @@ struct BwdPlan {
     static constexpr int bAFull = 0;
     static constexpr int bBFull = 1;                  // + stage
     static constexpr int bBEmpty = bBFull + kStages;  // + stage
-    static constexpr int bSFull = bBEmpty + kStages;
-    static constexpr int bPFull = bSFull + 1;         // + half
+    static constexpr int bSReady = bBEmpty + kStages; // + score buffer
+    static constexpr int bDPReady = bSReady + 2;
+    static constexpr int bPFull = bDPReady + 1;       // + half
     static constexpr int bDone = bPFull + 2;
     static constexpr int bCount = bDone + 1;
     static_assert(bCount * 8 + 16 <= 256, "barrier area");
@@ -73,7 +82,9 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
         mbar_init(bars + 8 * (P::bBFull + s), 1);
         mbar_init(bars + 8 * (P::bBEmpty + s), 1);
     }
-    mbar_init(bars + 8 * P::bSFull, 1);
+    mbar_init(bars + 8 * (P::bSReady + 0), 1);
+    mbar_init(bars + 8 * (P::bSReady + 1), 1);
+    mbar_init(bars + 8 * P::bDPReady, 1);
     mbar_init(bars + 8 * (P::bPFull + 0), 128);
     mbar_init(bars + 8 * (P::bPFull + 1), 128);
     mbar_init(bars + 8 * P::bDone, 1);
@@ -129,7 +140,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 256 + D;
+    // S^T buffers at columns 0 and (D 64 only) 384; dP^T 128; dV 256; dK 256 + D.
+    constexpr int kSBufs = 256 + 2 * D + 128 <= kTmemCols ? 2 : 1;
+    const uint32_t tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 256 + D;
+    auto tmem_s_of = [&](int it) { return tmem + ((kSBufs == 2 && (it & 1)) ? 384u : 0u); };
 
     auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
         c[tp.dim_of[operand][0]] = row;
@@ -188,25 +202,36 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
             const uint64_t q_mn = smem_desc(sbase + P::kB0, P::kTile, 1024);
             const uint64_t do_mn = smem_desc(sbase + P::kB1, P::kTile, 1024);
             bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bAFull), 0, abort_flag, 500, tp.status));
-            for (int it = 0; ok && it < nitems; ++it) {
+            // S^T = K Q^T of item `it` into its score buffer (the previous reader of that
+            // buffer, dV of an earlier item, was issued before: MMAs run in issue order).
+            auto issue_s = [&](int it) -> bool {
                 const int st = it % P::kStages;
                 const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (it / P::kStages) & 1, abort_flag, 510 + st, tp.status));
-                if (!ok) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (it / P::kStages) & 1, abort_flag, 510 + st, tp.status))) return false;
                 tc_fence_after();
-                // S^T = K Q^T and dP^T = V dO^T. The previous item's P^T / dS^T reads were issued
-                // before these and MMAs run in issue order.
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
-                    tc_mma(tmem_s, k_desc + off, q_desc + soff + off, idesc_s, ks > 0);
+                    tc_mma(tmem_s_of(it), k_desc + off, q_desc + soff + off, idesc_s, ks > 0);
                 }
+                tc_commit(bar(P::bSReady + it % kSBufs));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int it = 0; ok && it < nitems; ++it) {
+                const int st = it % P::kStages;
+                const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
+                // dP^T = V dO^T, behind the previous item's dK (which read dS^T from there).
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
                     tc_mma(tmem_dp, v_desc + off, do_desc + soff + off, idesc_s, ks > 0);
                 }
-                tc_commit(bar(P::bSFull));
+                tc_commit(bar(P::bDPReady));
+                if (kSBufs == 2 && it + 1 < nitems) {
+                    ok = issue_s(it + 1);
+                    if (!ok) break;
+                }
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), it & 1, abort_flag, 520 + g, tp.status));
@@ -218,13 +243,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
                         // B = dO / Q rows as the MN-major operand (16 rows of 128 bytes).
                         const uint32_t boff = soff + (((g * 4 + ks) * 2048) >> 4);
                         const uint32_t acc = (it > 0 || g > 0 || ks > 0) ? 1u : 0u;
-                        tc_mma_ts(tmem_dv, tmem_s + g * 64 + ks * 8, do_mn + boff, idesc_g, acc);
+                        tc_mma_ts(tmem_dv, tmem_s_of(it) + g * 64 + ks * 8, do_mn + boff, idesc_g, acc);
                         tc_mma_ts(tmem_dk, tmem_dp + g * 64 + ks * 8, q_mn + boff, idesc_g, acc);
                     }
                 }
                 if (!ok) break;
                 tc_commit(bar(P::bBEmpty + st));
                 if (it + 1 == nitems) tc_commit(bar(P::bDone));
+                if (kSBufs == 1 && it + 1 < nitems) ok = issue_s(it + 1);
             }
         }
     } else {
@@ -257,41 +283,61 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
             named_barrier_256();
             if (it + 1 < nitems) pre = fetch(it + 1);
             const int q0 = (qstart + it % per_head) * kBN;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), it & 1, abort_flag, 600 + g, tp.status));
+            const uint32_t tmem_s = tmem_s_of(it);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + it % kSBufs), (it / kSBufs) & 1, abort_flag, 600 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
             // Column c of this half is query q0 + g * 64 + c; key kk sees it when
             // kk <= q + shift, i.e. c >= first_col.
             const int first_col = p.causal ? kk - si.shift - q0 - g * 64 : -1;
+            // Phase 1: P^T = 2^(S^T scale - lse), kept in registers and stored (bf16) over the
+            // scores as the operand of dV.
+            float pv[64];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                float s[32], dp[32];
-                tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, s);
-                tmem_ld32(tmem_dp + lane_addr + g * 64 + c * 32, dp);
+                float sc[32];
+                tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, sc);
                 tmem_wait_ld();
-                uint32_t wp[16], wd[16];
                 const float4* l4 = reinterpret_cast<const float4*>(lse2 + g * 64 + c * 32);
-                const float4* d4 = reinterpret_cast<const float4*>(delta + g * 64 + c * 32);
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 lv = l4[e4], dv = d4[e4];
-                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w}, ds_[4] = {dv.x, dv.y, dv.z, dv.w};
-                    float pv[4], dsv[4];
+                    const float4 lv = l4[e4];
+                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int col = c * 32 + e4 * 4 + e;
                         const bool vis = key_ok && col >= first_col;
-                        const float x = vis ? fmaf(s[e4 * 4 + e], p.scale_log2, -ls[e]) : -INFINITY;
-                        pv[e] = fast_exp2(x);
-                        dsv[e] = pv[e] * (dp[e4 * 4 + e] - ds_[e]);
+                        const float x = vis ? fmaf(sc[e4 * 4 + e], p.scale_log2, -ls[e]) : -INFINITY;
+                        pv[col] = fast_exp2(x);
                     }
-                    wp[e4 * 2] = pack_bf16(pv[0], pv[1]);
-                    wp[e4 * 2 + 1] = pack_bf16(pv[2], pv[3]);
-                    wd[e4 * 2] = pack_bf16(dsv[0], dsv[1]);
-                    wd[e4 * 2 + 1] = pack_bf16(dsv[2], dsv[3]);
                 }
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t wp[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) wp[e] = pack_bf16(pv[c * 32 + 2 * e], pv[c * 32 + 2 * e + 1]);
                 // Packed results go over columns this thread has already consumed.
                 tmem_st16(tmem_s + lane_addr + g * 64 + c * 16, wp);
+            }
+            // Phase 2: dS^T = P^T o (dP^T - delta) over dP^T.
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDPReady), it & 1, abort_flag, 620 + g, tp.status));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float dp[32];
+                tmem_ld32(tmem_dp + lane_addr + g * 64 + c * 32, dp);
+                tmem_wait_ld();
+                uint32_t wd[16];
+                const float4* d4 = reinterpret_cast<const float4*>(delta + g * 64 + c * 32);
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 dv = d4[e4];
+                    const int col = c * 32 + e4 * 4;
+                    wd[e4 * 2] = pack_bf16(pv[col] * (dp[e4 * 4] - dv.x), pv[col + 1] * (dp[e4 * 4 + 1] - dv.y));
+                    wd[e4 * 2 + 1] = pack_bf16(pv[col + 2] * (dp[e4 * 4 + 2] - dv.z), pv[col + 3] * (dp[e4 * 4 + 3] - dv.w));
+                }
                 tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
             }
             tmem_wait_st();
@@ -395,7 +441,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    // S buffers at columns 0 and 384, dP 128, dQ 256 (D <= 128 columns).
+    const uint32_t tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    auto tmem_s_of = [&](int j) { return tmem + ((j & 1) ? 384u : 0u); };
 
     auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
         c[tp.dim_of[operand][0]] = row;
@@ -449,23 +497,36 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
             const uint64_t v_desc = smem_desc(sbase + P::kB1, 16, 1024);
             const uint64_t k_mn = smem_desc(sbase + P::kB0, P::kTile, 1024);
             bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bAFull), 0, abort_flag, 800, tp.status));
-            for (int j = 0; ok && j < nblocks; ++j) {
+            // S = Q K^T of block j into its buffer: free since the threads published dS of
+            // block j - 2 (they only read the scores).
+            auto issue_s = [&](int j) -> bool {
                 const int st = j % P::kStages;
                 const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (j / P::kStages) & 1, abort_flag, 810 + st, tp.status));
-                if (!ok) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (j / P::kStages) & 1, abort_flag, 810 + st, tp.status))) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
-                    tc_mma(tmem_s, q_desc + off, k_desc + soff + off, idesc_s, ks > 0);
+                    tc_mma(tmem_s_of(j), q_desc + off, k_desc + soff + off, idesc_s, ks > 0);
                 }
+                tc_commit(bar(P::bSReady + (j & 1)));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; ok && j < nblocks; ++j) {
+                const int st = j % P::kStages;
+                const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
+                // dP = dO V^T, behind the previous block's dQ MMA (which read dS from there).
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = ((ks / 4) * P::kTile + (ks % 4) * 32) >> 4;
                     tc_mma(tmem_dp, do_desc + off, v_desc + soff + off, idesc_s, ks > 0);
                 }
-                tc_commit(bar(P::bSFull));
+                tc_commit(bar(P::bDPReady));
+                if (j + 1 < nblocks) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + g), j & 1, abort_flag, 820 + g, tp.status));
@@ -499,24 +560,36 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
         if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
 
         for (int j = 0; j < nblocks; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSFull), j & 1, abort_flag, 900 + g, tp.status));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + (j & 1)), (j >> 1) & 1, abort_flag, 900 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
             const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
+            // Phase 1: P in registers while dP of this block is still being computed.
+            float pv[64];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                float s[32], dp[32];
-                tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, s);
+                float sc[32];
+                tmem_ld32(tmem_s_of(j) + lane_addr + g * 64 + c * 32, sc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float x = c * 32 + e < limit ? fmaf(sc[e], p.scale_log2, -lse2) : -INFINITY;
+                    pv[c * 32 + e] = fast_exp2(x);
+                }
+            }
+            // Phase 2: dS = P o (dP - delta) over dP.
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDPReady), j & 1, abort_flag, 920 + g, tp.status));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float dp[32];
                 tmem_ld32(tmem_dp + lane_addr + g * 64 + c * 32, dp);
                 tmem_wait_ld();
                 uint32_t wd[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const float x0 = c * 32 + 2 * e < limit ? fmaf(s[2 * e], p.scale_log2, -lse2) : -INFINITY;
-                    const float x1 = c * 32 + 2 * e + 1 < limit ? fmaf(s[2 * e + 1], p.scale_log2, -lse2) : -INFINITY;
-                    const float d0 = fast_exp2(x0) * (dp[2 * e] - delta);
-                    const float d1 = fast_exp2(x1) * (dp[2 * e + 1] - delta);
-                    wd[e] = pack_bf16(d0, d1);
+                    wd[e] = pack_bf16(pv[c * 32 + 2 * e] * (dp[2 * e] - delta), pv[c * 32 + 2 * e + 1] * (dp[2 * e + 1] - delta));
                 }
                 tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
             }

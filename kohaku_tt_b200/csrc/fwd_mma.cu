@@ -69,6 +69,17 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(const AttnParams p) {
         for (int n = 0; n < BN / 8; ++n) {
             s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         }
+        // The tile's mask terms, requested before the score MMAs so that they arrive
+        // meanwhile.
+        float mk[BN / 8][4];
+        const bool has_mask = p.mask_dtype != KTT_B200_MASK_NONE;
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                mk[n][e] = has_mask ? mask_term(p, si, b, h, (e < 2) ? row_a : row_b, k0 + n * 8 + t * 2 + (e & 1)) : 0.f;
+            }
+        }
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
             uint32_t a[4];
@@ -89,7 +100,7 @@ __global__ void __launch_bounds__(kThreads) fwd_mma_kernel(const AttnParams p) {
             for (int e = 0; e < 4; ++e) {
                 const int i = (e < 2) ? row_a : row_b;
                 const int j = k0 + n * 8 + t * 2 + (e & 1);
-                const float x = logit2(p, si, b, h, i, j, s[n][e]);
+                const float x = logit2_with(p, si, i, j, s[n][e], mk[n][e]);
                 s[n][e] = x;
                 mx[e >> 1] = fmaxf(mx[e >> 1], x);
             }

@@ -62,18 +62,28 @@ __device__ __forceinline__ void store_tile(
     }
 }
 
-// Base-2 logit of score s for (query i, key j) of sequence `si`: scale, additive mask,
-// key length and causal rule. -inf marks a pair that does not exist for this row.
+// Additive mask term (base 2) of (query i, key j), 0 without a mask. Indices are clamped
+// into the sequence instead of tested, so the load is unconditional: the loads of a whole
+// tile can then be in flight together (and ahead of the score MMAs) instead of one after
+// the other behind their tests.
+__device__ __forceinline__ float mask_term(const AttnParams& p, const SeqInfo& si, int b, int h, int i, int j) {
+    if (p.mask_dtype == KTT_B200_MASK_NONE) return 0.f;
+    const int ii = max(min(i, si.lq - 1), 0);     // rows past the end only pad the last tile
+    const int jj = max(min(j, si.klen - 1), 0);
+    return mask_value(p, b, h, ii, static_cast<int64_t>(si.k_off) + jj) * kLog2e;
+}
+
+// Base-2 logit of score s for (query i, key j) of sequence `si`: scale, additive mask term
+// (from mask_term), key length and causal rule. -inf marks a pair that does not exist for
+// this row.
+__device__ __forceinline__ float logit2_with(const AttnParams& p, const SeqInfo& si, int i, int j, float s, float term) {
+    const bool dead = j >= si.klen || (p.causal && j > i + si.shift);
+    return dead ? -INFINITY : fmaf(s, p.scale_log2, term);
+}
+
 __device__ __forceinline__ float logit2(
     const AttnParams& p, const SeqInfo& si, int b, int h, int i, int j, float s) {
-    if (j >= si.klen || (p.causal && j > i + si.shift)) return -INFINITY;
-    float x = s * p.scale_log2;
-    if (p.mask_dtype != KTT_B200_MASK_NONE) {
-        // Rows past the end only exist as padding of the last tile; clamp the index.
-        const int ii = i < si.lq ? i : si.lq - 1;
-        x += mask_value(p, b, h, ii, static_cast<int64_t>(si.k_off) + j) * kLog2e;
-    }
-    return x;
+    return logit2_with(p, si, i, j, s, mask_term(p, si, b, h, i, j));
 }
 
 // A-fragment (16 rows x 16 k) of a row-major bf16 smem matrix with leading dim LD.
