@@ -18,7 +18,7 @@ namespace {
 
 constexpr int kThreads = 128;
 
-// delta[b, h, i] = sum_d dO * O, one warp per row.
+// delta[b, h, i] = sum_d dO * O, one warp per row (any width and alignment).
 __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p) {
     const int b = blockIdx.z, h = blockIdx.y;
     const SeqInfo si = seq_info(p, b);
@@ -34,6 +34,35 @@ __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p)
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (lane == 0) p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + row] = acc;
+}
+
+// The same with 16-byte loads: LANES = Dv / 8 lanes per row, 256 / LANES rows per CTA.
+// Needs Dv in {64, 128} and 16-byte aligned rows (the launcher checks).
+template <int DV>
+__global__ void __launch_bounds__(256) bwd_delta_vec_kernel(const AttnParams p) {
+    constexpr int LANES = DV / 8, ROWS = 256 / LANES;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const SeqInfo si = seq_info(p, b);
+    const int row = blockIdx.x * ROWS + threadIdx.x / LANES;
+    const int c = (threadIdx.x % LANES) * 8;
+    float acc = 0.f;
+    if (row < si.lq) {
+        const uint4 o = __ldg(reinterpret_cast<const uint4*>(
+            p.out + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(si.q_off + row) * p.os[2] + c));
+        const uint4 d = __ldg(reinterpret_cast<const uint4*>(
+            p.dout + b * p.dos[0] + h * p.dos[1] + static_cast<int64_t>(si.q_off + row) * p.dos[2] + c));
+        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = __bfloat1622float2(o2[e]), y = __bfloat1622float2(d2[e]);
+            acc = fmaf(x.x, y.x, acc);
+            acc = fmaf(x.y, y.y, acc);
+        }
+    }
+#pragma unroll
+    for (int off = LANES / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (row < si.lq && c == 0) p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + row] = acc;
 }
 
 // dQ: one CTA per (64 query rows, head, batch); streams key/value blocks.
@@ -334,6 +363,19 @@ int launch_dkv(const AttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 int launch_backward_delta(const AttnParams& p, cudaStream_t stream) {
+    const bool aligned =
+        ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.dout)) & 15) == 0 &&
+        ((p.os[0] | p.os[1] | p.os[2] | p.dos[0] | p.dos[1] | p.dos[2]) & 7) == 0;
+    if (aligned && (p.dv == 64 || p.dv == 128)) {
+        const int rows = p.dv == 64 ? 32 : 16;
+        dim3 grid((p.sq + rows - 1) / rows, p.heads, p.batch);
+        if (p.dv == 64) {
+            bwd_delta_vec_kernel<64><<<grid, 256, 0, stream>>>(p);
+        } else {
+            bwd_delta_vec_kernel<128><<<grid, 256, 0, stream>>>(p);
+        }
+        return check_cuda(cudaGetLastError(), "bwd_delta launch");
+    }
     dim3 grid((p.sq + 3) / 4, p.heads, p.batch);
     bwd_delta_kernel<<<grid, kThreads, 0, stream>>>(p);
     return check_cuda(cudaGetLastError(), "bwd_delta launch");

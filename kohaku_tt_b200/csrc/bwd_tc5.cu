@@ -291,8 +291,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
             // kk <= q + shift, i.e. c >= first_col.
             const int first_col = p.causal ? kk - si.shift - q0 - g * 64 : -1;
             // Phase 1: P^T = 2^(S^T scale - lse), kept in registers and stored (bf16) over the
-            // scores as the operand of dV.
-            float pv[64];
+            // scores as the operand of dV. Two values per instruction on the packed fp32 pipe;
+            // a tile every key of which sees every query of this half skips the tests.
+            const bool whole = key_ok && first_col <= 0;
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            float2 pv[32];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 float sc[32];
@@ -302,21 +305,24 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     const float4 lv = l4[e4];
-                    const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int col = c * 32 + e4 * 4 + e;
-                        const bool vis = key_ok && col >= first_col;
-                        const float x = vis ? fmaf(sc[e4 * 4 + e], p.scale_log2, -ls[e]) : -INFINITY;
-                        pv[col] = fast_exp2(x);
+                    float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(-lv.x, -lv.y));
+                    float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(-lv.z, -lv.w));
+                    if (!whole) {
+                        const int col = c * 32 + e4 * 4;
+                        x0.x = (key_ok && col >= first_col) ? x0.x : -INFINITY;
+                        x0.y = (key_ok && col + 1 >= first_col) ? x0.y : -INFINITY;
+                        x1.x = (key_ok && col + 2 >= first_col) ? x1.x : -INFINITY;
+                        x1.y = (key_ok && col + 3 >= first_col) ? x1.y : -INFINITY;
                     }
+                    pv[c * 16 + e4 * 2] = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+                    pv[c * 16 + e4 * 2 + 1] = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
                 }
             }
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t wp[16];
 #pragma unroll
-                for (int e = 0; e < 16; ++e) wp[e] = pack_bf16(pv[c * 32 + 2 * e], pv[c * 32 + 2 * e + 1]);
+                for (int e = 0; e < 16; ++e) wp[e] = pack_bf16(pv[c * 16 + e].x, pv[c * 16 + e].y);
                 // Packed results go over columns this thread has already consumed.
                 tmem_st16(tmem_s + lane_addr + g * 64 + c * 16, wp);
             }
@@ -334,9 +340,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     const float4 dv = d4[e4];
-                    const int col = c * 32 + e4 * 4;
-                    wd[e4 * 2] = pack_bf16(pv[col] * (dp[e4 * 4] - dv.x), pv[col + 1] * (dp[e4 * 4 + 1] - dv.y));
-                    wd[e4 * 2 + 1] = pack_bf16(pv[col + 2] * (dp[e4 * 4 + 2] - dv.z), pv[col + 3] * (dp[e4 * 4 + 3] - dv.w));
+                    const float2 a0 = __fmul2_rn(pv[c * 16 + e4 * 2], __fadd2_rn(make_float2(dp[e4 * 4], dp[e4 * 4 + 1]), make_float2(-dv.x, -dv.y)));
+                    const float2 a1 = __fmul2_rn(pv[c * 16 + e4 * 2 + 1], __fadd2_rn(make_float2(dp[e4 * 4 + 2], dp[e4 * 4 + 3]), make_float2(-dv.z, -dv.w)));
+                    wd[e4 * 2] = pack_bf16(a0.x, a0.y);
+                    wd[e4 * 2 + 1] = pack_bf16(a1.x, a1.y);
                 }
                 tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
             }
@@ -564,17 +571,26 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
             if (!ok) break;
             tc_fence_after();
             const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
-            // Phase 1: P in registers while dP of this block is still being computed.
-            float pv[64];
+            // Phase 1: P in registers while dP of this block is still being computed. Two
+            // values per instruction on the packed fp32 pipe; wholly visible halves skip the
+            // tests.
+            const bool whole = limit >= 64;
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
+            const float2 nd2 = make_float2(-delta, -delta);
+            float2 pv[32];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 float sc[32];
                 tmem_ld32(tmem_s_of(j) + lane_addr + g * 64 + c * 32, sc);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float x = c * 32 + e < limit ? fmaf(sc[e], p.scale_log2, -lse2) : -INFINITY;
-                    pv[c * 32 + e] = fast_exp2(x);
+                for (int e = 0; e < 16; ++e) {
+                    float2 x = __ffma2_rn(make_float2(sc[2 * e], sc[2 * e + 1]), sc2, nl2);
+                    if (!whole) {
+                        x.x = c * 32 + 2 * e < limit ? x.x : -INFINITY;
+                        x.y = c * 32 + 2 * e + 1 < limit ? x.y : -INFINITY;
+                    }
+                    pv[c * 16 + e] = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                 }
             }
             // Phase 2: dS = P o (dP - delta) over dP.
@@ -589,7 +605,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
                 uint32_t wd[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    wd[e] = pack_bf16(pv[c * 32 + 2 * e] * (dp[2 * e] - delta), pv[c * 32 + 2 * e + 1] * (dp[2 * e + 1] - delta));
+                    const float2 a = __fmul2_rn(pv[c * 16 + e], __fadd2_rn(make_float2(dp[2 * e], dp[2 * e + 1]), nd2));
+                    wd[e] = pack_bf16(a.x, a.y);
                 }
                 tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
             }
@@ -662,9 +679,10 @@ __global__ void __launch_bounds__(256) bwd_dkv_reduce_kernel(const AttnParams p)
     const int b = r / p.kv_heads;
     const float* src = p.dkv_partial + (which * planes + (static_cast<int64_t>(b) * p.kv_heads + hk) * p.gsplit) * key_rows * D + row * D + c8 * 8;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < p.gsplit; ++s) {
-        const float4 x = *reinterpret_cast<const float4*>(src + s * key_rows * D);
-        const float4 y = *reinterpret_cast<const float4*>(src + s * key_rows * D + 4);
+#pragma unroll 8
+    for (int s = 0; s < p.gsplit; ++s) {  // fixed order; the unrolled loads are in flight together
+        const float4 x = __ldcs(reinterpret_cast<const float4*>(src + s * key_rows * D));
+        const float4 y = __ldcs(reinterpret_cast<const float4*>(src + s * key_rows * D + 4));
         acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
         acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
     }
