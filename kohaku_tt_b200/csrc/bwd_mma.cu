@@ -18,8 +18,18 @@ namespace {
 
 constexpr int kThreads = 128;
 
+// The first kernel of every backward also clears the tickets of the dK/dV CTAs that share a
+// key block (a grid of the delta kernels always has more threads than there are counters).
+__device__ __forceinline__ void zero_counters(int32_t* counters, int64_t n) {
+    if (!counters) return;
+    const int64_t block = (static_cast<int64_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    const int64_t i = block * blockDim.x + threadIdx.x;
+    if (i < n) counters[i] = 0;
+}
+
 // delta[b, h, i] = sum_d dO * O, one warp per row (any width and alignment).
-__global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p, int64_t ncounters) {
+    zero_counters(p.dkv_counters, ncounters);
     const int b = blockIdx.z, h = blockIdx.y;
     const SeqInfo si = seq_info(p, b);
     const int row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
@@ -39,7 +49,8 @@ __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p)
 // The same with 16-byte loads: LANES = Dv / 8 lanes per row, 256 / LANES rows per CTA.
 // Needs Dv in {64, 128} and 16-byte aligned rows (the launcher checks).
 template <int DV>
-__global__ void __launch_bounds__(256) bwd_delta_vec_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(256) bwd_delta_vec_kernel(const AttnParams p, int64_t ncounters) {
+    zero_counters(p.dkv_counters, ncounters);
     constexpr int LANES = DV / 8, ROWS = 256 / LANES;
     const int b = blockIdx.z, h = blockIdx.y;
     const SeqInfo si = seq_info(p, b);
@@ -363,6 +374,7 @@ int launch_dkv(const AttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 int launch_backward_delta(const AttnParams& p, cudaStream_t stream) {
+    const int64_t ncounters = p.dkv_counters ? backward_counter_count(p, p.gsplit) : 0;
     const bool aligned =
         ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.dout)) & 15) == 0 &&
         ((p.os[0] | p.os[1] | p.os[2] | p.dos[0] | p.dos[1] | p.dos[2]) & 7) == 0;
@@ -370,14 +382,14 @@ int launch_backward_delta(const AttnParams& p, cudaStream_t stream) {
         const int rows = p.dv == 64 ? 32 : 16;
         dim3 grid((p.sq + rows - 1) / rows, p.heads, p.batch);
         if (p.dv == 64) {
-            bwd_delta_vec_kernel<64><<<grid, 256, 0, stream>>>(p);
+            bwd_delta_vec_kernel<64><<<grid, 256, 0, stream>>>(p, ncounters);
         } else {
-            bwd_delta_vec_kernel<128><<<grid, 256, 0, stream>>>(p);
+            bwd_delta_vec_kernel<128><<<grid, 256, 0, stream>>>(p, ncounters);
         }
         return check_cuda(cudaGetLastError(), "bwd_delta launch");
     }
     dim3 grid((p.sq + 3) / 4, p.heads, p.batch);
-    bwd_delta_kernel<<<grid, kThreads, 0, stream>>>(p);
+    bwd_delta_kernel<<<grid, kThreads, 0, stream>>>(p, ncounters);
     return check_cuda(cudaGetLastError(), "bwd_delta launch");
 }
 

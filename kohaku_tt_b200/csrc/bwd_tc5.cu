@@ -95,11 +95,15 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
 
 // ---- dK / dV ----------------------------------------------------------------------------
 
+// Body of one dK/dV CTA; (bx, by, bz) = (kv head * gsplit + part, key block, batch).
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-    const BwdParams tp) {
+__device__ __forceinline__ void dkv_body(
+    const CUtensorMap* pmap_q, const CUtensorMap* pmap_k, const CUtensorMap* pmap_v, const CUtensorMap* pmap_do,
+    const BwdParams& tp, int bx, int by, int bz, int gridDim_y) {
+    const CUtensorMap& map_q = *pmap_q;
+    const CUtensorMap& map_k = *pmap_k;
+    const CUtensorMap& map_v = *pmap_v;
+    const CUtensorMap& map_do = *pmap_do;
     using P = BwdPlan<D>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // blockIdx.x = kv head * gsplit + part: this CTA handles query heads [g0, g0 + group) of
     // the kv head's GQA group.
-    const int hk = blockIdx.x / p.gsplit, part = blockIdx.x % p.gsplit, kb = blockIdx.y, b = blockIdx.z;
+    const int hk = bx / p.gsplit, part = bx % p.gsplit, kb = by, b = bz;
     const SeqInfo si = seq_info(p, b);
     const int k0 = kb * kBM;
     if (k0 >= si.lk) return;
@@ -396,6 +400,50 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
                 }
             }
         }
+        if (p.gsplit > 1 && p.dkv_counters) {
+            // The CTAs sharing this key block take a ticket each once their partial is
+            // stored; the one that draws the last sums the partials in the order of the
+            // parts (deterministic, the same sums whoever is last) and writes bf16.
+            // Every score thread comes here, whatever its waits returned.
+            int* last_flag = reinterpret_cast<int*>(vec);
+            named_barrier_256();  // all partial stores of this CTA are done
+            if (threadIdx.x == 0) {
+                int ticket = 0;
+                if (ok) {
+                    int32_t* counter = p.dkv_counters + (static_cast<int64_t>(b) * p.kv_heads + hk) * gridDim_y + kb;
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(counter) : "memory");
+                }
+                *last_flag = ok && ticket == p.gsplit - 1;
+            }
+            named_barrier_256();
+            if (*last_flag && kk < si.lk) {
+                const float mul = g == 0 ? 1.f : p.scale;
+                __nv_bfloat16* dst = g == 0
+                    ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + static_cast<int64_t>(si.k_off + kk) * p.dvs[2]
+                    : p.dk + b * p.dks[0] + hk * p.dks[1] + static_cast<int64_t>(si.k_off + kk) * p.dks[2];
+                const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
+                const int64_t planes = static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * p.gsplit;
+                const float* src = p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit) * key_rows * D +
+                                   static_cast<int64_t>(si.k_off + kk) * D;
+#pragma unroll 2
+                for (int c8 = 0; c8 < D / 8; ++c8) {
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+                    for (int s_ = 0; s_ < p.gsplit; ++s_) {
+                        const float4 x = __ldcg(reinterpret_cast<const float4*>(src + s_ * key_rows * D + c8 * 8));
+                        const float4 y = __ldcg(reinterpret_cast<const float4*>(src + s_ * key_rows * D + c8 * 8 + 4));
+                        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                    }
+                    uint4 v;
+                    v.x = pack_bf16(acc[0] * mul, acc[1] * mul);
+                    v.y = pack_bf16(acc[2] * mul, acc[3] * mul);
+                    v.z = pack_bf16(acc[4] * mul, acc[5] * mul);
+                    v.w = pack_bf16(acc[6] * mul, acc[7] * mul);
+                    *reinterpret_cast<uint4*>(dst + c8 * 8) = v;
+                }
+            }
+        }
     }
 
     tc_fence_before();
@@ -413,11 +461,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dkv_tc5_kernel(
 
 // ---- dQ ---------------------------------------------------------------------------------
 
+// Body of one dQ CTA; (bx, by, bz) = (head, query block counted from the end, batch).
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
-    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-    const BwdParams tp) {
+__device__ __forceinline__ void dq_body(
+    const CUtensorMap* pmap_q, const CUtensorMap* pmap_k, const CUtensorMap* pmap_v, const CUtensorMap* pmap_do,
+    const BwdParams& tp, int bx, int by, int bz, int ny) {
+    const CUtensorMap& map_q = *pmap_q;
+    const CUtensorMap& map_k = *pmap_k;
+    const CUtensorMap& map_v = *pmap_v;
+    const CUtensorMap& map_do = *pmap_do;
     using P = BwdPlan<D>;
     extern __shared__ __align__(1024) unsigned char smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -432,8 +484,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.x, b = blockIdx.z;
-    const int qb = gridDim.y - 1 - blockIdx.y;
+    const int h = bx, b = bz;
+    const int qb = ny - 1 - by;
     const SeqInfo si = seq_info(p, b);
     const int q0 = qb * kBM;
     if (q0 >= si.lq) return;
@@ -659,6 +711,23 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc5_kernel(
     }
 }
 
+// One launch for both halves of the backward: CTAs [0, n_dkv) are dK/dV CTAs, the rest dQ
+// CTAs (each list longest first). The two are independent of each other, and in one grid the
+// dQ CTAs fill the SMs that the tail of the dK/dV list leaves idle.
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) bwd_tc5_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+    const BwdParams tp, int dkv_x, int dkv_y, int n_dkv, int dq_x, int dq_y) {
+    int id = blockIdx.x;
+    if (id < n_dkv) {
+        dkv_body<D>(&map_q, &map_k, &map_v, &map_do, tp, id % dkv_x, (id / dkv_x) % dkv_y, id / (dkv_x * dkv_y), dkv_y);
+    } else {
+        id -= n_dkv;
+        dq_body<D>(&map_q, &map_k, &map_v, &map_do, tp, id % dq_x, (id / dq_x) % dq_y, id / (dq_x * dq_y), dq_y);
+    }
+}
+
 // Sums the gsplit fp32 partials of every key row in a fixed order and writes bf16 dV and
 // (scaled) dK. One thread per 8 output columns.
 template <int D>
@@ -743,20 +812,22 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     constexpr int smem = P::kBytes;
-    if (int rc = ensure_smem(bwd_dkv_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dkv_tc5)")) return rc;
-    if (int rc = ensure_smem(bwd_dq_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_dq_tc5)")) return rc;
-    dim3 grid_kv(p.kv_heads * p.gsplit, (p.sk + kBM - 1) / kBM, p.batch);
-    bwd_dkv_tc5_kernel<D><<<grid_kv, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
-    if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_tc5 launch")) return rc;
-    if (p.gsplit > 1) {
+    if (int rc = ensure_smem(bwd_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_tc5)")) return rc;
+    const int dkv_x = p.kv_heads * p.gsplit, dkv_y = (p.sk + kBM - 1) / kBM;
+    const int dq_x = p.heads, dq_y = (p.sq + kBM - 1) / kBM;
+    const int64_t n_dkv = static_cast<int64_t>(dkv_x) * dkv_y * p.batch;
+    const int64_t n_all = n_dkv + static_cast<int64_t>(dq_x) * dq_y * p.batch;
+    if (n_all > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: too many tiles");
+    bwd_tc5_kernel<D><<<static_cast<unsigned>(n_all), kThreads, smem, stream>>>(
+        mq, mk, mv, mdo, tp, dkv_x, dkv_y, static_cast<int>(n_dkv), dq_x, dq_y);
+    if (int rc = check_cuda(cudaGetLastError(), "bwd_tc5 launch")) return rc;
+    if (p.gsplit > 1 && !p.dkv_counters) {
         const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
         const int64_t threads = 2 * static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * key_rows * (D / 8);
         bwd_dkv_reduce_kernel<D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p);
         if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_reduce launch")) return rc;
     }
-    dim3 grid_q(p.heads, (p.sq + kBM - 1) / kBM, p.batch);
-    bwd_dq_tc5_kernel<D><<<grid_q, kThreads, smem, stream>>>(mq, mk, mv, mdo, tp);
-    return check_cuda(cudaGetLastError(), "bwd_dq_tc5 launch");
+    return 0;
 }
 
 }  // namespace
@@ -780,11 +851,21 @@ int backward_group_split(const AttnParams& p) {
     return static_cast<int>(want < group ? want : group);
 }
 
-int64_t backward_partial_bytes(const AttnParams& p, int gsplit) {
+int64_t backward_counter_offset(const AttnParams& p, int gsplit) {
     if (gsplit <= 1) return 0;
     const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
     const int64_t nb = p.cu_q ? 1 : p.batch;
-    return 2 * nb * p.kv_heads * gsplit * key_rows * p.d * 4;
+    return (2 * nb * p.kv_heads * gsplit * key_rows * p.d * 4 + 255) / 256 * 256;
+}
+
+int64_t backward_counter_count(const AttnParams& p, int gsplit) {
+    if (gsplit <= 1) return 0;
+    return static_cast<int64_t>(p.batch) * p.kv_heads * ((p.sk + kBM - 1) / kBM);
+}
+
+int64_t backward_partial_bytes(const AttnParams& p, int gsplit) {
+    if (gsplit <= 1) return 0;
+    return backward_counter_offset(p, gsplit) + (backward_counter_count(p, gsplit) * 4 + 255) / 256 * 256;
 }
 
 int launch_backward_tc5(const AttnParams& p, cudaStream_t stream) {

@@ -266,6 +266,9 @@ extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream)
     p.delta_bs = bs;
     p.delta_hs = hs;
     p.dkv_partial = reinterpret_cast<float*>(static_cast<unsigned char*>(a->workspace) + delta_bytes);
+    p.dkv_counters = p.gsplit > 1
+        ? reinterpret_cast<int32_t*>(static_cast<unsigned char*>(a->workspace) + delta_bytes + backward_counter_offset(p, p.gsplit))
+        : nullptr;
     note_call(2);
     const char* why = nullptr;
     const bool tc5 = backward_tc5_takes(p, &why);

@@ -45,6 +45,7 @@ struct AttnParams {
     // `gsplit` CTAs per key block, which leave fp32 partial dV / dK here for a reduction.
     int gsplit;
     float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows][d]
+    int32_t* dkv_counters;  // [batch][kv_heads][key blocks] tickets of the CTAs sharing a key block; zeroed by the delta kernel
 };
 
 // One sequence's extent inside the operands.
@@ -189,6 +190,9 @@ bool backward_tc5_takes(const AttnParams& p, const char** why);
 // (1 when there are enough key blocks to fill the GPU), and the fp32 bytes that needs.
 int backward_group_split(const AttnParams& p);
 int64_t backward_partial_bytes(const AttnParams& p, int gsplit);
+// Offset of the ticket counters inside that region (they follow the partial sums).
+int64_t backward_counter_offset(const AttnParams& p, int gsplit);
+int64_t backward_counter_count(const AttnParams& p, int gsplit);
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).

@@ -28,12 +28,6 @@
 
 #include <type_traits>
 
-#ifndef KTT_X_TROW
-#define KTT_X_TROW 0
-#endif
-#ifndef KTT_X_BATCH
-#define KTT_X_BATCH 1
-#endif
 namespace ktt {
 using namespace tc5;
 namespace {
@@ -401,7 +395,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                 }
                 continue;
             }
-            const bool tracer = first_item && row == KTT_X_TROW && blockIdx.x == 0;
+            const bool tracer = first_item && row == 0 && blockIdx.x == 0;
             float m_ref = -INFINITY;  // this half's reference maximum (base-2 logits), moved lazily
             float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // running sums, 4 lanes
             // Keys this row may see: [0, row_limit).
@@ -493,26 +487,6 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                     // different pipes at the same time.
                     auto exps = [&](auto poly_first) {
                         constexpr bool kFirst = decltype(poly_first)::value;
-#if KTT_X_BATCH
-                        // Written stage by stage over all pairs, so that dependent
-                        // instructions are far apart in the instruction stream.
-                        float2 x[CG / 2];
-#pragma unroll
-                        for (int e = 0; e < CG / 2; ++e) x[e] = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
-#pragma unroll
-                        for (int e = 0; e < CG / 2; ++e) {
-                            if (kFirst ? (e < P::kPolyPairs) : (e >= CG / 2 - P::kPolyPairs)) {
-                                x[e] = exp2_poly2(x[e]);
-                            } else {
-                                x[e].x = fast_exp2(x[e].x);
-                                x[e].y = fast_exp2(x[e].y);
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < CG / 2; ++e) wv[e] = pack_bf16(x[e].x, x[e].y);
-#pragma unroll
-                        for (int e = 0; e < CG / 2; ++e) l2[e & 1] = __fadd2_rn(l2[e & 1], x[e]);
-#else
 #pragma unroll
                         for (int e = 0; e < CG / 2; ++e) {
                             const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, nm2);
@@ -526,7 +500,6 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                             l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
                             wv[e] = pack_bf16(pr.x, pr.y);
                         }
-#endif
                     };
                     if (g & 1) {
                         exps(std::true_type{});

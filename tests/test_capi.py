@@ -80,8 +80,9 @@ def test_backward_workspace_size(built_lib):
     delta = 2 * 4 * 128 * 4
     assert built_lib.ktt_b200_sdpa_backward_workspace(ctypes.byref(_args(sq=100, kv_heads=4))) == delta
     # ... plus, for grouped heads on a small grid, fp32 dV / dK partials of each part the
-    # group is split into: 2 tensors x batch 2 x kv heads 2 x 2 parts x 64 keys x 64 dims.
-    assert built_lib.ktt_b200_sdpa_backward_workspace(ctypes.byref(_args(sq=100))) == delta + 2 * 2 * 2 * 2 * 64 * 64 * 4
+    # group is split into (2 tensors x batch 2 x kv heads 2 x 2 parts x 64 keys x 64 dims)
+    # and one ticket counter per (batch, kv head, key block), padded to 256 bytes.
+    assert built_lib.ktt_b200_sdpa_backward_workspace(ctypes.byref(_args(sq=100))) == delta + 2 * 2 * 2 * 2 * 64 * 64 * 4 + 256
 
 
 def test_decode_refusals(built_lib):
