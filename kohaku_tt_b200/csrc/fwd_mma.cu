@@ -19,7 +19,7 @@ constexpr int kBM = 64;       // query rows per CTA (16 per warp)
 constexpr int kThreads = 128;
 
 template <int DP, int BN>
-__global__ void __launch_bounds__(kThreads) fwd_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kThreads, DP <= 64 ? 4 : 1) fwd_mma_kernel(const AttnParams p) {
     constexpr int LD = DP + kPad;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);

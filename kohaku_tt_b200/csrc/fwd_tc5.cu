@@ -186,26 +186,22 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
     // it only arrives at the start-up barrier, the others wait there for it and for the
     // tensor-memory allocation.
     if (warp == P::kMmaWarp + 1) {
+      // One barrier per lane: lane i initialises barrier i with its arrival count.
+      static_assert(P::bCount <= 32, "one barrier per lane");
+      if (lane < P::bCount) {
+        uint32_t count = 1;
+        if (lane == P::bOFree) count = kSoftmaxThreads;
+        if (lane >= P::bPFull && lane < P::bPVDone) count = 128;
+        mbar_init(bar(lane), count);
+      }
       if (lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-        mbar_init(bar(P::bQFull), 1);
-        mbar_init(bar(P::bQFree), 1);
-        mbar_init(bar(P::bOFree), kSoftmaxThreads);
-        for (int s = 0; s < P::kStages; ++s) {
-            mbar_init(bar(P::bKVFull + s), 1);
-            mbar_init(bar(P::bKVEmpty + s), 1);
-        }
-        for (int i = 0; i < 2; ++i) mbar_init(bar(P::bSFull + i), 1);
-        for (int i = 0; i < 2 * G; ++i) {
-            mbar_init(bar(P::bPFull + i), 128);
-            mbar_init(bar(P::bPVDone + i), 1);
-        }
         *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        fence_async_smem();
       }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      fence_async_smem();
       __syncwarp();
       asm volatile("barrier.cta.arrive 0, %0;" ::"n"(P::kThreads) : "memory");
     } else {
