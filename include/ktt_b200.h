@@ -239,7 +239,8 @@ typedef struct ktt_b200_decode_append_args {
 KTT_B200_API int ktt_b200_decode_append(const ktt_b200_decode_append_args* args, void* stream);
 
 /* Merge of two partial attention results over disjoint key sets (ring attention steps):
- * out / lse [rows] are updated in place with (out2, lse2). fp32 lse, bf16 or fp32 out.
+ * out / lse [rows] are updated in place with (out2, lse2). fp32 lse; out_is_f32 = 0: out and
+ * out2 bf16, 1: both fp32, 2: fp32 out (an accumulator) with bf16 out2 (a kernel's output).
  * rows = B*H*S rows of dv values, row stride dv. No reference counterpart: the reference
  * has no sequence-parallel attention. */
 KTT_B200_API int ktt_b200_merge_partials(

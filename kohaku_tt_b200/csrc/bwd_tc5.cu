@@ -833,6 +833,10 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 bool backward_tc5_takes(const AttnParams& p, const char** why) {
+    if (p.mask_dtype != KTT_B200_MASK_NONE) {
+        *why = "masked gradients run on the warp-MMA kernels";
+        return false;
+    }
     if (!forward_tc5_takes(p, why)) return false;
     if (!aligned16(p.dout, p.dos) || !aligned16(p.dq, p.dqs) || !aligned16(p.dk, p.dks) || !aligned16(p.dv_out, p.dvs)) {
         *why = "dout, dq, dk and dv must be 16-byte aligned with strides that are multiples of 8";

@@ -133,15 +133,52 @@ __global__ void merge_partials_kernel(
         wb = eb / (ea + eb);
         l = m + __logf(ea + eb);
     }
-    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-        const int64_t i = row * dv + c;
-        if (f32) {
-            float* o = static_cast<float*>(out);
-            o[i] = o[i] * wa + static_cast<const float*>(out2)[i] * wb;
-        } else {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-            o[i] = __float2bfloat16(
-                __bfloat162float(o[i]) * wa + __bfloat162float(static_cast<const __nv_bfloat16*>(out2)[i]) * wb);
+    // f32: 0 = both bf16, 1 = both fp32, 2 = fp32 accumulator with a bf16 second operand.
+    if ((dv & 3) == 0) {
+        for (int c = threadIdx.x * 4; c < dv; c += blockDim.x * 4) {
+            const int64_t i = row * dv + c;
+            float x[4], y[4];
+            if (f32) {
+                const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(out) + i);
+                x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+            } else {
+                const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(out) + i);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+                x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+            }
+            if (f32 == 1) {
+                const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(out2) + i);
+                y[0] = t.x; y[1] = t.y; y[2] = t.z; y[3] = t.w;
+            } else {
+                const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(out2) + i);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+                y[0] = lo.x; y[1] = lo.y; y[2] = hi.x; y[3] = hi.y;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] = x[e] * wa + y[e] * wb;
+            if (f32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(out) + i) = make_float4(x[0], x[1], x[2], x[3]);
+            } else {
+                uint2 t;
+                t.x = pack_bf16(x[0], x[1]);
+                t.y = pack_bf16(x[2], x[3]);
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + i) = t;
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+            const int64_t i = row * dv + c;
+            const float y = f32 == 1 ? static_cast<const float*>(out2)[i]
+                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(out2)[i]);
+            if (f32) {
+                float* o = static_cast<float*>(out);
+                o[i] = o[i] * wa + y * wb;
+            } else {
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+                o[i] = __float2bfloat16(__bfloat162float(o[i]) * wa + y * wb);
+            }
         }
     }
     __syncwarp();  // one warp per row: every lane has read lse[row]
@@ -289,6 +326,7 @@ extern "C" int ktt_b200_merge_partials(
     if (!out || !lse || !out2 || !lse2 || rows < 0 || dv < 1) {
         return fail(KTT_B200_ERR_BAD_ARGUMENT, "merge_partials: null pointer or bad size");
     }
+    if (out_is_f32 < 0 || out_is_f32 > 2) return fail(KTT_B200_ERR_BAD_ARGUMENT, "merge_partials: out_is_f32 must be 0, 1 or 2");
     if (rows == 0) return 0;
     dim3 block(32, 8);
     const int64_t blocks = (rows + 7) / 8;

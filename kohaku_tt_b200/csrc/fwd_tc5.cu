@@ -148,7 +148,7 @@ __device__ __forceinline__ int work_of(int round, int cta, int ctas) {
 
 // ---- the kernel ------------------------------------------------------------------------
 
-template <int D, bool kTrace>
+template <int D, bool kTrace, bool kMask>
 __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const Tc5Params tp) {
@@ -409,16 +409,37 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                 const int limit = row_limit - j * kBN - g * CG;  // this group's columns [0, limit) are visible
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 const bool whole = limit >= CG;
+                // With a mask that is one row per (batch, head) the base-2 terms of this
+                // group's 64 keys are fetched first (indices clamped, loads unconditional)
+                // and are in flight with the scores.
+                float mk[kMask ? CG : 1];
+                if constexpr (kMask) {
+                    const int col0 = j * kBN + g * CG;
+#pragma unroll
+                    for (int e = 0; e < CG; ++e) {
+                        const int jj = max(min(col0 + e, si.klen - 1), 0);
+                        mk[e] = mask_value(p, k.b, k.h, 0, static_cast<int64_t>(si.k_off) + jj) * kLog2e;
+                    }
+                }
                 // The second half of the columns is still on its way while the maximum of
                 // the first is taken.
                 tmem_ld32(s_addr, s);
                 tmem_wait_ld();
                 tmem_ld32(s_addr + 32, s + 32);
+                if constexpr (kMask) {
+                    // Logits in place: s * scale + mask term; the maximum is taken over those.
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) s[e] = fmaf(s[e], p.scale_log2, mk[e]);
+                }
                 if (whole) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
                 }
                 tmem_wait_ld();
+                if constexpr (kMask) {
+#pragma unroll
+                    for (int e = 32; e < CG; ++e) s[e] = fmaf(s[e], p.scale_log2, mk[e]);
+                }
                 if (whole) {
 #pragma unroll
                     for (int e = 32; e < CG; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
@@ -429,7 +450,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                         mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
                     }
                 }
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * (kMask ? 1.f : p.scale_log2);
                 zone<kTrace>(tp, tracer && g == 0, j, 1);
 
                 // Lazy rescale: move the reference only when this block exceeds it by 2^8.
@@ -475,7 +496,8 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                 // P = 2^(s * scale - m) as packed bf16 pairs, two values per instruction where
                 // the packed fp32 pipe allows.
                 uint32_t wv[CG / 2];
-                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_use, -m_use);
+                const float sc1 = kMask ? 1.f : p.scale_log2;  // masked logits are already scaled
+                const float2 sc2 = make_float2(sc1, sc1), nm2 = make_float2(-m_use, -m_use);
                 if (whole) {
                     // Every column visible. kPolyPairs of this thread's pairs take the polynomial
                     // on the FMA pipe, the rest MUFU; odd groups start with the polynomial and
@@ -781,8 +803,9 @@ bool forward_tc5_takes(const AttnParams& p, const char** why) {
         *why = "head dim must be 64 or 128 with D == Dv";
         return false;
     }
-    if (p.mask_dtype != KTT_B200_MASK_NONE) {
-        *why = "masks run on the warp-MMA kernel";
+    if (p.mask_dtype != KTT_B200_MASK_NONE && (p.ms[2] != 0 || p.causal)) {
+        // A mask that is one row per (batch, head) (key padding) is applied in the kernel.
+        *why = "masks that differ between query rows run on the warp-MMA kernel";
         return false;
     }
     if (p.key_lengths) {
@@ -845,7 +868,9 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     constexpr int smem = P::kBytes;
-    auto kernel = tp.trace ? fwd_tc5_kernel<D, true> : fwd_tc5_kernel<D, false>;
+    const bool masked = p.mask_dtype != KTT_B200_MASK_NONE;
+    auto kernel = masked ? (tp.trace ? fwd_tc5_kernel<D, true, true> : fwd_tc5_kernel<D, false, true>)
+                         : (tp.trace ? fwd_tc5_kernel<D, true, false> : fwd_tc5_kernel<D, false, false>);
     if (int rc = ensure_smem(kernel, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
     tp.q_tiles = (p.sq + kBM - 1) / kBM;
     const int64_t work = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;

@@ -461,11 +461,13 @@ def decode_append(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin, by_posit
 
 def merge_partials(out, lse, out2, lse2):
     """In place: (out, lse) <- merge with (out2, lse2), two attention results of the
-    same queries over disjoint key sets. out [..., Dv] bf16 or fp32, lse [...] fp32."""
+    same queries over disjoint key sets. out [..., Dv] bf16 or fp32 (out2 the same, or bf16
+    into an fp32 out), lse [...] fp32."""
     _require_cuda(out, lse, out2, lse2)
     if not (out.is_contiguous() and out2.is_contiguous() and lse.is_contiguous() and lse2.is_contiguous()):
         raise ValueError("kohaku_tt_b200.merge_partials: operands must be contiguous")
-    if out.shape != out2.shape or lse.shape != lse2.shape or out.dtype != out2.dtype:
+    mixed = out.dtype == torch.float32 and out2.dtype == torch.bfloat16
+    if out.shape != out2.shape or lse.shape != lse2.shape or (out.dtype != out2.dtype and not mixed):
         raise ValueError("kohaku_tt_b200.merge_partials: operand shapes or dtypes differ")
     dv = out.shape[-1]
     rows = out.numel() // dv
@@ -477,6 +479,6 @@ def merge_partials(out, lse, out2, lse2):
         _lib.check(
             _lib.lib().ktt_b200_merge_partials(
                 out.data_ptr(), lse.data_ptr(), out2.data_ptr(), lse2.data_ptr(),
-                rows, dv, int(out.dtype == torch.float32), _stream(out.device)),
+                rows, dv, 2 if mixed else int(out.dtype == torch.float32), _stream(out.device)),
             "merge_partials")
     return out, lse

@@ -109,7 +109,7 @@ def _default_attend_backward(dout, q, k, v, out, lse, causal, scale):
 def _default_merge(acc_out, acc_lse, out, lse):
     from . import ops
 
-    ops.merge_partials(acc_out, acc_lse, out.float().contiguous(), lse.contiguous())
+    ops.merge_partials(acc_out, acc_lse, out.contiguous(), lse.contiguous())
 
 
 def _exchange(send, recv_like, group, rank, world):

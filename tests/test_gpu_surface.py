@@ -122,10 +122,21 @@ def test_merge_partials_equals_attention_over_the_union(cuda):
     qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
     o1, l1 = ops.sdpa_forward(qc, kc[:, :, :130].contiguous(), vc[:, :, :130].contiguous())
     o2, l2 = ops.sdpa_forward(qc, kc[:, :, 130:].contiguous(), vc[:, :, 130:].contiguous())
-    acc = o1.float().contiguous()
-    ops.merge_partials(acc, l1, o2.float().contiguous(), l2)
+    # Three operand forms give the same merge: fp32 with fp32, fp32 with the kernel's bf16
+    # output, bf16 with bf16; odd widths take the scalar path.
+    acc, la = o1.float().contiguous(), l1.clone()
+    ops.merge_partials(acc, la, o2.float().contiguous(), l2)
     assert rel(acc, ao.ruler_dense(q, k, v)) <= FWD_BOUND
-    assert (l1.cpu().double() - ao.ruler_lse(q, k, v)).abs().max() <= 3e-2
+    assert (la.cpu().double() - ao.ruler_lse(q, k, v)).abs().max() <= 3e-2
+    mixed, lm = o1.float().contiguous(), l1.clone()
+    ops.merge_partials(mixed, lm, o2, l2)
+    assert torch.equal(mixed, acc) and torch.equal(lm, la)
+    both, lb = o1.clone(), l1.clone()
+    ops.merge_partials(both, lb, o2, l2)
+    assert rel(both, acc) <= 4e-3 and torch.equal(lb, la)
+    narrow, ln = o1[..., :63].float().contiguous(), l1.clone()
+    ops.merge_partials(narrow, ln, o2[..., :63].contiguous(), l2)
+    assert torch.equal(narrow, acc[..., :63])
 
 
 # ---- torch.compile (tests/hardware/ops/test_sdpa_kernel.py:215-224) ----------------------
