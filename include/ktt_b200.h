@@ -111,7 +111,10 @@ typedef struct ktt_b200_attn_args {
     int64_t dq_strides[3];
     int64_t dk_strides[3];
     int64_t dv_strides[3];
-    /* Backward workspace of ktt_b200_sdpa_backward_workspace() bytes, 256-byte aligned. */
+    /* Backward: workspace of ktt_b200_sdpa_backward_workspace() bytes, 256-byte aligned.
+     * Forward (optional): 4 zero-filled bytes; with them the persistent tcgen05 kernel's CTAs
+     * draw their work items from a counter there instead of a fixed deal, which evens out
+     * uneven packed batches and SMs shared with other kernels. The kernel leaves the count. */
     void* workspace;
     int64_t workspace_bytes;
 } ktt_b200_attn_args;

@@ -253,6 +253,7 @@ extern "C" int ktt_b200_sdpa_forward(const ktt_b200_attn_args* a, void* stream) 
     }
     AttnParams p;
     to_params(a, p);
+    p.fwd_work_counter = (a->workspace && a->workspace_bytes >= 4) ? static_cast<int32_t*>(a->workspace) : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const char* why = nullptr;
     const bool tc5 = forward_tc5_takes(p, &why);

@@ -45,6 +45,7 @@ struct AttnParams {
     // `gsplit` CTAs per key block, which leave fp32 partial dV / dK here for a reduction.
     int gsplit;
     float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows][d]
+    int32_t* fwd_work_counter;  // forward, optional: one zeroed int32 the persistent CTAs draw their items from
     int32_t* dkv_counters;  // [batch][kv_heads][key blocks] tickets of the CTAs sharing a key block; zeroed by the delta kernel
 };
 

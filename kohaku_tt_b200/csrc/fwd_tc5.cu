@@ -69,8 +69,11 @@ struct Plan {
     static constexpr int kK = kQ + kSub * kTile;
     static constexpr int kV = kK + kStages * kSub * kTile;
     static constexpr int kML = kV + kStages * kSub * kTile;   // float2 [groups][128]: (m, l)
-    static constexpr int kBars = kML + kGroups * 128 * 8;
-    static constexpr int kBytes = kBars + 512;
+    static constexpr int kMaskRow = kML + kGroups * 128 * 8;   // float [groups][128 / groups]: a block's mask terms
+    static constexpr int kBars = kMaskRow + 128 * 4;
+    static constexpr int kBarBytes = 384;
+    static constexpr int kBytes = kBars + kBarBytes;
+    static_assert(kBytes <= 232448, "shared memory per CTA");
     // barrier indices (8 bytes each)
     static constexpr int bQFull = 0;
     static constexpr int bQFree = 1;
@@ -84,9 +87,12 @@ struct Plan {
     // every one of them within one phase of its waiters.
     static constexpr int bPFull = bSFull + 2;              // + 2 * group + buffer
     static constexpr int bPVDone = bPFull + 2 * kGroups;   // + 2 * group + buffer
-    static constexpr int bCount = bPVDone + 2 * kGroups;
-    static constexpr int kBarBytes = 512;
-    static_assert(bCount * 8 + 16 + 4 * kMmaWarp <= kBarBytes, "barrier area");
+    static constexpr int bMaskRow = bPVDone + 2 * kGroups; // + 2 * group + (0: readers done, 1: row written)
+    static constexpr int bWorkFull = bMaskRow + 2 * kGroups;   // + slot: an item index was published
+    static constexpr int bWorkFree = bWorkFull + 2;            // + slot: every reader has taken it
+    static constexpr int bEpilogue = bWorkFree + 2;            // all softmax threads have stored (m, l) of the item
+    static constexpr int bCount = bEpilogue + 1;
+    static_assert(bCount * 8 + 16 + 4 * kMmaWarp + 16 <= kBarBytes, "barrier area");
     static_assert(256 + kGroups * D <= 512, "tensor memory columns");
 };
 
@@ -98,6 +104,7 @@ struct Tc5Params {
     long long* trace;   // optional clock stamps (see ktt_b200_set_trace), else null
     int q_tiles;        // query tiles per batch entry (ceil(sq / 128))
     int work;           // work items = heads * batch * q_tiles
+    int* work_counter;  // optional (zero before the launch): the CTAs draw their items from it
 };
 
 // Profiling zones (the counterpart of the reference's FLASH_PROFILE device zones,
@@ -177,6 +184,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
     // Per item and softmax warp: "every wait of mine succeeded" (two items alternate).
     volatile int* ok_flags = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8 + 16);
+    volatile int* work_slot = ok_flags + P::kMmaWarp;       // [2] item indices drawn from the counter (after one flag per softmax warp)
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,7 +199,9 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
       if (lane < P::bCount) {
         uint32_t count = 1;
         if (lane == P::bOFree) count = kSoftmaxThreads;
-        if (lane >= P::bPFull && lane < P::bPVDone) count = 128;
+        if ((lane >= P::bPFull && lane < P::bPVDone) || (lane >= P::bMaskRow && lane < P::bWorkFull)) count = 128;
+        if (lane >= P::bWorkFree) count = kSoftmaxThreads + 1;   // every softmax thread and the MMA warp's lane 0
+        if (lane == P::bEpilogue) count = kSoftmaxThreads;
         mbar_init(bar(lane), count);
       }
       if (lane == 0) {
@@ -226,13 +236,62 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
     // stages, S buffers and barrier parities are functions of those.
     int blocks_done = 0;
 
+    // The n-th item of this CTA: -1 = no more, -2 = nothing at this position. Without a
+    // counter every role computes the same snake order by itself. With one, the producer
+    // warp draws indices (the list is sorted by decreasing work, so a CTA that started late
+    // or shares its SM simply draws fewer) and hands each to the other roles through a
+    // two-slot queue in shared memory.
+    const bool dynamic = tp.work_counter != nullptr;
+    auto static_item = [&](int n) -> int {
+        if (static_cast<int64_t>(n) * gridDim.x >= tp.work) return -1;
+        const int w = work_of(n, blockIdx.x, gridDim.x);
+        return w < tp.work ? w : -2;
+    };
+    auto draw_item = [&](int n, bool& ok) -> int {   // producer warp, converged
+        if (!dynamic) return static_item(n);
+        const int slot = n & 1;
+        if (n >= 2) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bWorkFree + slot), ((n >> 1) - 1) & 1, abort_flag, 120 + slot, tp.status));
+            if (!ok) return -1;
+        }
+        // Positions past the end of their sequence (packed batches have many) are skipped
+        // here, so the other roles never see them.
+        int w;
+        while (true) {
+            w = 0;
+            if (lane == 0) w = atomicAdd(tp.work_counter, 1);
+            w = __shfl_sync(0xffffffffu, w, 0);
+            if (w >= tp.work) {
+                w = -1;
+                break;
+            }
+            if (decode_work(tp, w).valid) break;
+        }
+        if (lane == 0) {
+            work_slot[slot] = w;
+            __threadfence_block();
+            mbar_arrive(bar(P::bWorkFull + slot));
+        }
+        return w;
+    };
+    auto take_item = [&](int n, bool& ok, bool arrives) -> int {   // the other roles
+        if (!dynamic) return static_item(n);
+        const int slot = n & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bWorkFull + slot), (n >> 1) & 1, abort_flag, 130 + slot, tp.status));
+        if (!ok) return -1;
+        const int w = work_slot[slot];
+        if (arrives) mbar_arrive(bar(P::bWorkFree + slot));
+        return w;
+    };
+
     if (warp == P::kMmaWarp + 1) {
         // ---------------- producer (whole warp, converged) ----------------
         int item = 0, blk = 0;
         bool ok = true;
-        for (int round = 0; ok && round * gridDim.x < tp.work; ++round) {
-            const int w = work_of(round, blockIdx.x, gridDim.x);
-            if (w >= tp.work) continue;
+        for (int n = 0; ok; ++n) {
+            const int w = draw_item(n, ok);
+            if (w == -1) break;
+            if (w == -2) continue;
             const Work k = decode_work(tp, w);
             if (k.nblocks == 0) continue;
             const int hk = k.h / group_size;
@@ -297,9 +356,10 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
             tc_commit(bar(P::bSFull + (gb & 1)));
             if (last) tc_commit(bar(P::bQFree));
         };
-        for (int round = 0; ok && round * gridDim.x < tp.work; ++round) {
-            const int w = work_of(round, blockIdx.x, gridDim.x);
-            if (w >= tp.work) continue;
+        for (int n = 0; ok; ++n) {
+            const int w = take_item(n, ok, lane == 0);
+            if (w == -1) break;
+            if (w == -2) continue;
             const Work k = decode_work(tp, w);
             if (k.nblocks == 0) continue;
             const bool mtracer = first_item && lane == 0 && blockIdx.x == 0;
@@ -373,9 +433,10 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
         bool first_item = true;
         float2* ml_base = reinterpret_cast<float2*>(smem + P::kML);
 
-        for (int round = 0; round * gridDim.x < tp.work; ++round) {
-            const int w = work_of(round, blockIdx.x, gridDim.x);
-            if (w >= tp.work) continue;
+        for (int n = 0; ok; ++n) {
+            const int w = take_item(n, ok, true);
+            if (w == -1) break;
+            if (w == -2) continue;
             const Work k = decode_work(tp, w);
             if (!k.valid) continue;
             const SeqInfo& si = k.si;
@@ -414,11 +475,26 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                 // and are in flight with the scores.
                 float mk[kMask ? CG : 1];
                 if constexpr (kMask) {
-                    const int col0 = j * kBN + g * CG;
+                    // One thread per column fetches the term (index clamped into the
+                    // sequence), the group shares the row through shared memory. The first
+                    // barrier keeps the previous block's readers ahead of the writers.
+                    // (Group-wide mbarriers with bounded waits, not bar.sync: a warp that has
+                    // given up elsewhere must not leave the others waiting here for ever.)
+                    float* mrow = reinterpret_cast<float*>(smem + P::kMaskRow) + g * CG;
+                    mbar_arrive(bar(P::bMaskRow + 2 * g));
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMaskRow + 2 * g), gb & 1, abort_flag, 340 + g, tp.status));
+                    if (!ok) break;
+                    if (row < CG) {
+                        const int jj = max(min(j * kBN + g * CG + row, si.klen - 1), 0);
+                        mrow[row] = mask_value(p, k.b, k.h, 0, static_cast<int64_t>(si.k_off) + jj) * kLog2e;
+                    }
+                    mbar_arrive(bar(P::bMaskRow + 2 * g + 1));
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMaskRow + 2 * g + 1), gb & 1, abort_flag, 350 + g, tp.status));
+                    if (!ok) break;
 #pragma unroll
-                    for (int e = 0; e < CG; ++e) {
-                        const int jj = max(min(col0 + e, si.klen - 1), 0);
-                        mk[e] = mask_value(p, k.b, k.h, 0, static_cast<int64_t>(si.k_off) + jj) * kLog2e;
+                    for (int e4 = 0; e4 < CG / 4; ++e4) {
+                        const float4 t = reinterpret_cast<const float4*>(mrow)[e4];
+                        mk[e4 * 4] = t.x; mk[e4 * 4 + 1] = t.y; mk[e4 * 4 + 2] = t.z; mk[e4 * 4 + 3] = t.w;
                     }
                 }
                 // The second half of the columns is still on its way while the maximum of
@@ -559,7 +635,14 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
             const float l_mine = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
             ml[g * 128 + row] = make_float2(m_ref, l_mine);
             if (lane == 0) ok_flags[warp] = ok;
-            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            // A bounded wait like every other in this kernel: no warp can be left behind at a
+            // plain barrier by one that has given up.
+            __syncwarp();
+            mbar_arrive(bar(P::bEpilogue));
+            {
+                const bool all_here = __all_sync(0xffffffffu, mbar_wait(bar(P::bEpilogue), item & 1, abort_flag, 360 + g, tp.status));
+                ok = ok && all_here;
+            }
             zone<kTrace>(tp, tracer && g == 0, 60, 1);
             // All softmax warps take the same decision, so none is left alone at this barrier.
 #pragma unroll
@@ -876,6 +959,7 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
     const int64_t work = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;
     if (work > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: too many query tiles");
     tp.work = static_cast<int>(work);
+    tp.work_counter = p.fwd_work_counter;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int grid = tp.work < sms ? tp.work : sms;  // persistent: one CTA per SM

@@ -112,6 +112,45 @@ def _mask_operand(args, mask, b, h, sq, sk):
     return m  # keeps the expanded view (and its storage) alive over the call
 
 
+# The persistent forward kernel can draw its work items from a counter instead of a fixed
+# deal (a zeroed int32 passed as the call's workspace: one small fill per call). On an
+# undisturbed GPU the fixed deal measured as fast or faster (headline batch 8, packed
+# 65,536 tokens), so it is off unless asked for: `dynamic_work(True)` for code whose
+# attention kernels share the SMs with other kernels.
+_DYNAMIC = {"on": False, "min_items_per_sm": 6}
+
+
+def dynamic_work(on=True, min_items_per_sm=6):
+    """Switches counter-driven work distribution of the tcgen05 forward on or off for work
+    lists of at least `min_items_per_sm` items per SM. Returns the previous setting."""
+    old = dict(_DYNAMIC)
+    _DYNAMIC["on"], _DYNAMIC["min_items_per_sm"] = bool(on), int(min_items_per_sm)
+    return old
+
+
+def _work_counter(args, device, dynamic=None):
+    """Sets args.workspace to a zeroed counter when dynamic work distribution applies
+    (`dynamic`: this call's own choice, None = the module setting)."""
+    if not (_DYNAMIC["on"] if dynamic is None else dynamic):
+        return None
+    tiles = (args.sq + 127) // 128
+    if args.heads * args.batch * tiles < _DYNAMIC["min_items_per_sm"] * _sm_count(device):
+        return None
+    counter = torch.zeros((4,), dtype=torch.int32, device=device)
+    args.workspace, args.workspace_bytes = counter.data_ptr(), 16
+    return counter
+
+
+_SMS = {}
+
+
+def _sm_count(device):
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _SMS:
+        _SMS[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _SMS[index]
+
+
 def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -154,7 +193,7 @@ def _dense_args(q, k, v, mask, key_lengths, causal, scale, kernel):
 
 
 def sdpa_forward(q, k, v, mask=None, key_lengths=None, causal=False, scale=None,
-                 need_lse=True, kernel="auto", lse_rows=None):
+                 need_lse=True, kernel="auto", lse_rows=None, dynamic=None):
     """Dense attention forward: out [B, H, Sq, Dv] bf16 and, with need_lse, the row
     log-sum-exp [B, H, lse_rows or Sq] fp32 (natural log).
 
@@ -176,7 +215,9 @@ def sdpa_forward(q, k, v, mask=None, key_lengths=None, causal=False, scale=None,
             lse = torch.empty((q.shape[0], q.shape[1], rows), dtype=torch.float32, device=q.device)
             args.lse = lse.data_ptr()
             _set3(args.lse_strides, (lse.stride(0), lse.stride(1), 1))
+        counter = _work_counter(args, q.device, dynamic)
         _lib.check(_lib.lib().ktt_b200_sdpa_forward(ctypes.byref(args), _stream(q.device)), "sdpa_forward")
+        del counter
     del keep
     return out, lse
 
@@ -277,7 +318,9 @@ def varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal=False, scale=None,
         args.out, args.lse = out.data_ptr(), lse.data_ptr()
         _set3(args.out_strides, _ths_strides(out))
         _set3(args.lse_strides, (0, lse.stride(0), 1))
+        counter = _work_counter(args, q.device)
         _lib.check(_lib.lib().ktt_b200_sdpa_forward(ctypes.byref(args), _stream(q.device)), "varlen_forward")
+        del counter
     del keep
     return out, lse
 

@@ -97,7 +97,9 @@ def zigzag_merge(shards, dim):
 def _default_attend(q, k, v, causal, scale):
     from . import ops
 
-    return ops.sdpa_forward(q, k, v, causal=causal, scale=scale, need_lse=True)
+    # The K/V exchange runs beside these kernels and takes SMs from them for a while: the
+    # CTAs draw their work from a counter, so the ones that start late just draw less.
+    return ops.sdpa_forward(q, k, v, causal=causal, scale=scale, need_lse=True, dynamic=True)
 
 
 def _default_attend_backward(dout, q, k, v, out, lse, causal, scale):
@@ -166,8 +168,9 @@ def ring_forward(q, k, v, group=None, scale=None, attend=None, merge=None):
             nxt, pending = _exchange(block, block, group, rank, world)
         kb, vb = block
         for half, key_halves, causal in _visible_parts(world, rank, step):
-            ks = kb if key_halves == (0, 1) else kb[:, :, :c].contiguous()
-            vs = vb if key_halves == (0, 1) else vb[:, :, :c].contiguous()
+            # The early chunk is a view: the kernels read it through its strides.
+            ks = kb if key_halves == (0, 1) else kb[:, :, :c]
+            vs = vb if key_halves == (0, 1) else vb[:, :, :c]
             out, lse = attend(qh[half], ks, vs, causal, scale)
             if acc_out[half] is None:
                 acc_out[half], acc_lse[half] = out.float().contiguous(), lse.contiguous().clone()
@@ -204,8 +207,8 @@ def ring_backward(dout, q, k, v, out, lse, group=None, scale=None, attend_backwa
             nxt_kv, pending_kv = _exchange(block[:2], block[:2], group, rank, world)
         for half, key_halves, causal in _visible_parts(world, rank, step):
             both = key_halves == (0, 1)
-            ks = kb if both else kb[:, :, :c].contiguous()
-            vs = vb if both else vb[:, :, :c].contiguous()
+            ks = kb if both else kb[:, :, :c]
+            vs = vb if both else vb[:, :, :c]
             gq, gk, gv = attend_backward(doh[half], qh[half], ks, vs, oh[half], lh[half], causal, scale)
             dq[half] += gq.float()
             span = slice(None) if both else slice(0, c)

@@ -136,7 +136,7 @@ def test_merge_partials_equals_attention_over_the_union(cuda):
     assert rel(both, acc) <= 4e-3 and torch.equal(lb, la)
     narrow, ln = o1[..., :63].float().contiguous(), l1.clone()
     ops.merge_partials(narrow, ln, o2[..., :63].contiguous(), l2)
-    assert torch.equal(narrow, acc[..., :63])
+    assert torch.allclose(narrow, acc[..., :63], rtol=1e-5, atol=1e-6)  # scalar path: same formula, other rounding of the multiply-adds
 
 
 # ---- torch.compile (tests/hardware/ops/test_sdpa_kernel.py:215-224) ----------------------
