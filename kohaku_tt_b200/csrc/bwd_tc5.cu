@@ -85,8 +85,8 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
     mbar_init(bars + 8 * (P::bSReady + 0), 1);
     mbar_init(bars + 8 * (P::bSReady + 1), 1);
     mbar_init(bars + 8 * P::bDPReady, 1);
-    mbar_init(bars + 8 * (P::bPFull + 0), 128);
-    mbar_init(bars + 8 * (P::bPFull + 1), 128);
+    mbar_init(bars + 8 * (P::bPFull + 0), 4);   // one arrival per warp of the group
+    mbar_init(bars + 8 * (P::bPFull + 1), 4);
     mbar_init(bars + 8 * P::bDone, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -353,7 +353,7 @@ __device__ __forceinline__ void dkv_body(
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(P::bPFull + g));
+            mbar_arrive_warp(bar(P::bPFull + g));
         }
 
         // Epilogue: group 0 writes dV, group 1 writes dK (scaled); rows past the end of the
@@ -664,7 +664,7 @@ __device__ __forceinline__ void dq_body(
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(P::bPFull + g));
+            mbar_arrive_warp(bar(P::bPFull + g));
         }
 
         if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 910, tp.status));

@@ -198,10 +198,11 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
       static_assert(P::bCount <= 32, "one barrier per lane");
       if (lane < P::bCount) {
         uint32_t count = 1;
-        if (lane == P::bOFree) count = kSoftmaxThreads;
-        if ((lane >= P::bPFull && lane < P::bPVDone) || (lane >= P::bMaskRow && lane < P::bWorkFull)) count = 128;
-        if (lane >= P::bWorkFree) count = kSoftmaxThreads + 1;   // every softmax thread and the MMA warp's lane 0
-        if (lane == P::bEpilogue) count = kSoftmaxThreads;
+        // Softmax threads arrive once per warp (mbar_arrive_warp).
+        if (lane == P::bOFree) count = 4 * G;
+        if ((lane >= P::bPFull && lane < P::bPVDone) || (lane >= P::bMaskRow && lane < P::bWorkFull)) count = 4;
+        if (lane >= P::bWorkFree) count = 4 * G + 1;   // every softmax warp and the MMA warp
+        if (lane == P::bEpilogue) count = 4 * G;
         mbar_init(bar(lane), count);
       }
       if (lane == 0) {
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
         ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bWorkFull + slot), (n >> 1) & 1, abort_flag, 130 + slot, tp.status));
         if (!ok) return -1;
         const int w = work_slot[slot];
-        if (arrives) mbar_arrive(bar(P::bWorkFree + slot));
+        if (arrives) mbar_arrive_warp(bar(P::bWorkFree + slot));
         return w;
     };
 
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
             if (last) tc_commit(bar(P::bQFree));
         };
         for (int n = 0; ok; ++n) {
-            const int w = take_item(n, ok, lane == 0);
+            const int w = take_item(n, ok, true);
             if (w == -1) break;
             if (w == -2) continue;
             const Work k = decode_work(tp, w);
@@ -481,14 +482,14 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                     // (Group-wide mbarriers with bounded waits, not bar.sync: a warp that has
                     // given up elsewhere must not leave the others waiting here for ever.)
                     float* mrow = reinterpret_cast<float*>(smem + P::kMaskRow) + g * CG;
-                    mbar_arrive(bar(P::bMaskRow + 2 * g));
+                    mbar_arrive_warp(bar(P::bMaskRow + 2 * g));
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMaskRow + 2 * g), gb & 1, abort_flag, 340 + g, tp.status));
                     if (!ok) break;
                     if (row < CG) {
                         const int jj = max(min(j * kBN + g * CG + row, si.klen - 1), 0);
                         mrow[row] = mask_value(p, k.b, k.h, 0, static_cast<int64_t>(si.k_off) + jj) * kLog2e;
                     }
-                    mbar_arrive(bar(P::bMaskRow + 2 * g + 1));
+                    mbar_arrive_warp(bar(P::bMaskRow + 2 * g + 1));
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMaskRow + 2 * g + 1), gb & 1, abort_flag, 350 + g, tp.status));
                     if (!ok) break;
 #pragma unroll
@@ -619,7 +620,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                 }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(bar(P::bPFull + 2 * g + (gb & 1)));
+                mbar_arrive_warp(bar(P::bPFull + 2 * g + (gb & 1)));
                 zone<kTrace>(tp, tracer && g == 0, j, 3);
             }
 
@@ -637,8 +638,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
             if (lane == 0) ok_flags[warp] = ok;
             // A bounded wait like every other in this kernel: no warp can be left behind at a
             // plain barrier by one that has given up.
-            __syncwarp();
-            mbar_arrive(bar(P::bEpilogue));
+            mbar_arrive_warp(bar(P::bEpilogue));
             {
                 const bool all_here = __all_sync(0xffffffffu, mbar_wait(bar(P::bEpilogue), item & 1, abort_flag, 360 + g, tp.status));
                 ok = ok && all_here;
@@ -695,7 +695,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                     if (c + 1 == kOut / kChunk) {
                         // The accumulators are in registers: the next item's P V may overwrite them.
                         tc_fence_before();
-                        mbar_arrive(bar(P::bOFree));
+                        mbar_arrive_warp(bar(P::bOFree));
                     }
                     if (real) {
 #pragma unroll
