@@ -134,7 +134,7 @@ def _work_counter(args, device, dynamic=None):
     if not (_DYNAMIC["on"] if dynamic is None else dynamic):
         return None
     tiles = (args.sq + 127) // 128
-    if args.heads * args.batch * tiles < _DYNAMIC["min_items_per_sm"] * _sm_count(device):
+    if dynamic is None and args.heads * args.batch * tiles < _DYNAMIC["min_items_per_sm"] * _sm_count(device):
         return None
     counter = torch.zeros((4,), dtype=torch.int32, device=device)
     args.workspace, args.workspace_bytes = counter.data_ptr(), 16

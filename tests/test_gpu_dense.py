@@ -305,3 +305,23 @@ def test_long_causal_work_lists(cuda, b, h, hk, s, d):
         scores = scores.masked_fill(torch.arange(s)[None, :] > rows[:, None], float("-inf"))
         ruler = torch.softmax(scores, dim=-1) @ vv
         assert rel(out[bi, hi, rows.to(cuda)].cpu(), ruler) <= FWD_BOUND
+
+
+def test_counter_driven_work_gives_the_same_bits(cuda):
+    """Which CTA draws an item does not touch the item's arithmetic: with the work counter
+    the tcgen05 forward returns exactly what the fixed deal returns (dense, packed-style
+    ragged sizes, masked row)."""
+    old = ops.dynamic_work(False)
+    try:
+        for b, h, hk, s, d, causal in [(2, 8, 2, 1000, 64, True), (1, 16, 16, 2048, 128, True), (3, 4, 4, 300, 64, False)]:
+            q, k, v = (t.to(cuda) for t in qkv(b, h, hk, s, s, d, b + h + s + d))
+            want, want_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash")
+            ops.dynamic_work(True, 0)
+            got, got_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash")
+            ops.dynamic_work(False)
+            again, _ = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash", dynamic=True)
+            assert torch.equal(got, want) and torch.equal(got_lse, want_lse) and torch.equal(again, want)
+        torch.cuda.synchronize()
+        _lib.device_status()
+    finally:
+        ops.dynamic_work(old["on"], old["min_items_per_sm"])
