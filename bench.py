@@ -339,7 +339,12 @@ def run_ours(args):
     achieved = flops / (per_launch_ms * 1e-3) / 1e12
     line["roofline"] = {
         "bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
-        "frac": achieved / peaks["bf16"], "traffic": None,
+        "frac": achieved / peaks["bf16"],
+        # DRAM bytes of one launch from the ncu capture summarised in
+        # profiles/fwd_tc5_headline.md (dram__bytes_read.sum + dram__bytes_write.sum; the
+        # output stays in L2 at this size). Algorithmic bytes are 8.4 MB: no re-reads.
+        "traffic": 4775936 if kernel == "tcgen05" and c["batch"] == 1 else None,
+        "traffic_unit": "bytes per launch (ncu)",
         "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / 2250.0,
     }
 
