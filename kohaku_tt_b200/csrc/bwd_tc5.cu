@@ -833,8 +833,8 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
 }  // namespace
 
 bool backward_tc5_takes(const AttnParams& p, const char** why) {
-    if (p.mask_dtype != KTT_B200_MASK_NONE) {
-        *why = "masked gradients run on the warp-MMA kernels";
+    if (p.mask_dtype != KTT_B200_MASK_NONE || p.key_lengths) {
+        *why = "gradients with a mask or key lengths run on the warp-MMA kernels";
         return false;
     }
     if (!forward_tc5_takes(p, why)) return false;

@@ -388,6 +388,25 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bOFree), (item - 1) & 1, abort_flag, 250, tp.status));
                     if (!ok) break;
                 }
+                if (p.key_lengths) {
+                    // Rows of the cache past this sequence's length may hold anything, and
+                    // P = 0 times an infinity would still poison the output: the value rows
+                    // past the length are blanked in the tile before P V reads it (TMA itself
+                    // only blanks rows past the end of the tensor). The key rows need nothing:
+                    // their scores are replaced before use.
+                    const int valid = k.si.klen - j * kBN;
+                    if (valid < kBN) {
+                        const int rows = kBN - (valid > 0 ? valid : 0), first = kBN - rows;
+                        unsigned char* vt = smem + P::kV + st * P::kSub * P::kTile;
+                        for (int idx = lane; idx < P::kSub * rows * 8; idx += 32) {
+                            const int sub = idx / (rows * 8), rem = idx % (rows * 8);
+                            *reinterpret_cast<uint4*>(vt + sub * P::kTile + (first + rem / 8) * 128 + (rem % 8) * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                    }
+                }
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bPFull + 2 * g + (gb & 1)), (gb >> 1) & 1, abort_flag, 240 + g, tp.status));
@@ -889,11 +908,6 @@ bool forward_tc5_takes(const AttnParams& p, const char** why) {
     if (p.mask_dtype != KTT_B200_MASK_NONE && (p.ms[2] != 0 || p.causal)) {
         // A mask that is one row per (batch, head) (key padding) is applied in the kernel.
         *why = "masks that differ between query rows run on the warp-MMA kernel";
-        return false;
-    }
-    if (p.key_lengths) {
-        // TMA cannot blank the rows past a length, and they may hold anything.
-        *why = "key lengths run on the warp-MMA and decode kernels";
         return false;
     }
     for (int i = 0; i < 3; ++i) {

@@ -48,6 +48,17 @@ def test_garbage_past_the_lengths_changes_nothing(cuda):
     a = ktt.sdpa(q.to(cuda), k.to(cuda), v.to(cuda), key_lengths=ln)
     b_ = ktt.sdpa(q.to(cuda), k2.to(cuda), v2.to(cuda), key_lengths=ln)
     assert torch.equal(a, b_)
+    # Each forward kernel by name (the tcgen05 one blanks the value rows past a length in
+    # its tile; NaN there as well), causal and not, against the float64 ruler too.
+    v3 = v2.clone()
+    for i, n in enumerate(lengths):
+        v3[i, :, n:] = float("nan")
+    for kernel in ("mma", "flash"):
+        for causal in (False, True):
+            clean, lse = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), key_lengths=ln, causal=causal, kernel=kernel)
+            dirty, lse2 = ops.sdpa_forward(q.to(cuda), k2.to(cuda), v3.to(cuda), key_lengths=ln, causal=causal, kernel=kernel)
+            assert torch.equal(clean, dirty) and torch.equal(lse, lse2), (kernel, causal)
+            assert rel(clean, ao.ruler_lengths(q, k, v, lengths, causal=causal)) <= FWD_BOUND, (kernel, causal)
     # Decode shape (one query row): the split-K kernel.
     q1 = q[:, :, :1].contiguous()
     a = ktt.sdpa(q1.to(cuda), k.to(cuda), v.to(cuda), key_lengths=ln)
@@ -62,6 +73,10 @@ def test_full_lengths_equal_plain_attention(cuda):
     plain, _ = ops.sdpa_forward(qc, kc, vc, kernel="mma")
     full, _ = ops.sdpa_forward(qc, kc, vc, key_lengths=torch.full((2,), 197, dtype=torch.int32, device=cuda),
                                kernel="mma")
+    assert torch.equal(plain, full)
+    plain, _ = ops.sdpa_forward(qc, kc, vc, kernel="flash")
+    full, _ = ops.sdpa_forward(qc, kc, vc, key_lengths=torch.full((2,), 197, dtype=torch.int32, device=cuda),
+                               kernel="flash")
     assert torch.equal(plain, full)
 
 
