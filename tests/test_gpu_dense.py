@@ -325,3 +325,20 @@ def test_counter_driven_work_gives_the_same_bits(cuda):
         _lib.device_status()
     finally:
         ops.dynamic_work(old["on"], old["min_items_per_sm"])
+
+
+# The reference's bench shapes (src/kohakutt/bench/ops.py:189-209): [3, 24, s, 128], plain and
+# causal, judged by their statistics against float64 (on two (batch, head) pairs: the full
+# float64 score matrices of the longest shape would not fit).
+@pytest.mark.parametrize("s", [279, 1043, 1615, 4379])
+@pytest.mark.parametrize("causal", [False, True])
+def test_bench_shapes_statistics(cuda, s, causal):
+    import kohaku_tt_b200 as ktt
+
+    q, k, v = qkv(3, 24, 24, s, s, 128, 0)
+    out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal)
+    for bi, hi in ((0, 0), (2, 23)):
+        sl = (slice(bi, bi + 1), slice(hi, hi + 1))
+        ruler = ao.ruler_dense(q[sl], k[sl], v[sl], causal=causal)
+        st = ktt.diff_stats(out[sl], ruler)
+        assert st["nonfinite"] == 0 and st["rel_median"] <= 1e-2 and st["abs_max"] <= 2e-2, (s, causal, st)

@@ -201,3 +201,43 @@ def test_key_lengths_op_compiles_whole(cuda):
     for got_g, want_g in ((a.grad, a2.grad), (b.grad, b2.grad), (c.grad, c2.grad)):
         assert torch.equal(got_g, want_g)
     assert torch.count_nonzero(b.grad[1, :, 40:]) == 0
+
+
+def test_sdxl_style_block_compiled_equals_eager(cuda):
+    """tests/hardware/compile/test_pitched_attention_graphs.py:12-27: B 2, T 128, TK 77, 20
+    heads of 64: linears, head views, self- and cross-attention with a key-padding mask."""
+    torch.manual_seed(0)
+    b, t, tk, h, d = 2, 128, 77, 20, 64
+    c = h * d
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv = torch.nn.Linear(c, 3 * c, bias=False)
+            self.q2 = torch.nn.Linear(c, c, bias=False)
+            self.kv2 = torch.nn.Linear(c, 2 * c, bias=False)
+            self.out = torch.nn.Linear(c, c, bias=False)
+
+        def forward(self, x, ctx, keep):
+            q, k, v = (z.view(b, t, h, d).transpose(1, 2) for z in self.qkv(x).chunk(3, dim=-1))
+            y = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, t, c)
+            q = self.q2(y).view(b, t, h, d).transpose(1, 2)
+            k, v = (z.view(b, tk, h, d).transpose(1, 2) for z in self.kv2(ctx).chunk(2, dim=-1))
+            y = F.scaled_dot_product_attention(q, k, v, attn_mask=keep).transpose(1, 2).reshape(b, t, c)
+            return self.out(y)
+
+    block = Block()
+    x, ctx = torch.randn(b, t, c) / 8, torch.randn(b, tk, c) / 8
+    keep = torch.ones(b, 1, 1, tk, dtype=torch.bool)
+    keep[..., 57:] = False
+    want = block.double()(x.double(), ctx.double(), keep)   # float64 on the CPU
+    block = block.float().to(cuda).to(torch.bfloat16)
+    xc, cc, kc = x.to(cuda).to(torch.bfloat16), ctx.to(cuda).to(torch.bfloat16), keep.to(cuda)
+    before = ktt.counters()
+    with torch.no_grad():
+        eager = block(xc, cc, kc)
+        d1 = _delta(before)
+        compiled = torch.compile(block, backend="aot_eager", fullgraph=True)(xc, cc, kc)
+    assert d1.get("attention_flash", 0) + d1.get("attention_mma", 0) == 2   # both attentions ran here
+    assert torch.equal(compiled, eager)
+    assert rel(eager, want) <= 3e-2   # bf16 linears around the attention
