@@ -1,20 +1,25 @@
 // Prefill / training forward on the Blackwell tensor path: TMA tile loads, tcgen05.mma
 // with accumulators in tensor memory, online softmax in registers.
 //
-// One CTA owns 128 query rows of one (batch, head) and streams 128-key blocks:
+// A persistent CTA per SM walks a list of work items; one item = 128 query rows of one
+// (batch, head) against its visible 128-key blocks. Ten warps:
 //
-//   warp 5 (producer)  TMA loads of Q once and of K/V blocks into a ring of stages
-//                      (128-byte swizzled tiles, mbarrier transaction counts)
-//   warp 4 (MMA)       one elected lane issues  S = Q K^T  (128 x 128 x D, both operands
-//                      K-major from shared memory, fp32 accumulator in TMEM columns
-//                      [0, 128)) and  O += P V  (128 x D x 128, P K-major and V MN-major
-//                      from shared memory, accumulator in TMEM columns [128, 128 + D))
-//   warps 0-3 (softmax) thread r owns query row r: reads its S row from TMEM, frees the
-//                      S buffer at once (the next S = Q K^T overlaps this block's
-//                      softmax), keeps the running maximum and sum in fp32, writes
-//                      P (bf16) into a double-buffered swizzled tile, and rescales O in
-//                      TMEM only when the maximum moved by more than 2^8 (the lazy
-//                      rescale of ktt_flash/compute.cpp, flash.md "row reference")
+//   warp 9 (producer)  TMA loads of an item's Q and of its K/V blocks into a ring of stages
+//                      (128-byte swizzled tiles, mbarrier transaction counts); with a work
+//                      counter it also draws the items and hands them to the other roles
+//   warp 8 (MMA)       issues  S = Q K^T  (128 x 128 x D, both operands K-major from shared
+//                      memory) into one of two score buffers in tensor memory, two blocks
+//                      ahead of the softmax, and  O_g += P_g V  per softmax group, with P
+//                      read from tensor memory and V as the MN-major operand
+//   warps 0-3, 4-7     two softmax groups: thread r of group g owns query row r and keys
+//                      [64 g, 64 g + 64) of every block, with its own running maximum, sum
+//                      and accumulator O_g; it writes P (bf16) over the score columns it
+//                      read and rescales O_g only when the maximum moved by more than 2^8
+//                      (the lazy rescale of ktt_flash/compute.cpp, flash.md "row
+//                      reference"); the groups are merged once per item
+//
+// Optional per call: a mask of one row per (batch, head), per-batch key lengths, profiling
+// stamps (template flags and runtime checks below).
 //
 // Same arithmetic contract as the reference's flash forward (ktt_flash/compute.cpp:
 // 193-491): base-2 softmax with fp32 statistics, P rounded to bf16 before P V, fp32
