@@ -1,5 +1,5 @@
-// Backward on the Blackwell tensor path: a dK/dV kernel and a dQ kernel, both TMA loads +
-// tcgen05.mma with accumulators in tensor memory.
+// Backward on the Blackwell tensor path: dK/dV CTAs and dQ CTAs (two bodies, one launch: see
+// bwd_tc5_kernel), both TMA loads + tcgen05.mma with accumulators in tensor memory.
 //
 // Same split and same arithmetic as the reference's backward (ktt_flash/program.cpp:
 // 1587-2006; bw_dq_compute.cpp, bw_dkv_compute.cpp): every gradient has one owner, nothing
