@@ -111,7 +111,14 @@ def _empty(device, dtype=torch.int64):
 
 
 def _rng(device):
-    return torch.zeros((2,), dtype=torch.uint64, device=device), torch.empty((), dtype=torch.uint64, device=device)
+    # Dropout is refused, so nobody reads the generator state: left unwritten (a zero fill
+    # would be one more kernel launch on every attention call).
+    return torch.empty((2,), dtype=torch.uint64, device=device), torch.empty((), dtype=torch.uint64, device=device)
+
+
+def _seed_pair(device):
+    """Philox seed and offset outputs of the fused ops: unwritten, for the same reason."""
+    return torch.empty((), dtype=torch.int64, device=device), torch.empty((), dtype=torch.int64, device=device)
 
 
 # ---- aten::_scaled_dot_product_flash_attention (+ backward) ------------------------
@@ -145,8 +152,8 @@ def _efficient_forward(q, k, v, attn_bias, compute_log_sumexp, dropout_p=0.0, is
         lse = torch.empty((q.size(0), q.size(1), 0), dtype=torch.float32, device=q.device)
     if cast:
         out = out.to(torch.float32)
-    seed = torch.zeros((), dtype=torch.int64, device=q.device)
-    return out, lse, seed, seed.clone()
+    seed, offset = _seed_pair(q.device)
+    return out, lse, seed, offset
 
 
 def _bias_gradient(grad_out, q, k, v, attn_bias, logsumexp, is_causal, scale):
@@ -192,9 +199,9 @@ def _cudnn_forward(q, k, v, attn_bias, compute_log_sumexp, dropout_p=0.0, is_cau
                                 need_lse=True)
     if cast:
         out = out.to(torch.float32)
-    seed = torch.zeros((), dtype=torch.int64, device=q.device)
+    seed, offset = _seed_pair(q.device)
     return (out, lse.unsqueeze(-1), _empty(q.device), _empty(q.device), q.size(2), k.size(2),
-            seed, seed.clone(), _empty(q.device, q.dtype))
+            seed, offset, _empty(q.device, q.dtype))
 
 
 def _cudnn_backward(grad_out, q, k, v, out, logsumexp, philox_seed, philox_offset, attn_bias,
@@ -217,8 +224,8 @@ def _overrideable_forward(q, k, v, attn_bias=None, dropout_p=0.0, is_causal=Fals
     out, lse = ops.sdpa_forward(qb, kb, vb, mask=attn_bias, causal=is_causal, scale=scale)
     if cast:
         out = out.to(torch.float32)
-    seed = torch.zeros((), dtype=torch.int64, device=q.device)
-    return (out, lse, _empty(q.device), _empty(q.device), q.size(2), k.size(2), seed, seed.clone(),
+    seed, offset = _seed_pair(q.device)
+    return (out, lse, _empty(q.device), _empty(q.device), q.size(2), k.size(2), seed, offset,
             _empty(q.device, q.dtype))
 
 
@@ -300,7 +307,7 @@ def _varlen_forward(query, key, value, cu_seq_q, cu_seq_k, max_q, max_k, is_caus
     cu_q = cu_seq_q.to(device=query.device, dtype=torch.int32).contiguous()
     cu_k = cu_q if cu_seq_k is None else cu_seq_k.to(device=query.device, dtype=torch.int32).contiguous()
     out, lse = ops.varlen_forward(query, key, value, cu_q, cu_k, max_q, max_k, causal=causal, scale=scale)
-    return out, lse, torch.zeros((2,), dtype=torch.uint64, device=query.device)
+    return out, lse, torch.empty((2,), dtype=torch.uint64, device=query.device)
 
 
 def _varlen_backward(grad_out, query, key, value, out, lse, cu_seq_q, cu_seq_k, max_q, max_k,
