@@ -6,13 +6,16 @@ Headline workload (N = 1): the Qwen2.5-0.5B-shaped GQA causal prefill forward, B
 14 query heads / 2 KV heads, D = 64, S = 2048, bf16, seeded N(0, 1) inputs. A step is one
 forward pass over one batch; with N > 1 every rank runs its own batch (weak scaling, no
 collective). The line also carries the forward+backward, decode, SDXL and packed
-workloads as `extra` legs, a roofline for the dominant kernel, and the reference's CPU
-path (PyTorch CPU SDPA on the same bf16 tensors) timed on this box's host cores.
+workloads as `extra` legs (each with its error statistics against the float64 ruler), a
+roofline for the dominant kernel, and the reference's CPU path (PyTorch CPU SDPA on the
+same bf16 tensors) timed on this box's host cores. With N > 1 the `extra` legs are the
+sharded forms of the decode, SDXL and packed workloads and the ring-attention leg.
 
 `--impl reference` times only that CPU path, on the headline workload.
 """
 
 import argparse
+import hashlib
 import json
 import math
 import os
@@ -29,11 +32,26 @@ if ROOT not in sys.path:
 
 HEADLINE = dict(batch=1, heads=14, kv_heads=2, seq=2048, head_dim=64)
 L2_BYTES = 126 * 1024 * 1024
+MIN_REGION_MS = 50.0   # the timed graph is replayed until the region is at least this long
 
 
 def causal_forward_flops(b, h, s, d):
     """2 FLOP per multiply-add, QK^T + PV over visible (query, key) pairs only."""
     return 4.0 * b * h * d * (s * (s + 1) / 2)
+
+
+def seeded(shapes, seed, device=None, dtype=torch.bfloat16):
+    """Seeded N(0, 1) tensors drawn in order on CPU in fp32, then cast (the reference's
+    tests draw their inputs this way, tests/hardware/ops/test_flash.py:48-53)."""
+    g = torch.Generator().manual_seed(seed)
+    out = tuple(torch.randn(*s, generator=g).to(dtype) for s in shapes)
+    return out if device is None else tuple(t.to(device) for t in out)
+
+
+def device_randn(shape, seed, device):
+    """Large operands are drawn on the device (seeded)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
 
 
 def measured_peaks():
@@ -44,6 +62,28 @@ def measured_peaks():
         return {"bf16": m["bf16_tflops"], "bf16_sustained": m["bf16_tflops_sustained"],
                 "hbm": m["hbm_gbs"], "source": "measured"}
     return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+def git_blob_hash(path):
+    """The git blob id of a file's current contents (what `git hash-object` prints)."""
+    with open(path, "rb") as f:
+        data = f.read()
+    return hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest()
+
+
+def captured_traffic():
+    """DRAM bytes per launch of the headline kernel from the tracked ncu figures beside the
+    profile summary; None when the kernel source has changed since the capture."""
+    path = os.path.join(ROOT, "profiles", "fwd_row_headline.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+        src = os.path.join(ROOT, "kohaku_tt_b200", "csrc", rec["kernel_source"])
+        if git_blob_hash(src) != rec["kernel_source_blob"]:
+            return None
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"])
+    except (OSError, KeyError, ValueError):
+        return None
 
 
 class ClockSampler:
@@ -110,19 +150,30 @@ def dist_env():
     return rank, world, local
 
 
-def headline_inputs(seed, device=None, pin=False):
-    from oracle import attention_oracle as ao
+def host_threads(world, local):
+    """Gives this rank its own share of the host cores (torchrun sets OMP_NUM_THREADS=1 and
+    leaves every rank on all CPUs) and returns the thread count."""
+    try:
+        cpus = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        cpus = list(range(os.cpu_count() or 1))
+    share = max(1, len(cpus) // max(world, 1))
+    if world > 1:
+        mine = cpus[local * share:(local + 1) * share] or cpus
+        try:
+            os.sched_setaffinity(0, mine)
+        except (AttributeError, OSError):
+            pass
+    torch.set_num_threads(share)
+    return share
 
+
+def headline_inputs(seed, device=None):
     c = HEADLINE
-    q, k, v = ao.make_inputs(
+    return seeded(
         [(c["batch"], c["heads"], c["seq"], c["head_dim"]),
          (c["batch"], c["kv_heads"], c["seq"], c["head_dim"]),
-         (c["batch"], c["kv_heads"], c["seq"], c["head_dim"])], seed)
-    if device is not None:
-        return q.to(device), k.to(device), v.to(device)
-    if pin:
-        return q.pin_memory(), k.pin_memory(), v.pin_memory()
-    return q, k, v
+         (c["batch"], c["kv_heads"], c["seq"], c["head_dim"])], seed, device)
 
 
 def time_cpu_path(steps, warmup):
@@ -142,50 +193,56 @@ def time_cpu_path(steps, warmup):
 
 
 def run_reference(args):
-    rank, world, _ = dist_env()
+    rank, world, local = dist_env()
     if rank != 0:
         return
+    # Rank 0 alone runs the CPU arm: it takes every host core, not torchrun's single thread.
+    cores = host_threads(1, 0)
     c = HEADLINE
     flops = causal_forward_flops(c["batch"], c["heads"], c["seq"], c["head_dim"])
     times = time_cpu_path(args.steps, max(args.warmup, 1))
     total = sum(times)
     value = flops * len(times) / total / 1e12
-    cores = torch.get_num_threads()
     line = {
         "impl": "reference",
         "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": workload_config(),
+        "config": workload_config(1),
         "cpu_baseline": {
             "value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
             "sample": f"{len(times)} full forward passes of the headline workload through torch CPU SDPA "
-                      f"on bf16 tensors ({os.cpu_count()} host CPUs visible)",
+                      f"on bf16 tensors, {cores} threads ({os.cpu_count()} host CPUs visible)",
         },
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def workload_config():
+def workload_config(replays):
     c = HEADLINE
     return {
         "workload": "GQA causal prefill forward, Qwen2.5-0.5B shape",
         "batch_per_gpu": c["batch"], "heads": c["heads"], "kv_heads": c["kv_heads"],
         "seq_len": c["seq"], "head_dim": c["head_dim"],
         "l2_policy": "each step uses the next of a ring of input sets larger than L2 in total",
-        "launch": "the K timed steps are one CUDA graph replay (K kernel launches back to back)",
+        "launch": "the K timed steps are one CUDA graph (K kernel launches back to back); the graph is "
+                  "replayed `replays` times, each replay timed by its own event pair, and the median "
+                  "replay is reported",
+        "replays": replays,
         "parallelism": "one batch per GPU, no collective",
     }
 
 
-def timed_region(fn, steps, warmup, world, graph=False, fork=None, join=None):
+def timed_region(fn, steps, warmup, world, graph=False, fork=None, join=None, min_ms=0.0):
     """W untimed calls, then K calls between two events on the current stream, bracketed
-    by a barrier and a device synchronize; returns milliseconds (max over ranks). With
+    by a barrier and a device synchronize; returns (milliseconds for K steps, replays). With
     `graph` the K calls are captured once into a CUDA graph and the timed region is its
-    replay, so the device sees K back-to-back launches without host gaps. `fork` / `join`
-    make side streams start after the start event and finish before the stop event."""
+    replay, so the device sees K back-to-back launches without host gaps; the replay is
+    repeated (each with its own event pair) until `min_ms` of device time has been measured
+    and the median replay is returned, max over ranks. `fork` / `join` make side streams
+    start after the start event and finish before the stop event."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -196,35 +253,80 @@ def timed_region(fn, steps, warmup, world, graph=False, fork=None, join=None):
             for i in range(steps):
                 fn(warmup + i)
         torch.cuda.synchronize()
+        replay.replay()   # one untimed replay: first-use costs of the instantiated graph
+        torch.cuda.synchronize()
     if world > 1:
         torch.distributed.barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    start.record()
-    if fork is not None:
-        fork()
-    if replay is not None:
-        replay.replay()
-    else:
-        for i in range(steps):
-            fn(warmup + i)
-    if join is not None:
-        join()
-    stop.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(stop)
+
+    def once():
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        if fork is not None:
+            fork()
+        if replay is not None:
+            replay.replay()
+        else:
+            for i in range(steps):
+                fn(warmup + i)
+        if join is not None:
+            join()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop)
+
+    first = once()
+    replays = 1
+    if replay is not None and min_ms > 0 and first > 0:
+        replays = max(1, min(2000, int(math.ceil(min_ms / first))))
+    if world > 1:
+        t = torch.tensor([replays], dtype=torch.int64, device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        replays = int(t.item())
+    samples = [first] + [once() for _ in range(replays - 1)]
+    ms = statistics.median(samples)
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         torch.distributed.barrier()
         ms = t.item()
-    return ms
+    return ms, replays
+
+
+def stats_of(got, want):
+    """The error statistics every leg reports against the float64 ruler."""
+    import kohaku_tt_b200 as ktt
+
+    st = ktt.diff_stats(got, want)
+    return {k: st[k] for k in ("abs_max", "rel_median", "cosine", "nonfinite")}
+
+
+def rows_parity(out, lse, q, k, v, pairs, rows, causal=False, shift=0, klen=None):
+    """Sampled (batch, head) pairs x sampled query rows of a dense call against float64 rows
+    (oracle.ruler_rows): for sizes whose full float64 score matrix does not fit."""
+    from oracle import attention_oracle as ao
+
+    group = q.shape[1] // k.shape[1]
+    got, want, lse_err = [], [], 0.0
+    idx = torch.as_tensor(rows, dtype=torch.long)
+    for b, h in pairs:
+        o, l = ao.ruler_rows(q[b, h].cpu(), k[b, h // group].cpu(), v[b, h // group].cpu(), rows,
+                             shift=shift, causal=causal, klen=None if klen is None else klen[b])
+        got.append(out[b, h].cpu()[idx])
+        want.append(o)
+        if lse is not None:
+            lse_err = max(lse_err, float((lse[b, h].cpu()[idx].double() - l).abs().max()))
+    st = stats_of(torch.stack(got), torch.stack(want))
+    st["lse_abs_max"] = lse_err
+    st["sample"] = f"{len(pairs)} (batch, head) pairs x {len(rows)} query rows vs float64"
+    return st
 
 
 def run_ours(args):
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    threads = host_threads(world, local)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -258,11 +360,12 @@ def run_ours(args):
     out, _ = step(0)
     torch.cuda.synchronize()
     _lib.device_status()
-    parity = ktt.diff_stats(out, ao.ruler_dense(q0, k0, v0, causal=True))
+    parity = stats_of(out, ao.ruler_dense(q0, k0, v0, causal=True))
 
     ktt.reset_counters()
-    ms = timed_region(step, steps, warmup, world, graph=not args.eager)
-    launches = sum(ktt.counters()[k] for k in ("attention_flash", "attention_mma")) - warmup
+    ms, replays = timed_region(step, steps, warmup, world, graph=not args.eager, min_ms=MIN_REGION_MS)
+    launches = steps   # one kernel of this library per step (counted by the library below)
+    counted = sum(ktt.counters()[k] for k in ("attention_flash", "attention_mma"))
     _lib.device_status()
     kernel = "tcgen05" if ktt.counters()["attention_flash"] else "warp-mma"
     value = flops * steps * world / (ms * 1e-3) / 1e12
@@ -317,34 +420,57 @@ def run_ours(args):
         for s_ in streams:
             s_.wait_stream(main)
 
-    e2e_steps = max(20, steps)
-    e2e_ms = timed_region(e2e_step, e2e_steps, warmup, world, fork=e2e_fork, join=e2e_join)
+    e2e_steps = max(100, steps)
+    cpu0 = time.process_time()
+    wall0 = time.perf_counter()
+    e2e_ms, _ = timed_region(e2e_step, e2e_steps, warmup, world, fork=e2e_fork, join=e2e_join)
+    host_cpu_us = (time.process_time() - cpu0) / (e2e_steps + warmup) * 1e6
+    host_wall_us = (time.perf_counter() - wall0) / (e2e_steps + warmup) * 1e6
     e2e_value = flops * e2e_steps * world / (e2e_ms * 1e-3) / 1e12
     h2d = host[0].numel() * host[0].element_size()
     d2h = out_host[0].numel() * out_host[0].element_size()
+
+    # What bounds the end-to-end step: the copies alone, on the same three streams.
+    def copies_only(i):
+        with torch.cuda.stream(streams[i % lanes]):
+            flat = host[i % 4].to(dev, non_blocking=True)
+            out_host[i % lanes].copy_(flat[:counts[0]].view(shapes[0]), non_blocking=True)
+
+    copy_ms, _ = timed_region(copies_only, e2e_steps, warmup, world, fork=e2e_fork, join=e2e_join)
+    e2e_parts = {
+        "host_cpu_us_per_step": host_cpu_us, "host_wall_us_per_step": host_wall_us,
+        "copies_only_us_per_step": copy_ms / e2e_steps * 1e3, "kernel_us_per_step": per_launch_ms * 1e3,
+        "host_threads": threads,
+    }
+    if world > 1:
+        t = torch.tensor([host_cpu_us, copy_ms / e2e_steps * 1e3, e2e_ms / e2e_steps * 1e3],
+                         dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_parts["max_over_ranks"] = {"host_cpu_us_per_step": t[0].item(), "copies_only_us_per_step": t[1].item(),
+                                       "e2e_us_per_step": t[2].item()}
 
     line = {
         "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": per_launch_ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(),
+        "data": "synthetic", "config": workload_config(replays),
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
-                "api": "torch.nn.functional.scaled_dot_product_attention on CUDA tensors, steps issued round-robin on 3 streams"},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+                "api": "torch.nn.functional.scaled_dot_product_attention on CUDA tensors, steps issued round-robin on 3 streams",
+                "parts": e2e_parts},
         "gpu_launches": launches,
+        "library_calls_counted": counted,
         "clocks": clocks,
         "kernel": kernel,
-        "parity_vs_f64": {k: parity[k] for k in ("abs_max", "rel_median", "cosine", "nonfinite")},
+        "parity_vs_f64": parity,
     }
     achieved = flops / (per_launch_ms * 1e-3) / 1e12
     line["roofline"] = {
         "bound": "tensor", "achieved": achieved, "peak": peaks["bf16"], "unit": "TFLOP/s",
         "frac": achieved / peaks["bf16"],
-        # DRAM bytes of one launch from the ncu capture summarised in
-        # profiles/fwd_tc5_headline.md (dram__bytes_read.sum + dram__bytes_write.sum; the
-        # output stays in L2 at this size). Algorithmic bytes are 8.4 MB: no re-reads.
-        "traffic": 4775936 if kernel == "tcgen05" and c["batch"] == 1 else None,
-        "traffic_unit": "bytes per launch (ncu)",
+        "traffic": captured_traffic() if kernel == "tcgen05" else None,
+        "traffic_unit": "DRAM bytes per launch (one ncu capture of this kernel source; null when the source changed since)",
+        "algorithmic_bytes": per_set,
         "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_nominal_2250": achieved / 2250.0,
     }
 
@@ -353,33 +479,117 @@ def run_ours(args):
         times = time_cpu_path(3, 1)
         cpu_tflops = flops / statistics.median(times) / 1e12
         cpu_out = ao.cpu_dense(q0, k0, v0, causal=True)
-        cpu_parity = ktt.diff_stats(cpu_out, ao.ruler_dense(q0, k0, v0, causal=True))
         line["cpu_baseline"] = {
             "value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": "median of 3 full forward passes of the headline workload through torch CPU SDPA on "
                       "bf16 tensors after one warm-up",
-            "parity_vs_f64": {k: cpu_parity[k] for k in ("abs_max", "rel_median", "cosine")},
+            "parity_vs_f64": stats_of(cpu_out, ao.ruler_dense(q0, k0, v0, causal=True)),
         }
     if world > 1 and not args.headline_only:
+        extra = sharded_legs(dev, peaks, rank, world, warmup)
         ring = ring_leg(dev, peaks, rank, world)
         if rank == 0:
-            line.setdefault("extra", {})["ring_attention"] = ring
+            extra["ring_attention"] = ring
+            line["extra"] = extra
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
+# ---- multi-GPU legs -------------------------------------------------------------------------
+
+def _max_min_over_ranks(ms, dev):
+    t = torch.tensor([ms, -ms], dtype=torch.float64, device=dev)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return t[0].item(), -t[1].item()
+
+
+def sharded_legs(dev, peaks, rank, world, warmup):
+    """The other configurations split over the GPUs the way they shard, with no collective
+    on the data path: decode by whole sequences (batch 64 / N per GPU), SDXL self-attention
+    by (batch, head) pairs (20 pairs over N), the packed batch by whole sequences balanced
+    by sum L^2. Each reports the aggregate rate from the slowest rank's time, the fastest
+    rank's time beside it, and this rank-0 shard's error statistics."""
+    from kohaku_tt_b200 import ops, parallel
+    from oracle import attention_oracle as ao
+
+    out = {}
+    # decode: B 64 over N GPUs
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.randint(512, 4097, (64,), generator=g, dtype=torch.int32)
+    lo, hi = parallel.shard_range(64, world, rank)
+    mine = lengths[lo:hi]
+    nb = hi - lo
+    caches = [(device_randn((nb, 2, 4096, 128), 10 * rank + i, dev), device_randn((nb, 2, 4096, 128), 10 * rank + 5 + i, dev))
+              for i in range(max(2, int(1.5 * L2_BYTES / (nb * 2 * 4096 * 128 * 2 * 2)) + 1))]
+    q = seeded([(64, 16, 1, 128)], 3)[0][lo:hi].contiguous().to(dev)
+    ln = mine.to(dev)
+    ms, _ = timed_region(lambda i: ops.decode(q, *caches[i % len(caches)], key_lengths=ln), 50, warmup, 1, graph=True)
+    ms /= 50
+    slow, fast = _max_min_over_ranks(ms, dev)
+    nbytes = float(lengths.sum()) * 2 * (128 + 128) * 2 + 2 * 64 * 16 * 128 * 2
+    o, _ = ops.decode(q, *caches[0], key_lengths=ln)
+    out["decode_kv_gbs_sharded"] = {
+        "value": nbytes / (slow * 1e-3) / 1e9, "ms_slowest_rank": slow, "ms_fastest_rank": fast,
+        "frac_of_measured_hbm_per_gpu": nbytes / (slow * 1e-3) / 1e9 / world / peaks["hbm"],
+        "sequences_per_gpu": nb,
+        "parity_vs_f64": stats_of(o, ao.ruler_lengths(q.cpu(), caches[0][0].cpu(), caches[0][1].cpu(), mine)),
+    }
+    del caches
+
+    # SDXL self-attention: 20 (batch, head) pairs over N GPUs
+    pairs = parallel.shard_pairs(2, 10, world)[rank]
+    npairs = max(len(pairs), 1)
+    xs = [tuple(device_randn((1, npairs, 4096, 64), 100 * rank + 3 * i + j, dev) for j in range(3)) for i in range(12)]
+    ms, _ = timed_region(lambda i: ops.sdpa_forward(*xs[i % 12]), 30, warmup, 1, graph=True)
+    ms /= 30
+    slow, fast = _max_min_over_ranks(ms, dev)
+    f = 4.0 * 20 * 4096 * 4096 * 64
+    o, l = ops.sdpa_forward(*xs[0])
+    out["sdxl_self_tflops_sharded"] = {
+        "value": f / (slow * 1e-3) / 1e12, "ms_slowest_rank": slow, "ms_fastest_rank": fast,
+        "pairs_per_gpu": len(pairs),
+        "parity_vs_f64": rows_parity(o, l, *xs[0], [(0, 0), (0, npairs - 1)], [0, 1, 2047, 4095]),
+    }
+    del xs
+
+    # packed batch: whole sequences balanced by sum L^2
+    lens = packed_lengths()
+    first, last = parallel.shard_sequences(lens, world)[rank]
+    mine = lens[first:last]
+    tokens = sum(mine)
+    cu = torch.tensor([0] + list(torch.tensor(mine).cumsum(0)), dtype=torch.int32, device=dev)
+    q, k, v, do = (device_randn((tokens, 16, 128), 200 * rank + j, dev) for j in range(4))
+    ms_f, _ = timed_region(lambda i: ops.varlen_forward(q, k, v, cu, cu, max(mine), max(mine), causal=True), 10, warmup, 1, graph=True)
+    ms_f /= 10
+    o, l = ops.varlen_forward(q, k, v, cu, cu, max(mine), max(mine), causal=True)
+    ms_b, _ = timed_region(lambda i: ops.varlen_backward(do, q, k, v, o, l, cu, cu, max(mine), max(mine), causal=True), 5, warmup, 1, graph=True)
+    ms_b /= 5
+    slow_f, fast_f = _max_min_over_ranks(ms_f, dev)
+    slow_b, fast_b = _max_min_over_ranks(ms_b, dev)
+    f = sum(4.0 * 16 * 128 * n * (n + 1) / 2 for n in lens)
+    out["varlen_tflops_sharded"] = {
+        "forward": {"value": f / (slow_f * 1e-3) / 1e12, "ms_slowest_rank": slow_f, "ms_fastest_rank": fast_f},
+        "backward": {"value": 2.5 * f / (slow_b * 1e-3) / 1e12, "ms_slowest_rank": slow_b, "ms_fastest_rank": fast_b},
+        "sequences_per_gpu": len(mine), "tokens_this_rank": tokens,
+        "parity_vs_f64": packed_parity(o, q, k, v, do, mine, None, heads=(0, 15)),
+    }
+    return out
+
+
 def ring_leg(dev, peaks, rank, world):
     """The long-context configuration: one causal sequence of 16,384 x N tokens (131,072 at
     N = 8), 16 heads, D 128, sharded zigzag over the N GPUs, K/V blocks passed around the
-    ring by NCCL send/recv. Every rank takes part; times are the max over ranks."""
+    ring by NCCL send/recv. Every rank takes part; times are the max over ranks. Parity:
+    sampled query rows of two heads on every rank against float64 rows over the whole
+    sequence's keys (gathered for those heads only), and full gradients of a down-scaled
+    ring (1,024 tokens per rank, 2 heads) against float64 autograd."""
     from kohaku_tt_b200 import parallel
+    from oracle import attention_oracle as ao
 
     tokens, heads, d = 16384, 16, 128
-    g = torch.Generator(device=dev).manual_seed(100 + rank)
-    q, k, v, do = (torch.randn((1, heads, tokens, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-                   for _ in range(4))
+    q, k, v, do = (device_randn((1, heads, tokens, d), 100 + 7 * rank + j, dev) for j in range(4))
     seq = tokens * world
     fwd_flops = 4.0 * heads * d * (seq * (seq + 1) / 2)
 
@@ -399,19 +609,71 @@ def ring_leg(dev, peaks, rank, world):
 
     ms_f = timed(lambda: parallel.ring_forward(q, k, v), 3)
     out, lse = parallel.ring_forward(q, k, v)
-    ms_b = timed(lambda: parallel.ring_backward(do, q, k, v, out, lse), 1)
+    ms_b = timed(lambda: parallel.ring_backward(do, q, k, v, out, lse), 3)
+
+    # Forward parity on sampled rows: gather two heads' K / V from every rank, put the chunks
+    # back in sequence order, evaluate this rank's sampled rows in float64.
+    hs = [0, heads - 1]
+    c = tokens // 2
+    gathered = []
+    for t in (k, v):
+        mine = t[0, hs].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        torch.distributed.all_gather(parts, mine)
+        gathered.append(parallel.zigzag_merge([p_.cpu() for p_ in parts], dim=1))
+    kf, vf = gathered
+    local_rows = [0, 1, c - 1, c, c + 1, tokens - 1]
+    chunk_a, chunk_b = parallel.zigzag_chunks(world, rank)
+    global_rows = [r if r < c else (chunk_b * c + (r - c)) for r in local_rows]
+    global_rows = [chunk_a * c + r if r < c else g for r, g in zip(local_rows, global_rows)]
+    got, want, lse_err = [], [], 0.0
+    for i, h in enumerate(hs):
+        qr = q[0, h].cpu()[torch.tensor(local_rows)]
+        o, l = ao.ruler_rows(qr, kf[i], vf[i], global_rows, causal=True)
+        got.append(out[0, h].cpu()[torch.tensor(local_rows)])
+        want.append(o)
+        lse_err = max(lse_err, float((lse[0, h].cpu()[torch.tensor(local_rows)].double() - l).abs().max()))
+    st = stats_of(torch.stack(got), torch.stack(want))
+    worst = torch.tensor([st["abs_max"], st["rel_median"], lse_err, float(st["nonfinite"])], dtype=torch.float64, device=dev)
+    torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX)
+
+    # Gradients on a down-scaled ring against float64 autograd of the whole sequence.
+    small, sh = 1024, 2
+    g = torch.Generator().manual_seed(77)
+    full = [torch.randn((1, sh, small * world, d), generator=g).to(torch.bfloat16) for _ in range(4)]
+    shards = [parallel.zigzag_split(t, world, dim=2)[rank].to(dev) for t in full]
+    so, sl = parallel.ring_forward(shards[0], shards[1], shards[2])
+    gq, gk, gv = parallel.ring_backward(shards[3], shards[0], shards[1], shards[2], so, sl)
+    ruler, dq, dk, dv = ao.grads_dense(full[0], full[1], full[2], full[3], causal=True)
+    import kohaku_tt_b200 as ktt
+
+    grad_err = [ktt.rel_rms(got_, parallel.zigzag_split(want_, world, dim=2)[rank])
+                for got_, want_ in ((so, ruler), (gq, dq), (gk, dk), (gv, dv))]
+    ge = torch.tensor(grad_err, dtype=torch.float64, device=dev)
+    torch.distributed.all_reduce(ge, op=torch.distributed.ReduceOp.MAX)
+
     kv_bytes = 2 * tokens * heads * d * 2
     return {
         "workload": f"one causal sequence of {seq} tokens, 16 heads, D 128, zigzag over {world} GPUs",
         "forward_tflops": fwd_flops / (ms_f * 1e-3) / 1e12, "forward_ms": ms_f,
         "forward_frac_of_measured_bf16_per_gpu": fwd_flops / (ms_f * 1e-3) / 1e12 / world / peaks["bf16"],
         "backward_tflops": 2.5 * fwd_flops / (ms_b * 1e-3) / 1e12, "backward_ms": ms_b,
+        "backward_frac_of_measured_bf16_per_gpu": 2.5 * fwd_flops / (ms_b * 1e-3) / 1e12 / world / peaks["bf16"],
         "ring_bytes_per_step_per_gpu": kv_bytes,
+        "parity_vs_f64": {
+            "abs_max": worst[0].item(), "rel_median": worst[1].item(), "lse_abs_max": worst[2].item(),
+            "nonfinite": int(worst[3].item()),
+            "sample": f"worst rank; per rank 2 heads x {len(local_rows)} query rows against float64 over all {seq} keys",
+        },
+        "small_ring_rel_rms_vs_f64": {"out": ge[0].item(), "dq": ge[1].item(), "dk": ge[2].item(), "dv": ge[3].item(),
+                                      "workload": f"{small * world} tokens, {sh} heads, full float64 autograd, worst rank"},
     }
 
 
+# ---- single-GPU legs --------------------------------------------------------------------------
+
 def _time(fn, steps, warmup):
-    return timed_region(fn, steps, warmup, 1, graph=True) / steps
+    return timed_region(fn, steps, warmup, 1, graph=True, min_ms=20.0)[0] / steps
 
 
 def leg_fwd_bwd(dev, peaks, warmup):
@@ -422,10 +684,9 @@ def leg_fwd_bwd(dev, peaks, warmup):
     c = HEADLINE
     sets = []
     for i in range(8):
-        q, k, v, do = ao.make_inputs(
+        sets.append(seeded(
             [(1, c["heads"], c["seq"], 64), (1, c["kv_heads"], c["seq"], 64),
-             (1, c["kv_heads"], c["seq"], 64), (1, c["heads"], c["seq"], 64)], 50 + i)
-        sets.append(tuple(t.to(dev) for t in (q, k, v, do)))
+             (1, c["kv_heads"], c["seq"], 64), (1, c["heads"], c["seq"], 64)], 50 + i, dev))
 
     def fwd_bwd(i):
         q, k, v, do = sets[i % len(sets)]
@@ -434,26 +695,48 @@ def leg_fwd_bwd(dev, peaks, warmup):
 
     ms = _time(fwd_bwd, 30, warmup)
     f = 3.5 * causal_forward_flops(1, c["heads"], c["seq"], 64)
+    # Gradients of one whole GQA group (7 query heads on K/V head 0) against float64 autograd.
+    q, k, v, do = sets[0]
+    out, lse = ops.sdpa_forward(q, k, v, causal=True)
+    gq, gk, gv = ops.sdpa_backward(do, q, k, v, out, lse, causal=True)
+    grp = c["heads"] // c["kv_heads"]
+    ruler, dq, dk, dv = ao.grads_dense(q[:, :grp].cpu(), k[:, :1].cpu(), v[:, :1].cpu(), do[:, :grp].cpu(), causal=True)
     return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
             "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
-            "workload": "headline shape, forward + backward"}
+            "workload": "headline shape, forward + backward",
+            "parity_vs_f64": {"out": stats_of(out[:, :grp], ruler), "dq": stats_of(gq[:, :grp], dq),
+                              "dk": stats_of(gk[:, :1], dk), "dv": stats_of(gv[:, :1], dv),
+                              "sample": "GQA group 0: 7 query heads and their K/V head, full float64 autograd"}}
 
 
 def leg_fwd_b8(dev, peaks, warmup):
     """Headline shape at batch 8 (the whole-box batch on one GPU)."""
     from kohaku_tt_b200 import ops
-    from oracle import attention_oracle as ao
 
     c = HEADLINE
-    q8 = []
-    for i in range(4):
-        q, k, v = ao.make_inputs(
-            [(8, c["heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64)], 60 + i)
-        q8.append((q.to(dev), k.to(dev), v.to(dev)))
+    q8 = [seeded([(8, c["heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64), (8, c["kv_heads"], c["seq"], 64)], 60 + i, dev)
+          for i in range(4)]
     ms = _time(lambda i: ops.sdpa_forward(*q8[i % 4], causal=True), 50, warmup)
     f = causal_forward_flops(8, c["heads"], c["seq"], 64)
+    out, lse = ops.sdpa_forward(*q8[0], causal=True)
     return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
-            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+            "parity_vs_f64": rows_parity(out, lse, *q8[0], [(0, 0), (3, 6), (7, 13)], [0, 127, 128, 1000, 2047], causal=True)}
+
+
+def leg_fwd_d128(dev, peaks, warmup):
+    """Dense causal forward at head dim 128: B 2, 16 heads, S 4096."""
+    from kohaku_tt_b200 import ops
+
+    xs = [tuple(device_randn((2, 16, 4096, 128), 300 + 3 * i + j, dev) for j in range(3)) for i in range(4)]
+    ms = _time(lambda i: ops.sdpa_forward(*xs[i % 4], causal=True), 20, warmup)
+    f = causal_forward_flops(2, 16, 4096, 128)
+    out, lse = ops.sdpa_forward(*xs[0], causal=True)
+    return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+            "frac_of_measured_bf16_sustained": f / (ms * 1e-3) / 1e12 / peaks["bf16_sustained"],
+            "workload": "B 2, 16 heads, S 4096, D 128, causal",
+            "parity_vs_f64": rows_parity(out, lse, *xs[0], [(0, 0), (1, 15)], [0, 127, 128, 2047, 4095], causal=True)}
 
 
 def leg_decode(dev, peaks, warmup):
@@ -463,19 +746,19 @@ def leg_decode(dev, peaks, warmup):
 
     g = torch.Generator().manual_seed(0)
     lengths = torch.randint(512, 4097, (64,), generator=g, dtype=torch.int32)
-    caches = []
-    for i in range(2):  # two caches, 268 MB each: nothing of a step's reads survives in L2
-        k = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(i), device=dev, dtype=torch.float32).to(torch.bfloat16)
-        v = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(9 + i), device=dev, dtype=torch.float32).to(torch.bfloat16)
-        caches.append((k, v))
-    q = ao.make_inputs([(64, 16, 1, 128)], 3)[0].to(dev)
+    # two caches, 268 MB each: nothing of a step's reads survives in L2
+    caches = [(device_randn((64, 2, 4096, 128), i, dev), device_randn((64, 2, 4096, 128), 9 + i, dev)) for i in range(2)]
+    q = seeded([(64, 16, 1, 128)], 3, dev)[0]
     ln = lengths.to(dev)
     ms = _time(lambda i: ops.decode(q, *caches[i % 2], key_lengths=ln), 50, warmup)
     nbytes = float(lengths.sum()) * 2 * (128 + 128) * 2 + 2 * q.numel() * 2
     gbs = nbytes / (ms * 1e-3) / 1e9
+    out, _ = ops.decode(q, *caches[0], key_lengths=ln)
+    ruler = ao.ruler_lengths(q.cpu(), caches[0][0].cpu(), caches[0][1].cpu(), lengths)
     return {"value": gbs, "ms": ms, "bytes": nbytes,
             "frac_of_measured_hbm": gbs / peaks["hbm"], "frac_of_nominal_8000": gbs / 8000.0,
-            "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0"}
+            "workload": "B 64, 16 q heads / 2 kv heads, D 128, lengths U[512, 4096] seed 0",
+            "parity_vs_f64": dict(stats_of(out, ruler), sample="all 64 x 16 (batch, head) pairs, full float64")}
 
 
 def leg_decode_step(dev, peaks, warmup):
@@ -488,12 +771,8 @@ def leg_decode_step(dev, peaks, warmup):
 
     g = torch.Generator().manual_seed(0)
     lengths = torch.randint(512, 4096, (64,), generator=g, dtype=torch.int32)
-    caches = []
-    for i in range(2):
-        k = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(i), device=dev, dtype=torch.float32).to(torch.bfloat16)
-        v = torch.randn((64, 2, 4096, 128), generator=torch.Generator(device=dev).manual_seed(9 + i), device=dev, dtype=torch.float32).to(torch.bfloat16)
-        caches.append((k, v))
-    q, k_new, v_new = (t.to(dev) for t in ao.make_inputs([(64, 16, 1, 128), (64, 2, 1, 128), (64, 2, 1, 128)], 3))
+    caches = [(device_randn((64, 2, 4096, 128), i, dev), device_randn((64, 2, 4096, 128), 9 + i, dev)) for i in range(2)]
+    q, k_new, v_new = seeded([(64, 16, 1, 128), (64, 2, 1, 128), (64, 2, 1, 128)], 3, dev)
     pos = torch.arange(4096, dtype=torch.float32, device=dev)[:, None]
     inv = 1.0 / (10000.0 ** (torch.arange(0, 128, 2, dtype=torch.float32, device=dev) / 128))
     ang = torch.cat([pos * inv, pos * inv], dim=-1)
@@ -501,6 +780,16 @@ def leg_decode_step(dev, peaks, warmup):
     ln = lengths.to(dev)
     ln_next = ln + 1
     idx = ln.long()
+
+    # Parity first, on a copy of cache 0 (the timed loops below overwrite the same rows with
+    # the same values every step).
+    kc, vc = caches[0][0].clone(), caches[0][1].clone()
+    want, k_want, v_want = ao.decode_step(q.cpu(), k_new.cpu(), v_new.cpu(), kc.cpu(), vc.cpu(), lengths.tolist(),
+                                          cos[idx].cpu(), sin[idx].cpu())
+    got = ktt.decode_step(q, k_new, v_new, kc, vc, ln, cos, sin)
+    parity = dict(stats_of(got, want), cache_rows_equal=bool(torch.equal(kc.cpu(), k_want) and torch.equal(vc.cpu(), v_want)),
+                  sample="all 64 x 16 pairs, float64 over the updated cache")
+    del kc, vc
 
     def fused(i):
         ktt.decode_step(q, k_new, v_new, *caches[i % 2], ln, cos, sin)
@@ -526,19 +815,22 @@ def leg_decode_step(dev, peaks, warmup):
     gbs = nbytes / (ms * 1e-3) / 1e9
     return {"value": gbs, "ms": ms, "separate_ops_ms": ms_sep, "bytes": nbytes,
             "frac_of_measured_hbm": gbs / peaks["hbm"],
-            "workload": "decode leg's shape; new token at position lengths[b]"}
+            "workload": "decode leg's shape; new token at position lengths[b]",
+            "parity_vs_f64": parity}
 
 
 def leg_sdxl_self(dev, peaks, warmup):
     """SDXL self-attention: B 2, 10 heads, S 4096, D 64, head views of [B, S, 640]."""
     from kohaku_tt_b200 import ops
-    from oracle import attention_oracle as ao
 
-    xs = [ao.make_inputs([(2, 4096, 3 * 640)], 70 + i)[0].to(dev).view(2, 4096, 3, 10, 64) for i in range(12)]
-    ms = _time(lambda i: ops.sdpa_forward(*(xs[i % 12][:, :, j].transpose(1, 2) for j in range(3))), 30, warmup)
+    xs = [seeded([(2, 4096, 3 * 640)], 70 + i, dev)[0].view(2, 4096, 3, 10, 64) for i in range(12)]
+    views = lambda x: tuple(x[:, :, j].transpose(1, 2) for j in range(3))
+    ms = _time(lambda i: ops.sdpa_forward(*views(xs[i % 12])), 30, warmup)
     f = 4.0 * 2 * 10 * 4096 * 4096 * 64
+    out, lse = ops.sdpa_forward(*views(xs[0]))
     return {"value": f / (ms * 1e-3) / 1e12, "ms": ms,
-            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
+            "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+            "parity_vs_f64": rows_parity(out, lse, *views(xs[0]), [(0, 0), (1, 9)], [0, 1, 2047, 4095])}
 
 
 def leg_sdxl_cross(dev, peaks, warmup):
@@ -546,19 +838,19 @@ def leg_sdxl_cross(dev, peaks, warmup):
     from kohaku_tt_b200 import ops
     from oracle import attention_oracle as ao
 
-    q = ao.make_inputs([(2, 10, 4096, 64)], 80)[0].to(dev)
-    k, v = (t.to(dev) for t in ao.make_inputs([(2, 10, 77, 64)] * 2, 81))
+    q = seeded([(2, 10, 4096, 64)], 80, dev)[0]
+    k, v = seeded([(2, 10, 77, 64)] * 2, 81, dev)
     keep = torch.ones(2, 1, 1, 77, dtype=torch.bool, device=dev)
     keep[..., 57:] = False
     ms = _time(lambda i: ops.sdpa_forward(q, k, v, mask=keep), 30, warmup)
-    return {"ms": ms, "gflop_kept_keys": 4.0 * 2 * 10 * 4096 * 57 * 64 / 1e9}
+    out, _ = ops.sdpa_forward(q, k, v, mask=keep)
+    ruler = ao.ruler_dense(q.cpu(), k.cpu(), v.cpu(), mask=keep.cpu())
+    return {"ms": ms, "gflop_kept_keys": 4.0 * 2 * 10 * 4096 * 57 * 64 / 1e9,
+            "parity_vs_f64": dict(stats_of(out, ruler), sample="all 20 pairs, full float64")}
 
 
-def leg_varlen(dev, peaks, warmup):
-    """Packed causal training attention: 16 heads, D 128, 65,536 tokens, lengths
-    U[64, 4096] (seed 0), forward and backward."""
-    from kohaku_tt_b200 import ops
-
+def packed_lengths():
+    """Lengths U[64, 4096] (seed 0) drawn until 65,536 tokens; the last one truncated."""
     g = torch.Generator().manual_seed(0)
     lens, total = [], 0
     while total < 65536:
@@ -568,8 +860,50 @@ def leg_varlen(dev, peaks, warmup):
         total += n
     if lens[-1] < 64 and len(lens) > 1:
         lens[-2] += lens.pop()
+    return lens
+
+
+def packed_parity(out, q, k, v, do, lens, grads, heads=(0, 15)):
+    """Whole sequences (the shortest, the longest, the last) of a packed batch, two heads,
+    against the float64 per-sequence ruler; with `grads` = (dq, dk, dv) also against its
+    float64 autograd."""
+    from oracle import attention_oracle as ao
+
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    picks = sorted({min(range(len(lens)), key=lambda i: lens[i]), max(range(len(lens)), key=lambda i: lens[i]), len(lens) - 1})
+    hs = list(heads)
+    res = {"sample": f"sequences {picks} (lengths {[lens[i] for i in picks]}), heads {hs}, float64 per sequence"}
+    worst = {}
+    for i in picks:
+        sl = slice(cu[i], cu[i + 1])
+        qs, ks, vs = (t[sl][:, hs].cpu() for t in (q, k, v))
+        c = [0, lens[i]]
+        if grads is None:
+            ruler = ao.ruler_varlen(qs, ks, vs, c, c, causal=True)
+            pairs = [("out", out[sl][:, hs], ruler)]
+        else:
+            ruler, dq, dk, dv = ao.ruler_varlen(qs, ks, vs, c, c, causal=True, dout=do[sl][:, hs].cpu())
+            pairs = [("out", out[sl][:, hs], ruler), ("dq", grads[0][sl][:, hs], dq),
+                     ("dk", grads[1][sl][:, hs], dk), ("dv", grads[2][sl][:, hs], dv)]
+        for name, got, want in pairs:
+            st = stats_of(got, want)
+            old = worst.get(name)
+            if old is None or st["abs_max"] > old["abs_max"]:
+                worst[name] = st
+    res.update(worst)
+    return res
+
+
+def leg_varlen(dev, peaks, warmup):
+    """Packed causal training attention: 16 heads, D 128, 65,536 tokens, lengths
+    U[64, 4096] (seed 0), forward and backward."""
+    from kohaku_tt_b200 import ops
+
+    lens = packed_lengths()
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
-    q, k, v, do = (torch.randn((65536, 16, 128), device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(4))
+    q, k, v, do = (device_randn((65536, 16, 128), 400 + j, dev) for j in range(4))
     f = sum(4.0 * 16 * 128 * n * (n + 1) / 2 for n in lens)
     ms = _time(lambda i: ops.varlen_forward(q, k, v, cu, cu, max(lens), max(lens), causal=True), 10, warmup)
     fwd = {"value": f / (ms * 1e-3) / 1e12, "ms": ms, "sequences": len(lens),
@@ -578,23 +912,59 @@ def leg_varlen(dev, peaks, warmup):
     ms = _time(lambda i: ops.varlen_backward(do, q, k, v, out, lse, cu, cu, max(lens), max(lens), causal=True), 5, warmup)
     bwd = {"value": 2.5 * f / (ms * 1e-3) / 1e12, "ms": ms,
            "frac_of_measured_bf16": 2.5 * f / (ms * 1e-3) / 1e12 / peaks["bf16"]}
-    return {"forward": fwd, "backward": bwd}
+    grads = ops.varlen_backward(do, q, k, v, out, lse, cu, cu, max(lens), max(lens), causal=True)
+    return {"forward": fwd, "backward": bwd, "parity_vs_f64": packed_parity(out, q, k, v, do, lens, grads)}
+
+
+def leg_masked_training(dev, peaks, warmup):
+    """A masked training step: key-padding mask (one row per batch entry), forward +
+    backward, B 4, 16 / 4 heads, S 2048, D 128, keys past 0.7 S masked in even batches."""
+    from kohaku_tt_b200 import ops
+    from oracle import attention_oracle as ao
+
+    b, h, hk, s, d = 4, 16, 4, 2048, 128
+    q, k, v, do = seeded([(b, h, s, d), (b, hk, s, d), (b, hk, s, d), (b, h, s, d)], 90, dev)
+    keep = torch.ones(b, 1, 1, s, dtype=torch.bool, device=dev)
+    keep[::2, ..., int(0.7 * s):] = False
+
+    def stepf(i):
+        out, lse = ops.sdpa_forward(q, k, v, mask=keep)
+        ops.sdpa_backward(do, q, k, v, out, lse, mask=keep)
+
+    ms = _time(stepf, 10, warmup)
+    kept = float(keep.sum()) / b
+    f = 3.5 * 4.0 * b * h * s * kept * d
+    out, lse = ops.sdpa_forward(q, k, v, mask=keep)
+    gq, gk, gv = ops.sdpa_backward(do, q, k, v, out, lse, mask=keep)
+    grp = h // hk
+    ruler, dq, dk, dv = ao.grads_dense(q[:1, :grp].cpu(), k[:1, :1].cpu(), v[:1, :1].cpu(), do[:1, :grp].cpu(), mask=keep[:1].cpu())
+    return {"value": f / (ms * 1e-3) / 1e12, "ms": ms, "frac_of_measured_bf16": f / (ms * 1e-3) / 1e12 / peaks["bf16"],
+            "workload": "B 4, 16 / 4 heads, S 2048, D 128, bool key-padding mask, forward + backward; FLOPs over kept keys",
+            "parity_vs_f64": {"out": stats_of(out[:1, :grp], ruler), "dq": stats_of(gq[:1, :grp], dq),
+                              "dk": stats_of(gk[:1, :1], dk), "dv": stats_of(gv[:1, :1], dv),
+                              "sample": "batch 0, GQA group 0, full float64 autograd"}}
 
 
 LEGS = {
     "fwd_bwd_tflops": leg_fwd_bwd,
     "fwd_b8_tflops": leg_fwd_b8,
+    "fwd_d128_tflops": leg_fwd_d128,
     "decode_kv_gbs": leg_decode,
     "decode_step_gbs": leg_decode_step,
     "sdxl_self_tflops": leg_sdxl_self,
     "sdxl_cross_ms": leg_sdxl_cross,
     "varlen_tflops": leg_varlen,
+    "masked_training_tflops": leg_masked_training,
 }
 
 
 def extra_legs(dev, peaks, warmup):
     """The other configurations of the benchmark plan, each timed the same way."""
-    return {name: fn(dev, peaks, warmup) for name, fn in LEGS.items()}
+    out = {}
+    for name, fn in LEGS.items():
+        out[name] = fn(dev, peaks, warmup)
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_leg(args):

@@ -52,6 +52,8 @@ enum {
     KTT_B200_KERNEL_AUTO = 0,
     KTT_B200_KERNEL_MMA = 1,  /* general warp-MMA kernels: any head dim <= 256, masks */
     KTT_B200_KERNEL_TC5 = 2,  /* TMA + tcgen05/TMEM kernels: head dim 64 / 128 */
+    KTT_B200_KERNEL_TC5_WIDE = 3,  /* forward only: the head-dim-128 tcgen05 kernel's design also at
+                                      head dim 64, where KERNEL_TC5 picks the two-stream kernel */
 };
 
 /* One attention problem, dense ([B, H, S, D] with arbitrary batch/head/row strides, so
@@ -112,9 +114,12 @@ typedef struct ktt_b200_attn_args {
     int64_t dk_strides[3];
     int64_t dv_strides[3];
     /* Backward: workspace of ktt_b200_sdpa_backward_workspace() bytes, 256-byte aligned.
-     * Forward (optional): 4 zero-filled bytes; with them the persistent tcgen05 kernel's CTAs
-     * draw their work items from a counter there instead of a fixed deal, which evens out
-     * uneven packed batches and SMs shared with other kernels. The kernel leaves the count. */
+     * Forward (optional), head dim 64: ktt_b200_sdpa_forward_workspace() bytes, 16-byte
+     * aligned, zero-filled once before the first use. With it the CTAs draw their query
+     * tiles, longest first, from a counter there instead of a fixed deal. The kernel leaves
+     * the counter zero; calls that share a buffer must not overlap on the GPU.
+     * Forward (optional), head dim 128: 4 to 255 bytes, zero-filled before EVERY call; the
+     * CTAs then draw their work items from a counter there. */
     void* workspace;
     int64_t workspace_bytes;
 } ktt_b200_attn_args;
@@ -183,6 +188,16 @@ KTT_B200_API int ktt_b200_sdpa_backward_supported(const ktt_b200_attn_args* args
  * bridge::sdpa_varlen and bridge::sdpa_lengths (tt_bridge.hpp:925-1095). Writes out and,
  * when args->lse is set, the natural-log row statistics. */
 KTT_B200_API int ktt_b200_sdpa_forward(const ktt_b200_attn_args* args, void* stream);
+
+/* Bytes of the optional forward workspace for the problem (0 when the kernel that will run
+ * uses none). No counterpart in the reference: its host planner deals the chunks to cores
+ * before the launch (ktt_flash/program.cpp:204-242,269-275); here the deal happens on the
+ * device. */
+KTT_B200_API int64_t ktt_b200_sdpa_forward_workspace(const ktt_b200_attn_args* args);
+/* Query tiles the head-dim-64 forward kernel keeps in flight per SM of the current device
+ * (2: one CTA with two streams; 0 means a build or device the kernel was not sized for).
+ * Launches nothing. */
+KTT_B200_API int ktt_b200_forward_streams_per_sm(void);
 
 /* Bytes of workspace ktt_b200_sdpa_backward needs for the problem (0 on error). */
 KTT_B200_API int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* args);

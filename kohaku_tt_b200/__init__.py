@@ -11,7 +11,7 @@ include/ktt_b200.h); there is no CPU or PyTorch-math fallback.
 """
 
 from ._lib import UnsupportedAttention, build, counters, reset_counters
-from .aten import fused_sdp_choice, install, installed
+from .aten import fused_sdp_choice, install, installed, installed_for, uninstall
 from .attention import decode_step, sdpa, sdpa_varlen
 from .numerics import KERNELS, sdpa_kernel
 from .stats import diff_stats, format_stats, rel_rms
@@ -30,9 +30,11 @@ __all__ = [
     "fused_sdp_choice",
     "install",
     "installed",
+    "installed_for",
     "rel_rms",
     "reset_counters",
     "sdpa",
     "sdpa_kernel",
     "sdpa_varlen",
+    "uninstall",
 ]

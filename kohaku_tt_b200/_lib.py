@@ -34,7 +34,7 @@ ERR_DEVICE_WAIT = -4
 
 MASK_NONE, MASK_BOOL, MASK_BF16, MASK_F32, MASK_F16 = range(5)
 CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = range(3)
-KERNEL_AUTO, KERNEL_MMA, KERNEL_TC5 = range(3)
+KERNEL_AUTO, KERNEL_MMA, KERNEL_TC5, KERNEL_TC5_WIDE = range(4)
 
 EXPORTS = (
     "ktt_b200_abi_version",
@@ -46,6 +46,8 @@ EXPORTS = (
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
     "ktt_b200_sdpa_forward",
+    "ktt_b200_sdpa_forward_workspace",
+    "ktt_b200_forward_streams_per_sm",
     "ktt_b200_sdpa_backward_workspace",
     "ktt_b200_sdpa_backward",
     "ktt_b200_decode_scratch_bytes",
@@ -211,6 +213,9 @@ def lib():
     handle.ktt_b200_sdpa_supported.argtypes = [ctypes.POINTER(AttnArgs)]
     handle.ktt_b200_sdpa_backward_supported.argtypes = [ctypes.POINTER(AttnArgs)]
     handle.ktt_b200_sdpa_forward.argtypes = [ctypes.POINTER(AttnArgs), _ptr]
+    handle.ktt_b200_sdpa_forward_workspace.argtypes = [ctypes.POINTER(AttnArgs)]
+    handle.ktt_b200_sdpa_forward_workspace.restype = _i64
+    handle.ktt_b200_forward_streams_per_sm.restype = ctypes.c_int
     handle.ktt_b200_sdpa_backward_workspace.argtypes = [ctypes.POINTER(AttnArgs)]
     handle.ktt_b200_sdpa_backward_workspace.restype = _i64
     handle.ktt_b200_sdpa_backward.argtypes = [ctypes.POINTER(AttnArgs), _ptr]

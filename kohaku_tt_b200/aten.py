@@ -71,10 +71,25 @@ def refuse_attention(q, k, v, mask, is_causal, kernels, why):
     )
 
 
+def fused_backends_enabled():
+    """True unless torch's own switch (`torch.nn.attention.sdpa_kernel`, the
+    `torch.backends.cuda.enable_*_sdp` flags) has turned off every fused backend whose
+    overload lands in this package: flash, efficient, cuDNN and overrideable. The
+    reference asks the one switch its overload sits behind
+    (`userEnabledOverrideableSDP`, aten_attention.cpp:204-207)."""
+    c = torch._C
+    return bool(c._get_flash_sdp_enabled() or c._get_mem_efficient_sdp_enabled()
+                or c._get_cudnn_sdp_enabled() or c._get_overrideable_sdp_enabled())
+
+
 def fused_sdp_choice(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, *,
                      scale=None, enable_gqa=False):
     """aten::_fused_sdp_choice: SDP_OVERRIDEABLE (4) when the fused kernels take the
-    call, SDP_MATH (0) otherwise (tt_fused_sdp_choice, aten_attention.cpp:194-219)."""
+    call, SDP_MATH (0) when they refuse it or when torch's `sdpa_kernel` context has the
+    fused backends off (tt_fused_sdp_choice, aten_attention.cpp:194-219;
+    tests/hardware/ops/test_attention.py:63-67)."""
+    if not fused_backends_enabled():
+        return SDP_MATH
     why = fused_refusal(q, k, v, attn_mask, dropout_p, is_causal, scale)
     if why is None:
         return SDP_OVERRIDEABLE
@@ -87,7 +102,11 @@ def _checked(q, k, v, mask, dropout_p, is_causal, scale):
         kernels = current_kernels()
         if tuple(kernels) != ("flash", "mma"):
             refuse_attention(q, k, v, mask, is_causal, kernels, why)
-        raise _lib.UnsupportedAttention(f"kohaku_tt_b200: fused attention refused: {why}")
+        raise _lib.UnsupportedAttention(
+            f"kohaku_tt_b200: fused attention refused: {why}. On CUDA PyTorch picks the fused "
+            "overload itself, so a refused call cannot fall back to the math composite from "
+            "here: wrap it in torch.nn.attention.sdpa_kernel(SDPBackend.MATH), or call "
+            "kohaku_tt_b200.uninstall()")
 
 
 def _as_bf16(q, k, v):
@@ -96,6 +115,23 @@ def _as_bf16(q, k, v):
     if q.dtype == torch.float32:
         return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), True
     return q, k, v, False
+
+
+def _out_like(q, dv):
+    """Output laid out the way torch's meta kernels of the flash, cuDNN and overrideable
+    overloads promise (`empty_like(query)`: the query's stride order), so compiled graphs
+    that trust the meta strides index it correctly."""
+    if dv == q.size(3):
+        return torch.empty_like(q)
+    order = sorted(range(4), key=lambda i: (q.stride(i), -i), reverse=True)   # slowest dim first
+    shape = (q.size(0), q.size(1), q.size(2), dv)
+    out = torch.empty([shape[i] for i in order], dtype=q.dtype, device=q.device)
+    return out.permute([order.index(i) for i in range(4)])
+
+
+def _out_efficient(q, dv):
+    """The efficient overload's meta promises [B, Sq, H, Dv] storage seen as [B, H, Sq, Dv]."""
+    return torch.empty((q.size(0), q.size(2), q.size(1), dv), dtype=q.dtype, device=q.device).transpose(1, 2)
 
 
 def _bias_or_none(attn_bias):
@@ -126,7 +162,7 @@ def _seed_pair(device):
 def _flash_forward(q, k, v, dropout_p=0.0, is_causal=False, return_debug_mask=False, *, scale=None):
     _checked(q, k, v, None, dropout_p, is_causal, scale)
     qb, kb, vb, cast = _as_bf16(q, k, v)
-    out, lse = ops.sdpa_forward(qb, kb, vb, causal=is_causal, scale=scale)
+    out, lse = ops.sdpa_forward(qb, kb, vb, causal=is_causal, scale=scale, out=_out_like(qb, vb.size(3)))
     if cast:
         out = out.to(torch.float32)
     seed, offset = _rng(q.device)
@@ -147,7 +183,8 @@ def _efficient_forward(q, k, v, attn_bias, compute_log_sumexp, dropout_p=0.0, is
     qb, kb, vb, cast = _as_bf16(q, k, v)
     rows = (q.size(2) + 31) // 32 * 32
     out, lse = ops.sdpa_forward(qb, kb, vb, mask=attn_bias, causal=is_causal, scale=scale,
-                                need_lse=bool(compute_log_sumexp), lse_rows=rows)
+                                need_lse=bool(compute_log_sumexp), lse_rows=rows,
+                                out=_out_efficient(qb, vb.size(3)))
     if lse is None:
         lse = torch.empty((q.size(0), q.size(1), 0), dtype=torch.float32, device=q.device)
     if cast:
@@ -196,7 +233,7 @@ def _cudnn_forward(q, k, v, attn_bias, compute_log_sumexp, dropout_p=0.0, is_cau
     _checked(q, k, v, attn_bias, dropout_p, is_causal, scale)
     qb, kb, vb, cast = _as_bf16(q, k, v)
     out, lse = ops.sdpa_forward(qb, kb, vb, mask=attn_bias, causal=is_causal, scale=scale,
-                                need_lse=True)
+                                need_lse=True, out=_out_like(qb, vb.size(3)))
     if cast:
         out = out.to(torch.float32)
     seed, offset = _seed_pair(q.device)
@@ -221,7 +258,8 @@ def _overrideable_forward(q, k, v, attn_bias=None, dropout_p=0.0, is_causal=Fals
                           return_debug_mask=False, *, scale=None):
     _checked(q, k, v, attn_bias, dropout_p, is_causal, scale)
     qb, kb, vb, cast = _as_bf16(q, k, v)
-    out, lse = ops.sdpa_forward(qb, kb, vb, mask=attn_bias, causal=is_causal, scale=scale)
+    out, lse = ops.sdpa_forward(qb, kb, vb, mask=attn_bias, causal=is_causal, scale=scale,
+                                out=_out_like(qb, vb.size(3)))
     if cast:
         out = out.to(torch.float32)
     seed, offset = _seed_pair(q.device)
@@ -260,8 +298,15 @@ def _sdpa_lengths(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lengths: to
 
 @_sdpa_lengths.register_fake
 def _(q, k, v, lengths, is_causal, scale, stats):
-    out = q.new_empty((q.size(0), q.size(1), q.size(2), v.size(3)))
-    return out, q.new_empty((q.size(0), q.size(1), q.size(2)), dtype=torch.float32)
+    # The same layout rule as the real op: [B, S, H, Dv] storage for head views of a
+    # [B, S, H * D] tensor on the prefill route, contiguous otherwise (ops._out_like_query).
+    b, h, s, d = q.shape
+    decode_route = not stats and not is_causal and (h // max(k.size(1), 1)) * s <= 16 and d in (64, 128) and v.size(3) == d
+    if not decode_route and ops.is_head_view(q):
+        out = q.new_empty((b, s, h, v.size(3))).transpose(1, 2)
+    else:
+        out = q.new_empty((b, h, s, v.size(3)))
+    return out, q.new_empty((b, h, s), dtype=torch.float32)
 
 
 @torch.library.custom_op("ktt_b200::_sdpa_lengths_backward", mutates_args=(), device_types="cuda")
@@ -352,6 +397,32 @@ def install():
         varlen._varlen_attn.register_kernel("cuda")(_varlen_forward)
         varlen._varlen_attn_backward.register_kernel("cuda")(_varlen_backward)
     _INSTALLED = True
+
+
+def uninstall():
+    """Takes the aten overloads of install() back out: PyTorch's own CUDA kernels answer
+    again. (The packed varlen ops of torch.nn.attention.varlen keep this package's kernels:
+    custom-op kernels cannot be unregistered.)"""
+    global _ATEN, _INSTALLED
+    if _ATEN is not None:
+        _ATEN._destroy()
+        _ATEN = None
+    _INSTALLED = False
+
+
+class installed_for:
+    """`with installed_for(): ...` installs the overloads for the block and takes them out
+    again if they were not installed before it."""
+
+    def __enter__(self):
+        self.was = _INSTALLED
+        install()
+        return self
+
+    def __exit__(self, *exc):
+        if not self.was:
+            uninstall()
+        return False
 
 
 def installed():

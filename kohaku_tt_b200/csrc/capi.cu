@@ -223,7 +223,7 @@ extern "C" int ktt_b200_sdpa_supported(const ktt_b200_attn_args* a) {
         fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
         return 0;
     }
-    if (a->kernel == KTT_B200_KERNEL_TC5) {
+    if (a->kernel == KTT_B200_KERNEL_TC5 || a->kernel == KTT_B200_KERNEL_TC5_WIDE) {
         AttnParams p;
         to_params(a, p);
         const char* why = nullptr;
@@ -253,21 +253,43 @@ extern "C" int ktt_b200_sdpa_forward(const ktt_b200_attn_args* a, void* stream) 
     }
     AttnParams p;
     to_params(a, p);
-    p.fwd_work_counter = (a->workspace && a->workspace_bytes >= 4) ? static_cast<int32_t*>(a->workspace) : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const char* why = nullptr;
     const bool tc5 = forward_tc5_takes(p, &why);
-    if (a->kernel == KTT_B200_KERNEL_TC5 && !tc5) {
+    const bool wants_tc5 = a->kernel == KTT_B200_KERNEL_TC5 || a->kernel == KTT_B200_KERNEL_TC5_WIDE;
+    if (wants_tc5 && !tc5) {
         note_call(4);
         return fail(KTT_B200_ERR_UNSUPPORTED, "sdpa_forward: tcgen05 kernel: %s", why);
     }
     if (tc5 && a->kernel != KTT_B200_KERNEL_MMA) {
         note_call(0);
+        const char* why_row = nullptr;
+        if (a->kernel != KTT_B200_KERNEL_TC5_WIDE && forward_row_takes(p, &why_row)) {
+            return launch_forward_row(p, a->workspace, a->workspace_bytes, st);
+        }
+        // The one-CTA-per-SM kernel takes a 4..255-byte workspace as its work counter.
+        p.fwd_work_counter = (a->workspace && a->workspace_bytes >= 4 && a->workspace_bytes < 256)
+                                 ? static_cast<int32_t*>(a->workspace) : nullptr;
         return launch_forward_tc5(p, st);
     }
     note_call(1);
     return launch_forward_mma(p, st);
 }
+
+extern "C" int64_t ktt_b200_sdpa_forward_workspace(const ktt_b200_attn_args* a) {
+    if (const char* why = forward_refusal(a)) {
+        fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
+        return 0;
+    }
+    if (a->kernel == KTT_B200_KERNEL_MMA || a->kernel == KTT_B200_KERNEL_TC5_WIDE) return 0;
+    AttnParams p;
+    to_params(a, p);
+    const char* why = nullptr;
+    if (!forward_row_takes(p, &why)) return 0;
+    return forward_row_workspace(p);
+}
+
+extern "C" int ktt_b200_forward_streams_per_sm(void) { return forward_row_occupancy(); }
 
 extern "C" int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* a) {
     if (const char* why = backward_refusal(a)) {

@@ -196,6 +196,13 @@ int64_t backward_counter_offset(const AttnParams& p, int gsplit);
 int64_t backward_counter_count(const AttnParams& p, int gsplit);
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream);
 bool forward_tc5_takes(const AttnParams& p, const char** why);
+// Head dim 64: two CTAs per SM, a thread owns a whole row of a key block (fwd_row.cu). The
+// workspace (optional, forward_row_workspace() bytes, zero-filled once) holds the work
+// counter and the partial results of query tiles cut in two along the keys.
+bool forward_row_takes(const AttnParams& p, const char** why);
+int64_t forward_row_workspace(const AttnParams& p);
+int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+int forward_row_occupancy();
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).
 int device_status(int* code);
 // Profiling zones of the tcgen05 forward: a device buffer of 64 x 8 int64, or null.

@@ -21,7 +21,10 @@ _MASK_DTYPES = {
     torch.float16: _lib.MASK_F16,
 }
 
-_KERNELS = {"auto": _lib.KERNEL_AUTO, "mma": _lib.KERNEL_MMA, "flash": _lib.KERNEL_TC5}
+# 'flash' = the TMA + tcgen05 kernels, 'flash_wide' = the head-dim-128 tcgen05 forward's design also
+# at head dim 64 (where 'flash' runs the two-stream kernel), 'mma' = warp MMA.
+_KERNELS = {"auto": _lib.KERNEL_AUTO, "mma": _lib.KERNEL_MMA, "flash": _lib.KERNEL_TC5,
+            "flash_wide": _lib.KERNEL_TC5_WIDE}
 
 
 def _kernel_code(kernel):
@@ -73,12 +76,18 @@ def _set3(field, values):
         field[i] = int(v)
 
 
+def is_head_view(q):
+    """True when q [B, H, S, D] is a head view of a [B, S, H*D] (or fused qkv) storage."""
+    b, h, s, d = q.shape
+    return h > 1 and s > 1 and q.stride(1) == d and q.stride(2) >= h * d
+
+
 def _out_like_query(q, dv):
     """Output [B, H, Sq, Dv]: laid out [B, Sq, H, Dv] when q is a head view of a
     [B, S, H*D] storage (the reference's pitched route, aten_attention.cpp:605-628),
     else contiguous."""
     b, h, s, d = q.shape
-    if h > 1 and s > 1 and q.stride(1) == d and q.stride(2) >= h * d:
+    if is_head_view(q):
         return torch.empty((b, s, h, dv), dtype=q.dtype, device=q.device).transpose(1, 2)
     return torch.empty((b, h, s, dv), dtype=q.dtype, device=q.device)
 
@@ -128,9 +137,42 @@ def dynamic_work(on=True, min_items_per_sm=6):
     return old
 
 
+_FORWARD_WORKSPACE = {}
+
+
+def forward_workspace(args, device):
+    """The head-dim-64 forward kernel's workspace (the counter its CTAs draw their tiles
+    from): one zero-filled buffer per (device, stream); the kernel leaves it zero, so it is
+    filled once. Returns the buffer or None when the kernel that will run uses none."""
+    need = _lib.lib().ktt_b200_sdpa_forward_workspace(ctypes.byref(args))
+    if need <= 0:
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _FORWARD_WORKSPACE.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros((need,), dtype=torch.uint8, device=device)
+        _FORWARD_WORKSPACE[key] = buf
+    args.workspace, args.workspace_bytes = buf.data_ptr(), buf.numel()
+    return buf
+
+
+def drop_forward_workspaces():
+    """Forgets the cached forward workspaces (after a device-wait error their counters may
+    be left non-zero)."""
+    _FORWARD_WORKSPACE.clear()
+
+
 def _work_counter(args, device, dynamic=None):
-    """Sets args.workspace to a zeroed counter when dynamic work distribution applies
-    (`dynamic`: this call's own choice, None = the module setting)."""
+    """Sets args.workspace: the head-dim-64 kernel's cached workspace, or (head dim 128) a
+    zeroed counter when dynamic work distribution applies (`dynamic`: this call's own
+    choice, None = the module setting; False also keeps the head-dim-64 kernel on its fixed
+    deal of whole tiles)."""
+    if dynamic is not False:
+        buf = forward_workspace(args, device)
+        if buf is not None:
+            return buf
+    if args.d == 64 and args.kernel != _lib.KERNEL_TC5_WIDE:
+        return None
     if not (_DYNAMIC["on"] if dynamic is None else dynamic):
         return None
     tiles = (args.sq + 127) // 128
@@ -193,7 +235,7 @@ def _dense_args(q, k, v, mask, key_lengths, causal, scale, kernel):
 
 
 def sdpa_forward(q, k, v, mask=None, key_lengths=None, causal=False, scale=None,
-                 need_lse=True, kernel="auto", lse_rows=None, dynamic=None):
+                 need_lse=True, kernel="auto", lse_rows=None, dynamic=None, out=None):
     """Dense attention forward: out [B, H, Sq, Dv] bf16 and, with need_lse, the row
     log-sum-exp [B, H, lse_rows or Sq] fp32 (natural log).
 
@@ -206,7 +248,10 @@ def sdpa_forward(q, k, v, mask=None, key_lengths=None, causal=False, scale=None,
     q, k, v = _rows_contiguous(q), _rows_contiguous(k), _rows_contiguous(v)
     args, keep = _dense_args(q, k, v, mask, key_lengths, causal, scale, kernel)
     with torch.cuda.device(q.device):
-        out = _out_like_query(q, v.shape[3])
+        if out is None:
+            out = _out_like_query(q, v.shape[3])
+        elif out.shape != (q.shape[0], q.shape[1], q.shape[2], v.shape[3]) or out.dtype != q.dtype or out.stride(3) != 1:
+            raise ValueError("kohaku_tt_b200.sdpa_forward: `out` must be [B, H, Sq, Dv] in q's dtype with a unit last stride")
         args.out = out.data_ptr()
         _set3(args.out_strides, _bhs_strides(out))
         lse = None

@@ -10,6 +10,7 @@ src/kohakutt/tools/kernel_audit.py:20-41). Those two are restated here, per surf
   ruler_varlen     tests/hardware/ops/test_flash_varlen.py:62-73 (per-sequence loop,
                    causal mask arange(m) < arange(n) + 1 + m - n)
   ruler_lse        test_flash.py:307-317 (logsumexp of the float64 scores)
+  ruler_rows       the same definition evaluated for sampled query rows of one pair
   grads_*          float64 autograd of the rulers (test_flash.py:197-215)
   cpu_*            the same calls on the bf16 CPU tensors (the reference's CPU path)
 
@@ -92,6 +93,25 @@ def ruler_lse(q, k, v, mask=None, causal=False, scale=None, lengths=None):
         keep = length_mask(torch.as_tensor(lengths), q.shape[2], k.shape[2], False)
         s = s.masked_fill(~keep, -math.inf)
     return torch.logsumexp(s, dim=-1)
+
+
+def ruler_rows(q, k, v, rows, shift=0, causal=False, scale=None, klen=None):
+    """float64 attention of a few query rows of ONE (batch, head): q [Sq, D] (or the rows
+    already picked, [len(rows), D]), k [Sk, D], v [Sk, Dv] -> (out [len(rows), Dv], lse).
+    Row i sees keys j <= i + shift when causal (shift = Lk - Lq is the bottom-right
+    alignment of varlen_plan.hpp:69-70, 0 the top-left one) and j < klen. For the sizes
+    whose full float64 score matrix does not fit (S 4096 and up, the 131,072-token ring):
+    each sampled row costs one [Sk, D] product."""
+    rows = torch.as_tensor(rows, dtype=torch.long)
+    qr = q if q.shape[0] == rows.numel() and q.shape[0] != k.shape[0] else q[rows]
+    sc = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    s = qr.double() @ k.double().T * sc
+    keys = torch.arange(k.shape[0])
+    if causal:
+        s = s.masked_fill(keys[None, :] > rows[:, None] + shift, -math.inf)
+    if klen is not None:
+        s = s.masked_fill(keys[None, :] >= klen, -math.inf)
+    return torch.softmax(s, dim=-1) @ v.double(), torch.logsumexp(s, dim=-1)
 
 
 def grads_dense(q, k, v, dout, mask=None, causal=False, scale=None, lengths=None, dtype=torch.float64):

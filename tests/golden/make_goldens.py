@@ -11,6 +11,8 @@ Sources of truth used, all the reference's own code:
   kohakutt.torch_backend.lengths.device_lengths        -> device_lengths.json
   kohakutt.torch_backend.varlen.key_mask               -> key_mask.pt
   ktt_flash/varlen_plan.hpp via oracle/_ref/varlen_plan -> varlen_plan.json
+  ktt.rotary's composite (csrc/aten/nn/aten_fused.cpp:30-43), a sequence of aten ops:
+  the same aten calls issued one by one on CPU tensors  -> rotary.pt
 
 Inputs are seeded exactly as the reference's tests seed theirs
 (tests/hardware/ops/test_flash.py:48-53): torch.Generator().manual_seed(seed), randn in
@@ -70,7 +72,36 @@ def cumulative(lengths):
     return out
 
 
+# Rotary cases: (x shape [B, H, S, D], rows of the cos / sin table, seed). The table has
+# more rows than S so that the composite's narrow(-2, 0, S) does something.
+ROTARY_CASES = [((2, 4, 7, 64), 16, 300), ((1, 2, 1, 128), 1, 301), ((3, 2, 33, 32), 40, 302)]
+
+
+def aten_rotary(x, cos, sin):
+    """The aten calls of rotary_composite (csrc/aten/nn/aten_fused.cpp:30-43), one per
+    line and in its order, on CPU tensors."""
+    s = x.size(-2)
+    xf = torch.ops.aten.to.dtype(x, torch.float32)
+    halves = torch.ops.aten.chunk.default(xf, 2, -1)
+    rotated = torch.ops.aten.cat.default([torch.ops.aten.neg.default(halves[1]), halves[0]], -1)
+    c = torch.ops.aten.to.dtype(torch.ops.aten.narrow.default(cos, -2, 0, s), torch.float32)
+    n = torch.ops.aten.to.dtype(torch.ops.aten.narrow.default(sin, -2, 0, s), torch.float32)
+    total = torch.ops.aten.add.Tensor(torch.ops.aten.mul.Tensor(xf, c), torch.ops.aten.mul.Tensor(rotated, n))
+    return torch.ops.aten.to.dtype(total, x.dtype)
+
+
+def rotary_fixture():
+    out = {}
+    for idx, (shape, rows, seed) in enumerate(ROTARY_CASES):
+        (x,) = seeded([shape], seed)
+        ang = seeded([(rows, shape[-1])], seed + 50, torch.float32)[0]
+        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        out[f"case{idx}"] = {"x": x, "cos": cos, "sin": sin, "y": aten_rotary(x, cos, sin)}
+    torch.save(out, os.path.join(HERE, "rotary.pt"))
+
+
 def main():
+    rotary_fixture()
     import kohakutt  # noqa: F401  (the reference package; AVAILABLE is False without a card)
     from kohakutt.core.stats import diff_stats
     from kohakutt.torch_backend import lengths as ref_lengths

@@ -25,16 +25,17 @@ FORWARD = [
 
 def _kernels_for(d, dv=None):
     dv = d if dv is None else dv
-    return ["mma", "flash"] if (d == dv and d in (64, 128)) else ["mma"]
+    if d != dv or d not in (64, 128):
+        return ["mma"]
+    # Head dim 64 has two tcgen05 forwards: 'flash' (two streams per SM) and 'flash_wide'.
+    return ["mma", "flash", "flash_wide"] if d == 64 else ["mma", "flash"]
 
 
 def _forward(kernel, q, k, v, **kw):
-    try:
-        return ops.sdpa_forward(q, k, v, kernel=kernel, **kw)
-    except _lib.UnsupportedAttention:
-        if kernel == "flash":
-            pytest.skip("the tcgen05 kernel does not take this call")
-        raise
+    """Every shape these tests hand the tcgen05 kernel (D == Dv in {64, 128}, aligned
+    contiguous operands, no mask or a one-row mask) is one it must take: a refusal raises
+    and fails the test."""
+    return ops.sdpa_forward(q, k, v, kernel=kernel, **kw)
 
 
 @pytest.mark.parametrize("b,h,hk,s,d,causal", FORWARD)
@@ -42,11 +43,7 @@ def test_forward_shapes(cuda, b, h, hk, s, d, causal):
     q, k, v = qkv(b, h, hk, s, s, d, b + h + s + d)
     ruler = ao.ruler_dense(q, k, v, causal=causal)
     for kernel in _kernels_for(d):
-        try:
-            out, lse = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal, kernel=kernel)
-        except _lib.UnsupportedAttention:
-            assert kernel == "flash"
-            continue
+        out, lse = _forward(kernel, q.to(cuda), k.to(cuda), v.to(cuda), causal=causal)
         assert out.shape == ruler.shape and out.dtype == torch.bfloat16
         assert rel(out, ruler) <= FWD_BOUND, kernel
         assert rms(lse, ao.ruler_lse(q, k, v, causal=causal)) <= LSE_RMS, kernel
@@ -147,11 +144,7 @@ def test_rectangular_causal_is_top_left(cuda, b, h, hk, sq, sk, d):
     q, k, v = qkv(b, h, hk, sq, sk, d, sq + sk)
     ruler = ao.ruler_dense(q, k, v, causal=True)
     for kernel in _kernels_for(d):
-        try:
-            out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), causal=True, kernel=kernel)
-        except _lib.UnsupportedAttention:
-            assert kernel == "flash"
-            continue
+        out, _ = _forward(kernel, q.to(cuda), k.to(cuda), v.to(cuda), causal=True)
         assert rel(out, ruler) <= FWD_BOUND, kernel
 
 
@@ -172,12 +165,8 @@ def test_backward_shapes(cuda, b, h, hk, s, d, causal):
     qc, kc, vc, doc = (t.to(cuda) for t in (q, k, v, do))
     out, lse = ops.sdpa_forward(qc, kc, vc, causal=causal)
     assert rel(out, ruler) <= FWD_BOUND
-    for kernel in _kernels_for(d):
-        try:
-            gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, causal=causal, kernel=kernel)
-        except _lib.UnsupportedAttention:
-            assert kernel == "flash"
-            continue
+    for kernel in ("mma", "flash") if d in (64, 128) else ("mma",):
+        gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, causal=causal, kernel=kernel)
         assert gk.shape == k.shape and gv.shape == v.shape
         for name, got, want in (("dq", gq, dq), ("dk", gk, dk), ("dv", gv, dv)):
             assert rel(got, want) <= GRAD_BOUND, (kernel, name)
@@ -223,10 +212,7 @@ def test_no_mixing_across_batch_head_pairs(cuda):
     v = (v.float() * (1 + pair)).to(torch.bfloat16)
     ruler = ao.ruler_dense(q, k, v)
     for kernel in ("mma", "flash"):
-        try:
-            out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), kernel=kernel)
-        except _lib.UnsupportedAttention:
-            continue
+        out, _ = _forward(kernel, q.to(cuda), k.to(cuda), v.to(cuda))
         for i in range(0, b, 3):
             for j in range(0, h, 5):
                 assert rel(out[i, j], ruler[i, j]) <= FWD_BOUND
@@ -243,10 +229,7 @@ def test_head_views_are_read_in_place_and_output_follows(cuda):
     xc = x.to(cuda).view(b, s, 3, h, d)
     qc, kc, vc = (xc[:, :, i].transpose(1, 2) for i in range(3))
     for kernel in ("mma", "flash"):
-        try:
-            out, _ = ops.sdpa_forward(qc, kc, vc, kernel=kernel)
-        except _lib.UnsupportedAttention:
-            continue
+        out, _ = _forward(kernel, qc, kc, vc)
         assert out.transpose(1, 2).is_contiguous()
         assert rel(out, ruler) <= FWD_BOUND
 
@@ -309,17 +292,18 @@ def test_long_causal_work_lists(cuda, b, h, hk, s, d):
 
 def test_counter_driven_work_gives_the_same_bits(cuda):
     """Which CTA draws an item does not touch the item's arithmetic: with the work counter
-    the tcgen05 forward returns exactly what the fixed deal returns (dense, packed-style
-    ragged sizes, masked row)."""
+    the one-CTA-per-SM tcgen05 forward returns exactly what the fixed deal returns (dense,
+    packed-style ragged sizes)."""
     old = ops.dynamic_work(False)
     try:
         for b, h, hk, s, d, causal in [(2, 8, 2, 1000, 64, True), (1, 16, 16, 2048, 128, True), (3, 4, 4, 300, 64, False)]:
             q, k, v = (t.to(cuda) for t in qkv(b, h, hk, s, s, d, b + h + s + d))
-            want, want_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash")
+            kernel = "flash_wide" if d == 64 else "flash"
+            want, want_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel=kernel)
             ops.dynamic_work(True, 0)
-            got, got_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash")
+            got, got_lse = ops.sdpa_forward(q, k, v, causal=causal, kernel=kernel)
             ops.dynamic_work(False)
-            again, _ = ops.sdpa_forward(q, k, v, causal=causal, kernel="flash", dynamic=True)
+            again, _ = ops.sdpa_forward(q, k, v, causal=causal, kernel=kernel, dynamic=True)
             assert torch.equal(got, want) and torch.equal(got_lse, want_lse) and torch.equal(again, want)
         torch.cuda.synchronize()
         _lib.device_status()

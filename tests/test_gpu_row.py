@@ -1,0 +1,99 @@
+"""The head-dim-64 forward kernel (two streams per SM; on small launches the two streams of
+a CTA share a query tile, half of its key blocks each) against the float64 ruler and the
+warp-MMA kernel, at the benchmark's own sizes."""
+
+import math
+
+import pytest
+import torch
+
+from kohaku_tt_b200 import _lib, ops
+from tests.gpu_util import FWD_BOUND, LSE_RMS, qkv, rel, rms
+
+pytestmark = pytest.mark.gpu
+
+
+def _sampled_rows_ruler(q, k, v, bi, hi, rows, causal):
+    """float64 attention of a few query rows of one (batch, head)."""
+    group = q.shape[1] // k.shape[1]
+    kk, vv = k[bi, hi // group].double(), v[bi, hi // group].double()
+    scores = (q[bi, hi, rows].double() @ kk.T) / math.sqrt(q.shape[-1])
+    if causal:
+        scores = scores.masked_fill(torch.arange(k.shape[2])[None, :] > rows[:, None], float("-inf"))
+    return torch.softmax(scores, dim=-1) @ vv, torch.logsumexp(scores, dim=-1)
+
+
+def test_two_streams_fit_one_sm(cuda):
+    assert _lib.lib().ktt_b200_forward_streams_per_sm() == 2
+
+
+# (b, h, hk, s, causal): the headline shape (tiles are cut: 224 tiles on 296 CTA slots), its
+# batch-8 form (whole tiles, several per CTA), SDXL self-attention's shape, ragged sizes.
+@pytest.mark.parametrize("b,h,hk,s,causal", [
+    (1, 14, 2, 2048, True), (8, 14, 2, 2048, True), (2, 10, 10, 4096, False),
+    (1, 4, 4, 1000, True), (3, 4, 1, 300, False), (1, 2, 2, 129, True),
+])
+def test_against_the_warp_mma_kernel_and_float64_rows(cuda, b, h, hk, s, causal):
+    q, k, v = qkv(b, h, hk, s, s, 64, b + h + s)
+    qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
+    for _ in range(3):  # repeated: which CTA draws which unit differs from launch to launch
+        out, lse = ops.sdpa_forward(qc, kc, vc, causal=causal, kernel="flash")
+    torch.cuda.synchronize()
+    _lib.device_status()
+    ref, ref_lse = ops.sdpa_forward(qc, kc, vc, causal=causal, kernel="mma")
+    assert rel(out.float(), ref.float()) <= 4e-3
+    assert (lse - ref_lse).abs().max().item() <= 2e-3
+    rows = torch.tensor(sorted({0, 1, 127, 128, s // 2, s - 129 if s > 129 else 0, s - 1}))
+    for bi, hi in ((0, 0), (b - 1, h - 1)):
+        ruler, ruler_lse = _sampled_rows_ruler(q, k, v, bi, hi, rows, causal)
+        assert rel(out[bi, hi, rows.to(cuda)].cpu(), ruler) <= FWD_BOUND
+        assert rms(lse[bi, hi, rows.to(cuda)], ruler_lse) <= LSE_RMS
+
+
+def test_shared_tiles_give_the_same_bits_every_time(cuda):
+    # 224 tiles on 148 SMs: every tile is shared by the two streams of a CTA. Which CTA draws
+    # which tile differs from launch to launch; the bits must not.
+    q, k, v = (t.to(cuda) for t in qkv(1, 14, 2, 2048, 2048, 64, 5))
+    first, first_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    for _ in range(6):
+        out, lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+        assert torch.equal(out, first) and torch.equal(lse, first_lse)
+    # The fixed deal (no workspace) shares the tiles the same way: the same bits again.
+    fixed, fixed_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash", dynamic=False)
+    assert torch.equal(fixed, first) and torch.equal(fixed_lse, first_lse)
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
+def test_drawn_work_equals_the_fixed_deal_for_whole_tiles(cuda):
+    # 1,792 tiles: each stream takes whole tiles; who draws a tile does not touch its arithmetic.
+    q, k, v = (t.to(cuda) for t in qkv(8, 14, 2, 2048, 2048, 64, 6))
+    drawn, drawn_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    fixed, fixed_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash", dynamic=False)
+    assert torch.equal(drawn, fixed) and torch.equal(drawn_lse, fixed_lse)
+
+
+def test_the_workspace_is_left_zeroed(cuda):
+    q, k, v = (t.to(cuda) for t in qkv(1, 14, 2, 2048, 2048, 64, 7))
+    ops.drop_forward_workspaces()
+    ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    torch.cuda.synchronize()
+    (buf,) = ops._FORWARD_WORKSPACE.values()
+    assert int(buf.to(torch.int32).abs().sum()) == 0
+
+
+def test_key_lengths_and_one_row_masks_on_shared_tiles(cuda):
+    import kohaku_tt_b200 as ktt
+    from oracle import attention_oracle as ao
+
+    b, h, hk, s = 2, 4, 2, 1500
+    q, k, v = qkv(b, h, hk, s, s, 64, 8)
+    lengths = [1500, 700]
+    out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), kernel="flash",
+                              key_lengths=torch.tensor(lengths, dtype=torch.int32, device=cuda))
+    assert rel(out, ao.ruler_lengths(q, k, v, lengths)) <= FWD_BOUND
+    keep = torch.rand(b, 1, 1, s, generator=torch.Generator().manual_seed(3)) > 0.3
+    keep[..., 0] = True
+    out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), mask=keep.to(cuda), kernel="flash")
+    assert rel(out, ao.ruler_dense(q, k, v, mask=keep)) <= FWD_BOUND
+    assert ktt.counters()["attention_flash"] > 0

@@ -241,3 +241,117 @@ def test_sdxl_style_block_compiled_equals_eager(cuda):
     assert d1.get("attention_flash", 0) + d1.get("attention_mma", 0) == 2   # both attentions ran here
     assert torch.equal(compiled, eager)
     assert rel(eager, want) <= 3e-2   # bf16 linears around the attention
+
+
+def test_sdpa_kernel_math_selects_math(cuda):
+    # tests/hardware/ops/test_attention.py:63-67: torch's own switch wins over the shapes.
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    q, k, v = (t.to(cuda) for t in qkv(1, 2, 2, 64, 64, 64, 1))
+    assert torch.ops.aten._fused_sdp_choice(q, k, v, None, 0.0, False) == 4
+    with sdpa_kernel(SDPBackend.MATH):
+        assert torch.ops.aten._fused_sdp_choice(q, k, v, None, 0.0, False) == 0
+        # ... and PyTorch's math composite then runs the call: none of the kernels here does.
+        before = ktt.counters()
+        out = F.scaled_dot_product_attention(q, k, v, dropout_p=0.0)
+        assert _delta(before) == {}
+    assert rel(out, ao.ruler_dense(q.cpu(), k.cpu(), v.cpu())) <= FWD_BOUND
+    assert torch.ops.aten._fused_sdp_choice(q, k, v, None, 0.0, False) == 4
+
+
+@pytest.mark.parametrize("bias_shape", [(2, 1, 96, 96), (1, 4, 1, 96)])
+def test_bias_gradient_matches_float64_autograd(cuda, bias_shape):
+    # aten_attention.cpp:781-811: dS summed over the dims the bias broadcasts.
+    b, h, s, d = 2, 4, 96, 64
+    q, k, v, do = qkv(b, h, h, s, s, d, 21, extra=1)
+    bias = torch.randn(bias_shape, generator=torch.Generator().manual_seed(22)).to(torch.bfloat16)
+    qd, kd, vd, bd = (t.double().requires_grad_(True) for t in (q, k, v, bias))
+    ruler = F.scaled_dot_product_attention(qd, kd, vd, attn_mask=bd)
+    ruler.backward(do.double())
+    qc, kc, vc, bc = (t.to(cuda).requires_grad_(True) for t in (q, k, v, bias))
+    before = ktt.counters()
+    out = F.scaled_dot_product_attention(qc, kc, vc, attn_mask=bc)
+    out.backward(do.to(cuda))
+    assert _delta(before).get("attention_backward") == 1
+    assert rel(out, ruler.detach()) <= FWD_BOUND
+    assert bc.grad is not None and bc.grad.shape == bias.shape
+    assert rel(bc.grad, bd.grad) <= GRAD_BOUND
+    for got, want in ((qc.grad, qd.grad), (kc.grad, kd.grad), (vc.grad, vd.grad)):
+        assert rel(got, want) <= GRAD_BOUND
+
+
+def test_inductor_compiles_forward_backward_and_key_lengths(cuda):
+    """tests/hardware/ops/test_sdpa_kernel.py:215-224 compiles with the product's real
+    backend; here that is inductor, which trusts the strides the meta kernels promise."""
+    q, k, v, do = qkv(2, 4, 2, 256, 256, 64, 12, extra=1)
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, causal=True)
+    qc, kc, vc = (t.to(cuda).requires_grad_(True) for t in (q, k, v))
+    fn = torch.compile(lambda a, b, c: F.scaled_dot_product_attention(a, b, c, is_causal=True, enable_gqa=True) * 2.0,
+                       backend="inductor", fullgraph=True)
+    before = ktt.counters()
+    out = fn(qc, kc, vc)
+    out.backward(do.to(cuda))
+    d = _delta(before)
+    assert d.get("attention_backward") == 1 and d.get("attention_flash", 0) + d.get("attention_mma", 0) == 1
+    assert rel(out, 2.0 * ruler) <= FWD_BOUND
+    for got, want in ((qc.grad, dq), (kc.grad, dk), (vc.grad, dv)):
+        assert rel(got, 2.0 * want) <= GRAD_BOUND
+
+    # A masked call with contiguous q takes the efficient overload, whose output is laid out
+    # [B, Sq, H, Dv]: the compiled graph must index it the way its meta kernel says.
+    keep = torch.ones(2, 1, 1, 256, dtype=torch.bool, device=cuda)
+    keep[..., 200:] = False
+    masked = torch.compile(lambda a, b, c, m: F.scaled_dot_product_attention(a, b, c, attn_mask=m, enable_gqa=True) + 1.0,
+                           backend="inductor", fullgraph=True)
+    with torch.no_grad():
+        got = masked(qc, kc, vc, keep)
+        want = F.scaled_dot_product_attention(qc, kc, vc, attn_mask=keep, enable_gqa=True) + 1.0
+    assert torch.equal(got, want)
+    assert rel(got - 1.0, ao.ruler_dense(q, k, v, mask=keep.cpu())) <= 2e-2   # the + 1 costs bf16 bits
+
+    # ktt.sdpa(key_lengths=) on a head view: the fake kernel promises the real op's layout.
+    x = ao.make_inputs([(2, 96, 3 * 4 * 64)], 16)[0].to(cuda).view(2, 96, 3, 4, 64)
+    qh, kh, vh = (x[:, :, i].transpose(1, 2) for i in range(3))
+    n = torch.tensor([96, 40], dtype=torch.int32, device=cuda)
+    lengths_fn = torch.compile(lambda a, b, c, m: ktt.sdpa(a, b, c, key_lengths=m) * 1.0, backend="inductor", fullgraph=True)
+    with torch.no_grad():
+        assert torch.equal(lengths_fn(qh, kh, vh, n), ktt.sdpa(qh, kh, vh, key_lengths=n))
+
+
+def test_refused_calls_say_how_to_reach_the_math_route_and_uninstall_restores_torch(cuda):
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    q, k, v = (t.to(cuda) for t in qkv(1, 2, 2, 64, 64, 64, 1))
+    with pytest.raises(NotImplementedError, match="sdpa_kernel"):
+        torch.ops.aten._scaled_dot_product_flash_attention(q, k, v, 0.1, False)
+    # The route the message names: dropout under the math backend runs PyTorch's composite.
+    with sdpa_kernel(SDPBackend.MATH):
+        assert F.scaled_dot_product_attention(q, k, v, dropout_p=0.1).shape == q.shape
+    ktt.uninstall()
+    try:
+        before = ktt.counters()
+        out = F.scaled_dot_product_attention(q, k, v)   # PyTorch's own CUDA kernel again
+        assert _delta(before) == {}
+        assert rel(out, ao.ruler_dense(q.cpu(), k.cpu(), v.cpu())) <= FWD_BOUND
+    finally:
+        ktt.install()
+    before = ktt.counters()
+    F.scaled_dot_product_attention(q, k, v)
+    assert sum(_delta(before).values()) == 1
+
+
+def test_packed_rows_without_keys_are_defined(cuda):
+    """Device offsets are not checked on the torch_attn route: a causal sequence with more
+    queries than keys gives its first Lq - Lk rows no key. Those rows come back as zeros
+    with lse = -inf, and their gradients are zero."""
+    from kohaku_tt_b200 import ops
+
+    lq, lk = [40, 7], [25, 7]
+    q, k, v, do = packed(lq, lk, 2, 2, 64, 31, extra=1)
+    out, lse = ops.varlen_forward(q.to(cuda), k.to(cuda), v.to(cuda), cu(lq, cuda), cu(lk, cuda), 40, 25, causal=True)
+    assert torch.count_nonzero(out[:15]) == 0 and torch.isinf(lse[:, :15]).all() and (lse[:, :15] < 0).all()
+    assert torch.isfinite(out).all() and torch.isfinite(lse[:, 15:]).all()
+    gq, gk, gv = ops.varlen_backward(do.to(cuda), q.to(cuda), k.to(cuda), v.to(cuda), out, lse,
+                                     cu(lq, cuda), cu(lk, cuda), 40, 25, causal=True)
+    assert torch.count_nonzero(gq[:15]) == 0
+    assert all(torch.isfinite(g).all() for g in (gq, gk, gv))

@@ -35,11 +35,8 @@ def test_forward_sets(cuda, lengths, h, hk, d, causal):
     ruler = ao.ruler_varlen(q, k, v, c, c, causal=causal)
     kernels = ["mma", "flash"] if d in (64, 128) else ["mma"]
     for kernel in kernels:
-        try:
-            out, lse = _run_forward(cuda, q, k, v, lengths, lengths, causal, kernel)
-        except _lib.UnsupportedAttention:
-            assert kernel == "flash"
-            continue
+        # Packed D 64 / 128 operands are aligned: a tcgen05 refusal raises and fails here.
+        out, lse = _run_forward(cuda, q, k, v, lengths, lengths, causal, kernel)
         assert out.shape == ruler.shape
         assert rel(out, ruler) <= FWD_BOUND, kernel
         for b in range(len(lengths)):  # per sequence: 3e-2 (test_flash_varlen.py:86-93)
@@ -113,12 +110,8 @@ def test_backward_sets(cuda, lq, lk, h, hk, d, causal):
     out, lse = ops.varlen_forward(qc, kc, vc, cu(lq, cuda), cu(lk, cuda), max(lq), max(lk), causal=causal)
     assert rel(out, ruler) <= FWD_BOUND
     for kernel in (["mma", "flash"] if d in (64, 128) else ["mma"]):
-        try:
-            gq, gk, gv = ops.varlen_backward(doc, qc, kc, vc, out, lse, cu(lq, cuda), cu(lk, cuda),
-                                             max(lq), max(lk), causal=causal, kernel=kernel)
-        except _lib.UnsupportedAttention:
-            assert kernel == "flash"
-            continue
+        gq, gk, gv = ops.varlen_backward(doc, qc, kc, vc, out, lse, cu(lq, cuda), cu(lk, cuda),
+                                         max(lq), max(lk), causal=causal, kernel=kernel)
         for name, got, want in (("dq", gq, dq), ("dk", gk, dk), ("dv", gv, dv)):
             assert rel(got, want) <= VARLEN_GRAD_BOUND, (kernel, name)
         for b, n in enumerate(lq):
