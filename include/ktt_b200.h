@@ -168,13 +168,22 @@ KTT_B200_API int ktt_b200_reset_counters(void);
  * after synchronising the stream; the next forward call also checks it. */
 KTT_B200_API int ktt_b200_device_status(int* code);
 
+/* Test support for the report above: launches one warp that waits, with a limit of ~1e5
+ * cycles, on a barrier nobody arrives at. The wait gives up (code 999), the kernel returns
+ * normally and the device stays healthy; after a synchronize ktt_b200_device_status reports
+ * KTT_B200_ERR_DEVICE_WAIT, as does the next tcgen05 launch. Nothing faults, traps or spins
+ * for longer than the limit. */
+KTT_B200_API int ktt_b200_selftest_wait_timeout(void* stream);
+
 /* Profiling zones, the counterpart of the reference's FLASH_PROFILE device zones
  * (ktt_flash/compute.cpp:25-30, program.hpp:56-65): with a device buffer of 64 x 8 int64
  * set, CTA (0, 0, 0) of every tcgen05 forward launch stamps clock64 per key block (slots:
  * S ready, pass 1 done, previous P V done, pass 2 done, P published, MMA lane before the
  * next Q K^T, after the wait for P, after issuing P V), and rows 64 .. 64 + 1023 receive per
  * CTA its start and end on the global nanosecond timer, its SM and its key-block count; the
- * buffer then holds (64 + 1024) x 8 int64. NULL turns it off (default). */
+ * buffer then holds (64 + 1024) x 8 int64. The decode kernel writes, per CTA, rows 64.. with
+ * six nanosecond stamps: start, dependency wait over, lengths scanned, first tile landed,
+ * stream done, end. NULL turns it off (default). */
 KTT_B200_API int ktt_b200_set_trace(void* device_buffer);
 
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward

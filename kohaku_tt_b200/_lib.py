@@ -14,6 +14,8 @@ CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
 LIB_DIR = os.path.join(_HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libktt_b200.so")
+# Extra nvcc flags for experiments (for example -DKTT_ROW_POLY_PAIRS=3); empty in normal use.
+EXTRA_NVCC_FLAGS = os.environ.get("KTT_B200_NVCC_FLAGS", "").split()
 
 NVCC_FLAGS = [
     "-gencode",
@@ -42,6 +44,7 @@ EXPORTS = (
     "ktt_b200_counters",
     "ktt_b200_reset_counters",
     "ktt_b200_device_status",
+    "ktt_b200_selftest_wait_timeout",
     "ktt_b200_set_trace",
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
@@ -175,7 +178,7 @@ def build(force=False, verbose=False):
         raise RuntimeError("kohaku_tt_b200: nvcc not found; cannot build libktt_b200.so")
     os.makedirs(LIB_DIR, exist_ok=True)
     tmp = LIB_PATH + ".tmp"
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", tmp, *sources()]
+    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_NVCC_FLAGS, "-I", INCLUDE, "-o", tmp, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -187,6 +190,55 @@ def build(force=False, verbose=False):
     if verbose:
         print(proc.stderr)
     return LIB_PATH
+
+
+SHIM_SRC = os.path.join(CSRC, "torch_shim", "aten_shim.cpp")
+SHIM_PATH = os.path.join(LIB_DIR, "libktt_b200_aten.so")
+
+
+def build_shim(force=False):
+    """Compiles the C++ registration of the aten overloads (csrc/torch_shim/aten_shim.cpp)
+    against the installed torch and libktt_b200.so. Returns its path."""
+    import torch
+    from torch.utils import cpp_extension
+
+    deps = [SHIM_SRC, os.path.join(INCLUDE, "ktt_b200.h")]
+    if not force and os.path.exists(SHIM_PATH) and all(os.path.getmtime(d) <= os.path.getmtime(SHIM_PATH) for d in deps):
+        return SHIM_PATH
+    build()
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    tmp = SHIM_PATH + ".tmp"
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    for inc in cpp_extension.include_paths():
+        cmd += ["-I", inc]
+    cmd += ["-I", os.path.join(cuda_home, "include"), SHIM_SRC, "-o", tmp,
+            "-L", torch_lib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+            "-L", LIB_DIR, "-lktt_b200", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("kohaku_tt_b200: g++ failed on the aten shim\n" + proc.stderr[-8000:])
+    os.replace(tmp, SHIM_PATH)
+    return SHIM_PATH
+
+
+_SHIM = None
+
+
+def shim():
+    """The loaded C++ registration shim, or None when it has not been built (the Python
+    registration of aten.py then stands in)."""
+    global _SHIM
+    if _SHIM is None and os.path.exists(SHIM_PATH):
+        lib()
+        import torch  # noqa: F401  (its libraries must be loaded first)
+
+        handle = ctypes.CDLL(SHIM_PATH)
+        handle.ktt_b200_aten_set_scope.argtypes = [ctypes.c_int, ctypes.c_char_p]
+        handle.ktt_b200_aten_set_scope.restype = None
+        _SHIM = handle
+    return _SHIM
 
 
 _LIB = None
@@ -225,6 +277,7 @@ def lib():
     handle.ktt_b200_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
     handle.ktt_b200_decode_append.argtypes = [ctypes.POINTER(DecodeAppendArgs), _ptr]
     handle.ktt_b200_set_trace.argtypes = [_ptr]
+    handle.ktt_b200_selftest_wait_timeout.argtypes = [_ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]
     if handle.ktt_b200_abi_version() != 1:
         raise RuntimeError("kohaku_tt_b200: libktt_b200.so has another ABI version")

@@ -366,19 +366,62 @@ def _varlen_backward(grad_out, query, key, value, out, lse, cu_seq_q, cu_seq_k, 
                                causal=causal, scale=scale)
 
 
-def install():
+_VARLEN_DONE = False
+_USING_SHIM = False
+
+
+def using_cpp_registration():
+    """True when the aten overloads are registered from C++ (csrc/torch_shim), False when
+    the Python registration below stands in."""
+    return _INSTALLED and _USING_SHIM
+
+
+def install(python=None):
     """Points the CUDA kernels of the aten fused-SDPA overloads, `_fused_sdp_choice` and
     torch's packed varlen ops at this package. Idempotent. Raises when the library is
-    missing: a silent PyTorch route would defeat the point of installing."""
-    global _ATEN, _INSTALLED
+    missing: a silent PyTorch route would defeat the point of installing.
+
+    The overloads are registered from C++ (a TORCH_LIBRARY-style block in
+    csrc/torch_shim/aten_shim.cpp, as the reference registers its own,
+    aten_attention.cpp:959-974) when that shim has been built; `python=True` (or the
+    environment variable KTT_B200_PYTHON_ATEN=1) asks for the Python registration below,
+    which is also the stand-in when the shim is missing."""
+    global _ATEN, _INSTALLED, _VARLEN_DONE, _USING_SHIM
     if _INSTALLED:
         return
     _lib.lib()
+    import os
     import warnings
 
+    if python is None:
+        python = os.environ.get("KTT_B200_PYTHON_ATEN", "0") == "1"
+    handle = None if python else _lib.shim()
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")  # "overriding a previously registered kernel"
-        _ATEN = torch.library.Library("aten", "IMPL")
+        if handle is not None:
+            if handle.ktt_b200_aten_install() != 0:
+                raise RuntimeError("kohaku_tt_b200: the C++ registration of the aten overloads failed")
+            _USING_SHIM = True
+            from .numerics import _tell_shim
+
+            _tell_shim()
+        else:
+            _USING_SHIM = False
+            _register_python()
+        if not _VARLEN_DONE:
+            from torch.nn.attention import varlen
+
+            varlen._varlen_attn.register_kernel("cuda")(_varlen_forward)
+            varlen._varlen_attn_backward.register_kernel("cuda")(_varlen_backward)
+            _VARLEN_DONE = True
+    _INSTALLED = True
+
+
+def _register_python():
+    """The same overloads registered from Python (torch.library)."""
+    global _ATEN
+    _ATEN = torch.library.Library("aten", "IMPL")
+    if True:
         table = {
             "_scaled_dot_product_flash_attention": _flash_forward,
             "_scaled_dot_product_flash_attention_backward": _flash_backward,
@@ -392,21 +435,19 @@ def install():
         }
         for name, fn in table.items():
             _ATEN.impl(name, fn, "CUDA")
-        from torch.nn.attention import varlen
-
-        varlen._varlen_attn.register_kernel("cuda")(_varlen_forward)
-        varlen._varlen_attn_backward.register_kernel("cuda")(_varlen_backward)
-    _INSTALLED = True
 
 
 def uninstall():
     """Takes the aten overloads of install() back out: PyTorch's own CUDA kernels answer
     again. (The packed varlen ops of torch.nn.attention.varlen keep this package's kernels:
     custom-op kernels cannot be unregistered.)"""
-    global _ATEN, _INSTALLED
+    global _ATEN, _INSTALLED, _USING_SHIM
     if _ATEN is not None:
         _ATEN._destroy()
         _ATEN = None
+    if _USING_SHIM:
+        _lib.shim().ktt_b200_aten_uninstall()
+        _USING_SHIM = False
     _INSTALLED = False
 
 

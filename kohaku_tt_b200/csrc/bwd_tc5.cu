@@ -23,7 +23,8 @@
 //
 // Ten warps per CTA: warps 0-7 are two groups of 128 threads (one thread per TMEM lane, each
 // group owning 64 of the block's 128 score columns), warp 8 issues MMAs, warp 9 issues TMA.
-// Every mbarrier wait is bounded as in the forward kernel.
+// Every wait is a bounded mbarrier wait as in the forward kernel, the meetings of the score
+// warps included. Optional per call: key lengths, a mask of one row per (batch, head).
 //
 // Overlap: the scores have two buffers in tensor memory wherever 128 columns are left (the dQ
 // kernel at both head dims, the dK/dV kernel at D 64), so the score MMA of item i + 1 runs
@@ -47,7 +48,6 @@ struct BwdParams {
     int dim_of[4][3];  // q, k, v, dout: tensor-map coordinate slot of row, head, batch
 };
 
-__device__ __forceinline__ void named_barrier_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Shared-memory plan: a resident pair of tiles (A0, A1), a ring of streamed pairs (B0, B1),
 // two double-buffered vectors of 128 floats, barriers.
@@ -60,8 +60,8 @@ struct BwdPlan {
     static constexpr int kA1 = kA0 + kSub * kTile;
     static constexpr int kB0 = kA1 + kSub * kTile;
     static constexpr int kB1 = kB0 + kStages * kSub * kTile;
-    static constexpr int kVec = kB1 + kStages * kSub * kTile;  // float [2 buffers][2 vectors][128]
-    static constexpr int kBars = kVec + 2 * 2 * 128 * 4;
+    static constexpr int kVec = kB1 + kStages * kSub * kTile;  // float [2 buffers][3 vectors][128]
+    static constexpr int kBars = kVec + 2 * 3 * 128 * 4;
     static constexpr int kBytes = kBars + 256;
     static constexpr int bAFull = 0;
     static constexpr int bBFull = 1;                  // + stage
@@ -70,7 +70,8 @@ struct BwdPlan {
     static constexpr int bDPReady = bSReady + 2;
     static constexpr int bPFull = bDPReady + 1;       // + half
     static constexpr int bDone = bPFull + 2;
-    static constexpr int bCount = bDone + 1;
+    static constexpr int bMeet = bDone + 1;           // the eight score warps meet (bounded, unlike bar.sync)
+    static constexpr int bCount = bMeet + 1;
     static_assert(bCount * 8 + 16 <= 256, "barrier area");
 };
 
@@ -88,6 +89,7 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
     mbar_init(bars + 8 * (P::bPFull + 0), 4);   // one arrival per warp of the group
     mbar_init(bars + 8 * (P::bPFull + 1), 4);
     mbar_init(bars + 8 * P::bDone, 1);
+    mbar_init(bars + 8 * P::bMeet, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -96,7 +98,7 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
 // ---- dK / dV ----------------------------------------------------------------------------
 
 // Body of one dK/dV CTA; (bx, by, bz) = (kv head * gsplit + part, key block, batch).
-template <int D>
+template <int D, bool kMask>
 __device__ __forceinline__ void dkv_body(
     const CUtensorMap* pmap_q, const CUtensorMap* pmap_k, const CUtensorMap* pmap_v, const CUtensorMap* pmap_do,
     const BwdParams& tp, int bx, int by, int bz, int gridDim_y) {
@@ -206,6 +208,19 @@ __device__ __forceinline__ void dkv_body(
             const uint64_t q_mn = smem_desc(sbase + P::kB0, P::kTile, 1024);
             const uint64_t do_mn = smem_desc(sbase + P::kB1, P::kTile, 1024);
             bool ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bAFull), 0, abort_flag, 500, tp.status));
+            if (ok && p.key_lengths && si.klen - k0 < kBM) {
+                // Cache rows past the length may hold anything (0 x inf would poison dK and dV):
+                // blank this CTA's key and value rows past it; their scores are masked anyway.
+                const int first = si.klen - k0;   // > 0 here (nitems > 0)
+                for (int idx = lane; idx < P::kSub * (kBM - first) * 8; idx += 32) {
+                    const int sub = idx / ((kBM - first) * 8), rem = idx % ((kBM - first) * 8);
+                    const int off = sub * P::kTile + (first + rem / 8) * 128 + (rem % 8) * 16;
+                    *reinterpret_cast<uint4*>(smem + P::kA0 + off) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(smem + P::kA1 + off) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_async_smem();
+                __syncwarp();
+            }
             // S^T = K Q^T of item `it` into its score buffer (the previous reader of that
             // buffer, dV of an earlier item, was issued before: MMAs run in issue order).
             auto issue_s = [&](int it) -> bool {
@@ -265,6 +280,25 @@ __device__ __forceinline__ void dkv_body(
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const bool key_ok = kk < si.klen;
         bool ok = true;
+        uint32_t meets = 0;
+        // The eight score warps meet (bounded: a warp that gave up cannot strand the others).
+        auto meet = [&](int code) -> bool {
+            mbar_arrive_warp(bar(P::bMeet));
+            const bool met = __all_sync(0xffffffffu, mbar_wait(bar(P::bMeet), meets & 1, abort_flag, code, tp.status));
+            ++meets;
+            return met;
+        };
+        // A mask of one row per (batch, head): this thread's key has one term per query head.
+        float mterm = 0.f;
+        auto mask_term = [&](int it) {
+            if constexpr (kMask) {
+                if (it % per_head == 0) {
+                    const int h = hk * full_group + g0 + it / per_head;
+                    const int key = max(min(kk, si.klen - 1), 0);
+                    mterm = mask_value(p, b, h, 0, static_cast<int64_t>(si.k_off) + key) * kLog2e;
+                }
+            }
+        };
 
         // Row terms of one item: group 0 threads fetch lse (as base-2, +inf for rows that do
         // not exist or saw no key), group 1 threads fetch delta.
@@ -284,7 +318,9 @@ __device__ __forceinline__ void dkv_body(
             float* lse2 = vec + (it & 1) * 256;
             float* delta = lse2 + 128;
             (g == 0 ? lse2 : delta)[row] = pre;
-            named_barrier_256();
+            ok = meet(630);
+            if (!ok) break;
+            mask_term(it);
             if (it + 1 < nitems) pre = fetch(it + 1);
             const int q0 = (qstart + it % per_head) * kBN;
             const uint32_t tmem_s = tmem_s_of(it);
@@ -309,8 +345,8 @@ __device__ __forceinline__ void dkv_body(
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     const float4 lv = l4[e4];
-                    float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(-lv.x, -lv.y));
-                    float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(-lv.z, -lv.w));
+                    float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
+                    float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
                     if (!whole) {
                         const int col = c * 32 + e4 * 4;
                         x0.x = (key_ok && col >= first_col) ? x0.x : -INFINITY;
@@ -406,7 +442,7 @@ __device__ __forceinline__ void dkv_body(
             // parts (deterministic, the same sums whoever is last) and writes bf16.
             // Every score thread comes here, whatever its waits returned.
             int* last_flag = reinterpret_cast<int*>(vec);
-            named_barrier_256();  // all partial stores of this CTA are done
+            bool met = meet(640);  // all partial stores of this CTA are done
             if (threadIdx.x == 0) {
                 int ticket = 0;
                 if (ok) {
@@ -415,8 +451,8 @@ __device__ __forceinline__ void dkv_body(
                 }
                 *last_flag = ok && ticket == p.gsplit - 1;
             }
-            named_barrier_256();
-            if (*last_flag && kk < si.lk) {
+            met = meet(641) && met;
+            if (met && *last_flag && kk < si.lk) {
                 const float mul = g == 0 ? 1.f : p.scale;
                 __nv_bfloat16* dst = g == 0
                     ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + static_cast<int64_t>(si.k_off + kk) * p.dvs[2]
@@ -462,7 +498,7 @@ __device__ __forceinline__ void dkv_body(
 // ---- dQ ---------------------------------------------------------------------------------
 
 // Body of one dQ CTA; (bx, by, bz) = (head, query block counted from the end, batch).
-template <int D>
+template <int D, bool kMask>
 __device__ __forceinline__ void dq_body(
     const CUtensorMap* pmap_q, const CUtensorMap* pmap_k, const CUtensorMap* pmap_v, const CUtensorMap* pmap_do,
     const BwdParams& tp, int bx, int by, int bz, int ny) {
@@ -562,6 +598,18 @@ __device__ __forceinline__ void dq_body(
                 const int st = j % P::kStages;
                 const uint32_t soff = (st * P::kSub * P::kTile) >> 4;
                 if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBFull + st), (j / P::kStages) & 1, abort_flag, 810 + st, tp.status))) return false;
+                if (p.key_lengths && si.klen - j * kBN < kBN) {
+                    // Blank the key and value rows past the length (see the dK/dV body).
+                    const int first = si.klen - j * kBN;   // > 0: the block has a visible key
+                    for (int idx = lane; idx < P::kSub * (kBN - first) * 8; idx += 32) {
+                        const int sub = idx / ((kBN - first) * 8), rem = idx % ((kBN - first) * 8);
+                        const int off = (st * P::kSub + sub) * P::kTile + (first + rem / 8) * 128 + (rem % 8) * 16;
+                        *reinterpret_cast<uint4*>(smem + P::kB0 + off) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(smem + P::kB1 + off) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                }
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
@@ -617,8 +665,20 @@ __device__ __forceinline__ void dq_body(
         }
         int row_limit = si.klen;
         if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
+        float* vec = reinterpret_cast<float*>(smem + P::kVec);   // [block parity][128]: a block's mask terms
 
         for (int j = 0; j < nblocks; ++j) {
+            if constexpr (kMask) {
+                // A mask of one row per (batch, head): one thread per key column fetches the
+                // block's terms; the buffer of block j - 2 is free (everybody met since).
+                if (g == 0) {
+                    const int key = max(min(j * kBN + row, si.klen - 1), 0);
+                    vec[(j & 1) * 128 + row] = mask_value(p, b, h, 0, static_cast<int64_t>(si.k_off) + key) * kLog2e;
+                }
+                mbar_arrive_warp(bar(P::bMeet));
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMeet), j & 1, abort_flag, 930 + g, tp.status));
+                if (!ok) break;
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + (j & 1)), (j >> 1) & 1, abort_flag, 900 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
@@ -638,6 +698,10 @@ __device__ __forceinline__ void dq_body(
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     float2 x = __ffma2_rn(make_float2(sc[2 * e], sc[2 * e + 1]), sc2, nl2);
+                    if constexpr (kMask) {
+                        const float2 t = reinterpret_cast<const float2*>(vec + (j & 1) * 128 + g * 64 + c * 32)[e];
+                        x = __fadd2_rn(x, t);
+                    }
                     if (!whole) {
                         x.x = c * 32 + 2 * e < limit ? x.x : -INFINITY;
                         x.y = c * 32 + 2 * e + 1 < limit ? x.y : -INFINITY;
@@ -657,7 +721,11 @@ __device__ __forceinline__ void dq_body(
                 uint32_t wd[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const float2 a = __fmul2_rn(pv[c * 16 + e], __fadd2_rn(make_float2(dp[2 * e], dp[2 * e + 1]), nd2));
+                    float2 a = __fmul2_rn(pv[c * 16 + e], __fadd2_rn(make_float2(dp[2 * e], dp[2 * e + 1]), nd2));
+                    if (!whole) {   // hidden keys: exactly 0 whatever dP holds there
+                        a.x = c * 32 + 2 * e < limit ? a.x : 0.f;
+                        a.y = c * 32 + 2 * e + 1 < limit ? a.y : 0.f;
+                    }
                     wd[e] = pack_bf16(a.x, a.y);
                 }
                 tmem_st16(tmem_dp + lane_addr + g * 64 + c * 16, wd);
@@ -714,56 +782,18 @@ __device__ __forceinline__ void dq_body(
 // One launch for both halves of the backward: CTAs [0, n_dkv) are dK/dV CTAs, the rest dQ
 // CTAs (each list longest first). The two are independent of each other, and in one grid the
 // dQ CTAs fill the SMs that the tail of the dK/dV list leaves idle.
-template <int D>
+template <int D, bool kMask>
 __global__ void __launch_bounds__(kThreads, 1) bwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const BwdParams tp, int dkv_x, int dkv_y, int n_dkv, int dq_x, int dq_y) {
     int id = blockIdx.x;
     if (id < n_dkv) {
-        dkv_body<D>(&map_q, &map_k, &map_v, &map_do, tp, id % dkv_x, (id / dkv_x) % dkv_y, id / (dkv_x * dkv_y), dkv_y);
+        dkv_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id % dkv_x, (id / dkv_x) % dkv_y, id / (dkv_x * dkv_y), dkv_y);
     } else {
         id -= n_dkv;
-        dq_body<D>(&map_q, &map_k, &map_v, &map_do, tp, id % dq_x, (id / dq_x) % dq_y, id / (dq_x * dq_y), dq_y);
+        dq_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id % dq_x, (id / dq_x) % dq_y, id / (dq_x * dq_y), dq_y);
     }
-}
-
-// Sums the gsplit fp32 partials of every key row in a fixed order and writes bf16 dV and
-// (scaled) dK. One thread per 8 output columns.
-template <int D>
-__global__ void __launch_bounds__(256) bwd_dkv_reduce_kernel(const AttnParams p) {
-    const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
-    const int nb = p.cu_q ? 1 : p.batch;
-    const int64_t planes = static_cast<int64_t>(nb) * p.kv_heads * p.gsplit;
-    const int64_t per_tensor = static_cast<int64_t>(nb) * p.kv_heads * key_rows * (D / 8);
-    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (idx >= 2 * per_tensor) return;
-    const int which = idx >= per_tensor;  // 0: dV, 1: dK
-    int64_t r = idx - which * per_tensor;
-    const int c8 = r % (D / 8);
-    r /= D / 8;
-    const int64_t row = r % key_rows;
-    r /= key_rows;
-    const int hk = r % p.kv_heads;
-    const int b = r / p.kv_heads;
-    const float* src = p.dkv_partial + (which * planes + (static_cast<int64_t>(b) * p.kv_heads + hk) * p.gsplit) * key_rows * D + row * D + c8 * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-    for (int s = 0; s < p.gsplit; ++s) {  // fixed order; the unrolled loads are in flight together
-        const float4 x = __ldcs(reinterpret_cast<const float4*>(src + s * key_rows * D));
-        const float4 y = __ldcs(reinterpret_cast<const float4*>(src + s * key_rows * D + 4));
-        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
-    }
-    const float mul = which ? p.scale : 1.f;
-    __nv_bfloat16* dst = which ? p.dk + b * p.dks[0] + hk * p.dks[1] + row * p.dks[2]
-                               : p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + row * p.dvs[2];
-    uint4 v;
-    v.x = pack_bf16(acc[0] * mul, acc[1] * mul);
-    v.y = pack_bf16(acc[2] * mul, acc[3] * mul);
-    v.z = pack_bf16(acc[4] * mul, acc[5] * mul);
-    v.w = pack_bf16(acc[6] * mul, acc[7] * mul);
-    *reinterpret_cast<uint4*>(dst + c8 * 8) = v;
 }
 
 bool aligned16(const void* ptr, const int64_t strides[3]) {
@@ -812,31 +842,25 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     constexpr int smem = P::kBytes;
-    if (int rc = ensure_smem(bwd_tc5_kernel<D>, smem, "cudaFuncSetAttribute(bwd_tc5)")) return rc;
+    const bool masked = p.mask_dtype != KTT_B200_MASK_NONE;
+    auto kernel = masked ? bwd_tc5_kernel<D, true> : bwd_tc5_kernel<D, false>;
+    if (int rc = ensure_smem(kernel, smem, "cudaFuncSetAttribute(bwd_tc5)")) return rc;
     const int dkv_x = p.kv_heads * p.gsplit, dkv_y = (p.sk + kBM - 1) / kBM;
     const int dq_x = p.heads, dq_y = (p.sq + kBM - 1) / kBM;
     const int64_t n_dkv = static_cast<int64_t>(dkv_x) * dkv_y * p.batch;
     const int64_t n_all = n_dkv + static_cast<int64_t>(dq_x) * dq_y * p.batch;
     if (n_all > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: too many tiles");
-    bwd_tc5_kernel<D><<<static_cast<unsigned>(n_all), kThreads, smem, stream>>>(
+    if (p.gsplit > 1 && !p.dkv_counters) return fail(KTT_B200_ERR_BAD_ARGUMENT, "tcgen05 backward: the group split needs its ticket counters");
+    kernel<<<static_cast<unsigned>(n_all), kThreads, smem, stream>>>(
         mq, mk, mv, mdo, tp, dkv_x, dkv_y, static_cast<int>(n_dkv), dq_x, dq_y);
-    if (int rc = check_cuda(cudaGetLastError(), "bwd_tc5 launch")) return rc;
-    if (p.gsplit > 1 && !p.dkv_counters) {
-        const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
-        const int64_t threads = 2 * static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * key_rows * (D / 8);
-        bwd_dkv_reduce_kernel<D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p);
-        if (int rc = check_cuda(cudaGetLastError(), "bwd_dkv_reduce launch")) return rc;
-    }
-    return 0;
+    return check_cuda(cudaGetLastError(), "bwd_tc5 launch");
 }
 
 }  // namespace
 
 bool backward_tc5_takes(const AttnParams& p, const char** why) {
-    if (p.mask_dtype != KTT_B200_MASK_NONE || p.key_lengths) {
-        *why = "gradients with a mask or key lengths run on the warp-MMA kernels";
-        return false;
-    }
+    // Masks of one row per (batch, head) and key lengths are taken (forward_tc5_takes keeps
+    // the masks that differ between query rows on the warp-MMA kernels).
     if (!forward_tc5_takes(p, why)) return false;
     if (!aligned16(p.dout, p.dos) || !aligned16(p.dq, p.dqs) || !aligned16(p.dk, p.dks) || !aligned16(p.dv_out, p.dvs)) {
         *why = "dout, dq, dk and dv must be 16-byte aligned with strides that are multiples of 8";

@@ -208,6 +208,10 @@ extern "C" int ktt_b200_device_status(int* code) {
     return 0;
 }
 
+extern "C" int ktt_b200_selftest_wait_timeout(void* stream) {
+    return selftest_wait_timeout(static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ktt_b200_set_trace(void* device_buffer) {
     set_trace_buffer(static_cast<long long*>(device_buffer));
     return 0;

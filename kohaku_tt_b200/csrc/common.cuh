@@ -205,7 +205,10 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
 int forward_row_occupancy();
 // 0, or KTT_B200_ERR_DEVICE_WAIT with the code of the first wait that ran out (cleared).
 int device_status(int* code);
+// Test support: launches one warp whose bounded wait runs out after ~1e5 cycles.
+int selftest_wait_timeout(cudaStream_t stream);
 // Profiling zones of the tcgen05 forward: a device buffer of 64 x 8 int64, or null.
 void set_trace_buffer(long long* device_buffer);
+long long* get_trace_buffer();   // what set_trace_buffer was given last, or null
 
 }  // namespace ktt

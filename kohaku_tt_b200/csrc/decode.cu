@@ -59,6 +59,7 @@ struct DecodeParams {
     int64_t rope_stride;
     int rope_by_position;
     int32_t* lengths_out;
+    long long* trace;   // optional (ktt_b200_set_trace): per CTA, nanosecond stamps of its phases
 };
 
 namespace {
@@ -190,7 +191,25 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     const int group = p.heads / p.kv_heads;
     const int rows = group * p.sq;  // valid rows of the 16-row MMA tile
 
+    // Launched with programmatic stream serialization: the next kernel in the stream may be
+    // scheduled while this one drains; nothing here reads global memory before the previous
+    // kernel in the stream has completed (a decode loop appends to the cache it reads).
+    // Phase stamps (global nanosecond timer) of this CTA when a trace buffer is set: start,
+    // after the dependency wait, after the length scan, first tile landed, stream done, end.
+    auto stamp = [&](int slot) {
+        if (p.trace && threadIdx.x == 0 && blockIdx.x < 1024) {
+            long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[(64 + blockIdx.x) * 8 + slot] = t;
+        }
+    };
+    stamp(0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    stamp(1);
+
     scan_lengths<kAppend>(p, prefix_s, lens_s, misc);
+    stamp(2);
     if (kAppend && blockIdx.x == 0 && p.lengths_out) {
         for (int b = threadIdx.x; b < p.batch; b += kThreads) p.lengths_out[b] = lens_s[b];
     }
@@ -382,6 +401,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
         // (The query loads above are in flight while this waits for the tile.)
         cp_async_wait<NS - 1>();
         __syncwarp();
+        if (u == u0) stamp(3);
 
         if (kAppend) {
             // The warp whose 16 rows hold the new token's slot puts the rotated key and the
@@ -567,7 +587,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     }
     cp_async_wait<0>();
     __syncthreads();
+    stamp(4);
     if (npend_s[0] > 0) draw_tickets();
+    stamp(5);
 }
 
 int stream_ctas_for_device() {
@@ -582,8 +604,17 @@ template <int D, int NS, bool kAppend>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
     constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (2 * kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
     if (int rc = ensure_smem(decode_kernel<D, NS, kAppend>, smem, "cudaFuncSetAttribute(decode)")) return rc;
-    decode_kernel<D, NS, kAppend><<<ctas, kThreads, smem, stream>>>(p);
-    return check_cuda(cudaGetLastError(), "decode launch");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, decode_kernel<D, NS, kAppend>, p), "decode launch");
 }
 
 // Scratch layout: 1024 ticket counters (int32), then m, l, O partials.
@@ -659,6 +690,7 @@ int run_decode(const ktt_b200_decode_args* a, unsigned char* base, const Scratch
     p.slots = lay.slots;
     p.k_new = p.v_new = p.rope_cos = p.rope_sin = nullptr;
     p.lengths_out = nullptr;
+    p.trace = get_trace_buffer();
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     note_call(3);
     if (app) {

@@ -16,12 +16,13 @@
 //   1 producer warp    TMA loads of Q and of the K / V ring (three stages), and the draw of
 //                      the stream's work from a counter in global memory
 //
-// Why sixteen row warps: measured on B200, one warp alone drives the MUFU pipe at half its
-// rate however independent its exponentials are, and two warps that take turns (one
-// exponentiating, one reading scores) are no faster than two that run in step. A scheduler
-// needs two warps inside the exponential pass to fill the pipe and two more to cover the
-// score reads, the maximum, the P store and the waits: four row warps per scheduler, which
-// with tensor memory for two tiles (2 x 256 columns) means two threads per row.
+// Why sixteen row warps: measured on B200, inside this kernel one warp alone drives the
+// MUFU pipe at about half its rate, and two take ~1,500 cycles for a block's exponentials
+// where four take ~2,000: the pass is MUFU-bound only with four row warps per scheduler,
+// which with tensor memory for two tiles (2 x 256 columns) means two threads per row. (Tried
+// and measured, not kept: making the two streams take turns at the exponential pass through
+// a lock per scheduler - slower, and locks on four schedulers can wait on one another in a
+// cycle; starting stream 1 late - the streams' phases made no difference.)
 // Tensor memory per stream (256 columns): S [0,128), P [128,192) as packed bf16 pairs,
 // O [192,256).
 //
@@ -120,8 +121,6 @@ struct RowParams {
     int q_tiles;
     int units;          // tiles = heads * batch * q_tiles
     int dual;           // the two streams of a CTA share each tile (few tiles per SM)
-    int take_turns;     // the streams take turns at the exponential pass (per scheduler)
-    int start_offset;   // cycles stream 1's rows wait before their first block (experiment)
     int* work_counter;  // null: a fixed deal
     int* done_counter;
 };
@@ -216,9 +215,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
     unsigned char* shared0 = smem_all + S * P::kTileBytes + P::kBars + P::bCount * 8;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(shared0);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(shared0 + 8);
-    // One word per scheduler: which stream's pair of row warps is inside the exponential pass
-    // ((stream + 1) << 8 | warps inside), 0 = nobody.
-    int* mufu_turn = reinterpret_cast<int*>(smem_all + S * P::kTileBytes + P::kBars + P::bCount * 8 + 32);   // [4], stream 0's area
     volatile int* work_slot = reinterpret_cast<volatile int*>(small + P::kBars + P::bCount * 8 + 16);  // [2], per stream (bytes 16..23)
 
     const AttnParams& p = tp.a;
@@ -242,7 +238,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
             *abort_flag = 0;
-            mufu_turn[0] = mufu_turn[1] = mufu_turn[2] = mufu_turn[3] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -498,11 +493,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
             return met;
         };
 
-        if (tp.start_offset > 0 && stream == 1) {
-            const long long t0 = clock64();
-            while (clock64() - t0 < tp.start_offset) {
-            }
-        }
         for (int n = 0; ok; ++n) {
             const int u = take_unit(n, ok);
             if (u == -1) break;
@@ -690,24 +680,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                 };
                 uint32_t wv[8];
                 tmem_ld16(s_addr, sa);
-                if (tp.take_turns) {
-                    // The exponential pass belongs to one stream at a time on each scheduler: two
-                    // warps fill the MUFU pipe, and the other stream's pair meanwhile reads
-                    // scores, takes maxima, publishes P or waits for the tensor core, instead of
-                    // all four exponentiating in step and then all four leaving the pipe idle.
-                    if (lane == 0) {
-                        const int mine = (stream + 1) << 8;
-                        const long long t0 = clock64();
-                        while (true) {
-                            const int seen = atomicCAS(mufu_turn + quarter, 0, mine | 1);
-                            if (seen == 0) break;
-                            if (seen == (mine | 1) && atomicCAS(mufu_turn + quarter, mine | 1, mine | 2) == (mine | 1)) break;
-                            if (*abort_flag || clock64() - t0 > kWaitCycles) break;
-                            __nanosleep(20);
-                        }
-                    }
-                    __syncwarp();
-                }
                 tmem_wait_ld();
                 rzone<kTrace>(tp, tracer, jj, 4);
                 tmem_ld16(s_addr + 16, sb);
@@ -741,14 +713,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                 tc_fence_before();
                 mbar_arrive_warp(bar(P::bSFree));
                 exps(sb, 3, wv);
-                if (tp.take_turns) {
-                    __syncwarp();
-                    if (lane == 0) {
-                        // Leave: the second warp of the pair to do so frees the scheduler's turn.
-                        const int mine = (stream + 1) << 8;
-                        if (atomicCAS(mufu_turn + quarter, mine | 2, mine | 1) != (mine | 2)) atomicExch(mufu_turn + quarter, 0);
-                    }
-                }
                 rzone<kTrace>(tp, tracer, jj, 2);
                 tmem_st8(p_addr + 24, wv);
                 tmem_wait_st();
@@ -899,16 +863,6 @@ int sm_count() {
     return sms[dev];
 }
 
-// Debug switch: KTT_B200_ROW_TURNS=1 makes the streams take turns at the exponential pass.
-int row_take_turns() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("KTT_B200_ROW_TURNS");
-        v = (e && e[0] == '1') ? 1 : 0;
-    }
-    return v;
-}
-
 // Environment switch for experiments: KTT_B200_ROW_DUAL = 0 / 1 forces the mode.
 int forced_dual() {
     static int v = -2;
@@ -973,14 +927,14 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
     // Few tiles per SM: the two streams of a CTA share each tile.
     tp.dual = tiles <= 6 * static_cast<int64_t>(sms) ? 1 : 0;
     if (forced_dual() >= 0) tp.dual = forced_dual() ? 1 : 0;
-    const bool have_ws = workspace && workspace_bytes >= kRowHeaderBytes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+    // The counter pays when a dealing position gets several tiles; with one or two the fixed
+    // deal (longest first, snake order) is as even and saves the round trip to the counter
+    // before each tile's first load.
+    const int64_t positions = static_cast<int64_t>(sms) * (tp.dual ? 1 : P::kStreams);
+    const bool have_ws = workspace && workspace_bytes >= kRowHeaderBytes && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0 &&
+                         tiles > 2 * positions;
     tp.work_counter = have_ws ? static_cast<int*>(workspace) : nullptr;
     tp.done_counter = have_ws ? static_cast<int*>(workspace) + 1 : nullptr;
-    tp.take_turns = row_take_turns();
-    {
-        const char* e = getenv("KTT_B200_ROW_OFFSET");
-        tp.start_offset = e ? atoi(e) : 0;
-    }
     const bool masked = p.mask_dtype != KTT_B200_MASK_NONE;
     auto kernel = masked ? (tp.trace ? fwd_row_kernel<true, true> : fwd_row_kernel<false, true>)
                          : (tp.trace ? fwd_row_kernel<true, false> : fwd_row_kernel<false, false>);

@@ -987,10 +987,35 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
 }
 
 void set_trace_buffer(long long* device_buffer) { tc5::set_trace(device_buffer); }
+long long* get_trace_buffer() { return tc5::trace_buffer(); }
 
 int launch_forward_tc5(const AttnParams& p, cudaStream_t stream) {
     if (p.d == 64) return launch_tc5<64>(p, stream);
     return launch_tc5<128>(p, stream);
+}
+
+namespace {
+// One warp waits, with a short limit, on a barrier nobody arrives at: the wait gives up,
+// records its code in the status word and the kernel returns normally.
+__global__ void wait_timeout_kernel(int* status, long long limit) {
+    __shared__ uint64_t barrier;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&barrier), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const bool got = mbar_wait_slow(smem_u32(&barrier), 0, &abort_flag, 999, status, limit);
+    if (got && threadIdx.x == 0) atomicCAS_system(status, 0, 998);   // cannot happen: nobody arrives
+}
+}  // namespace
+
+int selftest_wait_timeout(cudaStream_t stream) {
+    int* dev_status = nullptr;
+    if (!status_word(&dev_status) || !dev_status) return fail(KTT_B200_ERR_LAUNCH, "no status word");
+    wait_timeout_kernel<<<1, 32, 0, stream>>>(dev_status, 100000);
+    return check_cuda(cudaGetLastError(), "wait_timeout launch");
 }
 
 int device_status(int* code) {

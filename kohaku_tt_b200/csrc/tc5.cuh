@@ -46,12 +46,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait. Returns false when it gave up (its own limit, or another role's).
 __device__ __noinline__ inline bool mbar_wait_slow(
-    uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status) {
+    uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status, long long limit = kWaitCycles) {
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             atomicCAS_system(status, 0, code);
             return false;

@@ -49,8 +49,34 @@ class sdpa_kernel(contextlib.ContextDecorator):
 
     def __enter__(self):
         _stack().append(self.kernels)
+        _tell_shim()
         return self.kernels
 
     def __exit__(self, *exc):
         _stack().pop()
+        _tell_shim()
         return False
+
+
+def _tell_shim():
+    """The C++ registration of the aten overloads keeps its own copy of the calling thread's
+    scope (it cannot call back into Python per attention call)."""
+    from . import _lib
+
+    handle = _lib._SHIM
+    if handle is None:
+        return
+    stack = _stack()
+    if not stack:
+        handle.ktt_b200_aten_set_scope(_lib.KERNEL_AUTO, b"")
+        return
+    allowed = stack[-1]
+    if set(allowed) >= {"flash", "mma"}:
+        code = _lib.KERNEL_AUTO
+    elif "flash" in allowed:
+        code = _lib.KERNEL_TC5
+    elif "mma" in allowed:
+        code = _lib.KERNEL_MMA
+    else:
+        code = -1
+    handle.ktt_b200_aten_set_scope(code, ", ".join(repr(k) for k in allowed).encode())

@@ -172,23 +172,46 @@ def test_backward_shapes(cuda, b, h, hk, s, d, causal):
             assert rel(got, want) <= GRAD_BOUND, (kernel, name)
 
 
-def test_masked_backward(cuda):
+@pytest.mark.parametrize("kernel", ["mma", "flash"])
+@pytest.mark.parametrize("d,kind", [(64, "bool"), (128, "bool"), (64, "values")])
+def test_masked_backward(cuda, kernel, d, kind):
     # Masked calls train through the same fused backward here (the reference recomputes
-    # with separate ops, aten_attention.cpp:781-811).
-    b, h, hk, s, d = 2, 4, 2, 200, 64
-    q, k, v, do = qkv(b, h, hk, s, s, d, 77, extra=1)
+    # with separate ops, aten_attention.cpp:781-811): key-padding masks of one row per
+    # (batch, head) on both kernel families.
+    b, h, hk, s = 2, 4, 2, 200
+    q, k, v, do = qkv(b, h, hk, s, s, d, 77 + d, extra=1)
     keep = _padding_keep(b, s)[:, None, None, :]
-    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, mask=keep)
-    qc, kc, vc, doc, mc = (t.to(cuda) for t in (q, k, v, do, keep))
+    mask = keep
+    if kind == "values":   # an additive row per (batch, head), -inf where dropped
+        mask = torch.randn(b, h, 1, s, generator=torch.Generator().manual_seed(5)).masked_fill(~keep, -math.inf)
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, mask=mask)
+    qc, kc, vc, doc, mc = (t.to(cuda) for t in (q, k, v, do, mask))
     out, lse = ops.sdpa_forward(qc, kc, vc, mask=mc)
-    gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, mask=mc)
-    for got, want in ((gq, dq), (gk, dk), (gv, dv)):
-        assert rel(got, want) <= GRAD_BOUND
+    gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, mask=mc, kernel=kernel)
+    for name, got, want in (("dq", gq, dq), ("dk", gk, dk), ("dv", gv, dv)):
+        assert rel(got, want) <= GRAD_BOUND, name
     # Keys every row masks get exactly zero gradients (flash.md "exact zeros").
     dropped = ~keep[:, 0, 0, :]
     for i in range(b):
         assert gk[i][:, dropped[i].to(cuda)].abs().max() == 0
         assert gv[i][:, dropped[i].to(cuda)].abs().max() == 0
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
+def test_masks_that_differ_between_rows_train_on_the_general_kernel(cuda):
+    b, h, s, d = 1, 2, 130, 64
+    q, k, v, do = qkv(b, h, h, s, s, d, 78, extra=1)
+    mask = torch.randn(b, 1, s, s, generator=torch.Generator().manual_seed(6))
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, mask=mask)
+    qc, kc, vc, doc, mc = (t.to(cuda) for t in (q, k, v, do, mask))
+    out, lse = ops.sdpa_forward(qc, kc, vc, mask=mc)
+    gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, mask=mc)
+    assert rel(out, ruler) <= FWD_BOUND
+    for got, want in ((gq, dq), (gk, dk), (gv, dv)):
+        assert rel(got, want) <= GRAD_BOUND
+    with pytest.raises(_lib.UnsupportedAttention):
+        ops.sdpa_backward(doc, qc, kc, vc, out, lse, mask=mc, kernel="flash")
 
 
 def test_exact_zero_gradients(cuda):

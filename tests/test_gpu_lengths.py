@@ -66,6 +66,32 @@ def test_garbage_past_the_lengths_changes_nothing(cuda):
     assert torch.equal(a, b_)
 
 
+@pytest.mark.parametrize("kernel", ["mma", "flash"])
+@pytest.mark.parametrize("d,causal", [(64, False), (128, True)])
+def test_key_length_gradients_on_each_kernel_ignore_garbage(cuda, kernel, d, causal):
+    """Gradients with key lengths on the warp-MMA and on the tcgen05 backward: against
+    float64, exact zeros past each length, and bit-equal when the cache holds inf / NaN past
+    the lengths (test_attention_lengths.py:107-124 carried to the backward)."""
+    b, h, hk, s, lengths = 3, 4, 2, 300, [300, 1, 170]
+    q, k, v, do = qkv(b, h, hk, s, s, d, 50 + d, extra=1)
+    ruler, dq, dk, dv = ao.grads_dense(q, k, v, do, lengths=lengths, causal=causal)
+    ln = torch.tensor(lengths, dtype=torch.int32, device=cuda)
+    qc, kc, vc, doc = (t.to(cuda) for t in (q, k, v, do))
+    out, lse = ops.sdpa_forward(qc, kc, vc, key_lengths=ln, causal=causal)
+    gq, gk, gv = ops.sdpa_backward(doc, qc, kc, vc, out, lse, key_lengths=ln, causal=causal, kernel=kernel)
+    for name, got, want in (("dq", gq, dq), ("dk", gk, dk), ("dv", gv, dv)):
+        assert rel(got, want) <= 2.5e-2, name
+    k2, v2 = k.clone(), v.clone()
+    for i, n in enumerate(lengths):
+        assert gk[i, :, n:].abs().max() == 0 and gv[i, :, n:].abs().max() == 0
+        k2[i, :, n:] = float("inf")
+        v2[i, :, n:] = float("nan")
+    hq, hk_, hv = ops.sdpa_backward(doc, qc, k2.to(cuda), v2.to(cuda), out, lse, key_lengths=ln, causal=causal, kernel=kernel)
+    assert torch.equal(hq, gq) and torch.equal(hk_, gk) and torch.equal(hv, gv)
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
 def test_full_lengths_equal_plain_attention(cuda):
     # test_attention_lengths.py:127-139 (same kernel, so bit for bit).
     q, k, v = qkv(2, 4, 2, 197, 197, 64, 6)

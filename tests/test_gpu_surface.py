@@ -355,3 +355,41 @@ def test_packed_rows_without_keys_are_defined(cuda):
                                      cu(lq, cuda), cu(lk, cuda), 40, 25, causal=True)
     assert torch.count_nonzero(gq[:15]) == 0
     assert all(torch.isfinite(g).all() for g in (gq, gk, gv))
+
+
+def test_cpp_and_python_registrations_agree(cuda):
+    """The overloads are registered from C++ (csrc/torch_shim) by default; the Python
+    registration is the stand-in. Same kernels, same layouts, same bits; the kernel scope
+    reaches both."""
+    from kohaku_tt_b200 import aten
+
+    assert aten.using_cpp_registration()
+    q, k, v, do = qkv(2, 4, 2, 200, 200, 64, 41, extra=1)
+    keep = torch.ones(2, 1, 1, 200, dtype=torch.bool)
+    keep[..., 150:] = False
+
+    def run():
+        qc, kc, vc = (t.to(cuda).requires_grad_(True) for t in (q, k, v))
+        out = F.scaled_dot_product_attention(qc, kc, vc, is_causal=True, enable_gqa=True)
+        out.backward(do.to(cuda))
+        with torch.no_grad():
+            masked = F.scaled_dot_product_attention(qc, kc, vc, attn_mask=keep.to(cuda), enable_gqa=True)
+        before = ktt.counters()
+        with ktt.sdpa_kernel("mma"), torch.no_grad():
+            F.scaled_dot_product_attention(qc, kc, vc, enable_gqa=True)
+        return out.detach(), qc.grad, kc.grad, vc.grad, masked, masked.stride(), _delta(before)
+
+    cpp = run()
+    ktt.uninstall()
+    try:
+        ktt.install(python=True)
+        assert not aten.using_cpp_registration()
+        py = run()
+    finally:
+        ktt.uninstall()
+        ktt.install()
+    assert aten.using_cpp_registration()
+    for a, b in zip(cpp[:5], py[:5]):
+        assert torch.equal(a, b)
+    assert cpp[5] == py[5]
+    assert cpp[6] == py[6] == {"attention_mma": 1}
