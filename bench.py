@@ -330,7 +330,13 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=dev)
+        # The ring leg's send / recv kernels run beside the persistent attention kernels: a
+        # few NCCL CTAs move 134 MB per step in well under a step's compute, and every SM
+        # they do not take keeps its attention CTA.
+        opts = torch.distributed.ProcessGroupNCCL.Options()
+        opts.config.max_ctas = 4
+        opts.config.min_ctas = 1
+        torch.distributed.init_process_group("nccl", device_id=dev, pg_options=opts)
 
     import torch.nn.functional as F
 

@@ -231,6 +231,7 @@ KTT_B200_API int ktt_b200_decode(const ktt_b200_decode_args* args, void* stream)
  *  - Every call on a device uses the same array. It needs no clearing between calls, but
  *    calls that overlap on the GPU (different streams, no ordering) corrupt each other:
  *    keep them on one stream or order them with events.
+ *  - The array is the current device's: call with the device current whose stream is passed.
  *  - Every GPU that loads the library holds the 4 MiB until the process ends. */
 KTT_B200_API int ktt_b200_decode_static(const ktt_b200_decode_args* args, void* stream);
 

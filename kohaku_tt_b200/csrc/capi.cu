@@ -119,7 +119,7 @@ void delta_layout(const ktt_b200_attn_args* a, int64_t& bs, int64_t& hs, int64_t
 }
 
 __global__ void merge_partials_kernel(
-    void* out, float* lse, const void* out2, const float* lse2, int64_t rows, int dv, int f32) {
+    void* out, float* lse, const void* out2, const float* lse2, int64_t rows, int dv, int f32, int vec) {
     const int64_t row = blockIdx.x * static_cast<int64_t>(blockDim.y) + threadIdx.y;
     if (row >= rows) return;
     const float a = lse[row], b = lse2[row];
@@ -134,7 +134,7 @@ __global__ void merge_partials_kernel(
         l = m + __logf(ea + eb);
     }
     // f32: 0 = both bf16, 1 = both fp32, 2 = fp32 accumulator with a bf16 second operand.
-    if ((dv & 3) == 0) {
+    if (vec) {
         for (int c = threadIdx.x * 4; c < dv; c += blockDim.x * 4) {
             const int64_t i = row * dv + c;
             float x[4], y[4];
@@ -357,7 +357,12 @@ extern "C" int ktt_b200_merge_partials(
     if (rows == 0) return 0;
     dim3 block(32, 8);
     const int64_t blocks = (rows + 7) / 8;
+    // Four values per access only where both operands allow it: rows of a multiple of four
+    // values whose first element is 16-byte (fp32) or 8-byte (bf16) aligned.
+    const uintptr_t need_out = out_is_f32 ? 15 : 7, need_out2 = out_is_f32 == 1 ? 15 : 7;
+    const int vec = (dv & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & need_out) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out2) & need_out2) == 0;
     merge_partials_kernel<<<static_cast<unsigned>(blocks), block, 0, static_cast<cudaStream_t>(stream)>>>(
-        out, lse, out2, lse2, rows, dv, out_is_f32);
+        out, lse, out2, lse2, rows, dv, out_is_f32, vec);
     return check_cuda(cudaGetLastError(), "merge_partials launch");
 }

@@ -186,8 +186,13 @@ def ring_forward(q, k, v, group=None, scale=None, attend=None, merge=None):
 
 def ring_backward(dout, q, k, v, out, lse, group=None, scale=None, attend_backward=None):
     """dq, dk, dv of ring_forward for this rank's shard. K/V blocks travel the ring again,
-    each with an fp32 accumulator for its dk / dv that collects every rank's contribution
-    and is handed back to the block's owner after the last step."""
+    each followed by an fp32 accumulator for its dk / dv that collects every rank's
+    contribution and is handed back to the block's owner after the last step.
+
+    The accumulators run one hop behind the blocks: a rank computes its contribution to the
+    block it holds while that block's accumulator is still on its way from the previous
+    rank, adds the two when it lands and sends the sum on while the next block is being
+    worked on. Neither exchange waits for the other's compute."""
     attend_backward = attend_backward or _default_attend_backward
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -196,15 +201,16 @@ def ring_backward(dout, q, k, v, out, lse, group=None, scale=None, attend_backwa
     qh, doh, oh = halves(q), halves(dout), halves(out)
     lh = [lse[:, :, :c].contiguous(), lse[:, :, c:].contiguous()]
     dq = [torch.zeros(qh[0].shape, dtype=torch.float32, device=q.device) for _ in range(2)]
-    block = [k.contiguous(), v.contiguous(),
-             torch.zeros(k.shape, dtype=torch.float32, device=k.device),
-             torch.zeros(v.shape, dtype=torch.float32, device=v.device)]
+    kv = [k.contiguous(), v.contiguous()]
+    acc_in, acc_reqs, acc_sent = None, None, None   # the block in hand's accumulators on their way here (and the sums on their way out)
     for step in range(world):
-        kb, vb, dkb, dvb = block
-        # K/V can leave while this step computes; the accumulators leave after it.
+        kb, vb = kv
         pending_kv = None
         if step + 1 < world:
-            nxt_kv, pending_kv = _exchange(block[:2], block[:2], group, rank, world)
+            nxt_kv, pending_kv = _exchange(kv, kv, group, rank, world)
+        # This rank's contribution to the block in hand.
+        gk_sum = torch.zeros(kb.shape, dtype=torch.float32, device=kb.device)
+        gv_sum = torch.zeros(vb.shape, dtype=torch.float32, device=vb.device)
         for half, key_halves, causal in _visible_parts(world, rank, step):
             both = key_halves == (0, 1)
             ks = kb if both else kb[:, :, :c]
@@ -212,15 +218,23 @@ def ring_backward(dout, q, k, v, out, lse, group=None, scale=None, attend_backwa
             gq, gk, gv = attend_backward(doh[half], qh[half], ks, vs, oh[half], lh[half], causal, scale)
             dq[half] += gq.float()
             span = slice(None) if both else slice(0, c)
-            dkb[:, :, span] += gk.float()
-            dvb[:, :, span] += gv.float()
-        nxt_acc, pending_acc = _exchange([dkb, dvb], [dkb, dvb], group, rank, world)
-        for req in pending_acc:
-            req.wait()
+            gk_sum[:, :, span] += gk.float()
+            gv_sum[:, :, span] += gv.float()
+        if acc_reqs is not None:        # what the ranks before this one have added for the block
+            for req in acc_reqs:        # (one exchange: the previous sums have left by then too)
+                req.wait()
+            gk_sum += acc_in[0]
+            gv_sum += acc_in[1]
+        # Send the sums on (after the last step: home to the block's owner) and start receiving
+        # the accumulators of the next block in hand.
+        acc_sent = [gk_sum, gv_sum]
+        acc_in, acc_reqs = _exchange(acc_sent, acc_sent, group, rank, world)
         if pending_kv is not None:
             for req in pending_kv:
                 req.wait()
-            block = [nxt_kv[0], nxt_kv[1], nxt_acc[0], nxt_acc[1]]
-        else:
-            block = [kb, vb, nxt_acc[0], nxt_acc[1]]  # the accumulators are home again
-    return (torch.cat(dq, dim=2).to(q.dtype), block[2].to(k.dtype), block[3].to(v.dtype))
+            kv = nxt_kv
+    for req in acc_reqs:
+        req.wait()
+    del acc_sent
+    # After `world` hops the accumulators of this rank's own block are back.
+    return (torch.cat(dq, dim=2).to(q.dtype), acc_in[0].to(k.dtype), acc_in[1].to(v.dtype))

@@ -83,7 +83,8 @@ def test_key_length_gradients_on_each_kernel_ignore_garbage(cuda, kernel, d, cau
         assert rel(got, want) <= 2.5e-2, name
     k2, v2 = k.clone(), v.clone()
     for i, n in enumerate(lengths):
-        assert gk[i, :, n:].abs().max() == 0 and gv[i, :, n:].abs().max() == 0
+        if n < s:
+            assert gk[i, :, n:].abs().max() == 0 and gv[i, :, n:].abs().max() == 0
         k2[i, :, n:] = float("inf")
         v2[i, :, n:] = float("nan")
     hq, hk_, hv = ops.sdpa_backward(doc, qc, k2.to(cuda), v2.to(cuda), out, lse, key_lengths=ln, causal=causal, kernel=kernel)

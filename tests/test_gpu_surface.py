@@ -137,6 +137,16 @@ def test_merge_partials_equals_attention_over_the_union(cuda):
     narrow, ln = o1[..., :63].float().contiguous(), l1.clone()
     ops.merge_partials(narrow, ln, o2[..., :63].contiguous(), l2)
     assert torch.allclose(narrow, acc[..., :63], rtol=1e-5, atol=1e-6)  # scalar path: same formula, other rounding of the multiply-adds
+    # Operands that start at an odd element (views with a storage offset) are contiguous but
+    # not 16-byte aligned: the scalar path takes them instead of a misaligned vector access.
+    pad_a = torch.zeros(o1.numel() + 1, dtype=torch.float32, device=cuda)
+    pad_b = torch.zeros(o2.numel() + 1, dtype=torch.bfloat16, device=cuda)
+    off_a, off_b = pad_a[1:].view(o1.shape), pad_b[1:].view(o2.shape)
+    off_a.copy_(o1.float())
+    off_b.copy_(o2)
+    lo = l1.clone()
+    ops.merge_partials(off_a, lo, off_b, l2)
+    assert torch.allclose(off_a, acc, rtol=1e-5, atol=1e-6) and torch.equal(lo, la)
 
 
 # ---- torch.compile (tests/hardware/ops/test_sdpa_kernel.py:215-224) ----------------------

@@ -33,7 +33,7 @@ def _args(q, k, v, out, lengths, scale=None):
     return a
 
 
-def _both(cuda, seed, b, h, hk, d, cap):
+def _both(cuda, seed, b, h, hk, d, cap, splits=0):
     """(static result, regular result, float64 ruler) for one seeded decode problem."""
     q, k, v = qkv(b, h, hk, 1, cap, d, seed)
     g = torch.Generator().manual_seed(seed)
@@ -42,17 +42,35 @@ def _both(cuda, seed, b, h, hk, d, cap):
     stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
     static_out = torch.empty_like(qc)
     args = _args(qc, kc, vc, static_out, ln)
+    args.splits = splits
+    # The property the entry point exists for: the call itself allocates nothing. Everything
+    # it touches exists already, so neither torch's allocator nor the driver's free-memory
+    # count moves across it.
+    torch.cuda.synchronize()
+    free_before, held_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
     _lib.check(_lib.lib().ktt_b200_decode_static(ctypes.byref(args), stream), "decode_static")
-    regular_out, _ = ops.decode(qc, kc, vc, key_lengths=ln)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == held_before
+    if _both.warm:   # the first call on a device takes the array's address and sets kernel attributes
+        assert torch.cuda.mem_get_info()[0] == free_before
+    _both.warm = True
+    regular_out, _ = ops.decode(qc, kc, vc, key_lengths=ln, splits=splits)
     torch.cuda.synchronize()
     return static_out, regular_out, ao.ruler_lengths(q, k, v, lengths)
 
 
+_both.warm = False
+
+
 def test_static_decode_matches_the_regular_entry_point_twice(cuda):
-    # Two calls in a row, the second smaller and with other data: stale partials of the
-    # first call sit in the shared array while the second runs.
-    for seed, shape in ((1, (16, 16, 2, 128, 1024)), (2, (5, 8, 8, 64, 300))):
-        static_out, regular_out, ruler = _both(cuda, seed, *shape)
+    # Calls in a row on the one shared array: large then small (stale partials of the first
+    # sit there while the second runs), then small to large again and another split count
+    # (the tickets must be back at zero, and slots laid out for an earlier call must not
+    # alias live partials).
+    cases = ((1, (16, 16, 2, 128, 1024), 0), (2, (5, 8, 8, 64, 300), 0), (3, (16, 16, 2, 128, 1024), 2),
+             (4, (24, 16, 2, 128, 700), 0))
+    for seed, shape, splits in cases:
+        static_out, regular_out, ruler = _both(cuda, seed, *shape, splits=splits)
         # Same kernels, same split: the two entry points agree bit for bit, and both sit
         # inside the forward bound against the float64 ruler.
         assert torch.equal(static_out, regular_out), seed
