@@ -323,22 +323,31 @@ def _(grad, out, lse, q, k, v, lengths, is_causal, scale):
 
 # ---- packed varlen ops (torch_attn::_varlen_attn*, kohakutt/torch_backend/varlen.py) ----
 
+_FULL_WINDOW, _CAUSAL_WINDOW = (-1, -1), (-1, 0)
+
+
 def _causal(is_causal, window_size):
-    """True for causal attention; raises for windows other than (-1, -1) and (-1, 0)
-    (varlen.py:107-114)."""
-    window = list(window_size) if window_size is not None else [-1, -1]
-    if window not in ([-1, -1], [-1, 0]):
+    """Folds torch's (left, right) attention window into the causal flag. Only the two
+    windows that mean "everything" and "everything up to the diagonal" exist here; a
+    sliding window is refused rather than silently widened (the contract of
+    kohakutt/torch_backend/varlen.py:107-114)."""
+    window = _FULL_WINDOW if window_size is None else tuple(window_size)
+    if window == _CAUSAL_WINDOW:
+        return True
+    if window != _FULL_WINDOW:
         raise NotImplementedError(
             "kohaku_tt_b200: varlen attention takes window_size (-1, -1) or (-1, 0)"
         )
-    return bool(is_causal) or window == [-1, 0]
+    return bool(is_causal)
 
 
 def _unsupported(**given):
-    names = [name for name, value in given.items() if value is not None]
-    if names:
+    """Refuses optional arguments of torch's packed op that have no kernel behind them
+    (paged caches, per-sequence used lengths): any that was actually passed is named."""
+    passed = sorted(name for name in given if given[name] is not None)
+    if passed:
         raise NotImplementedError(
-            f"kohaku_tt_b200: varlen attention does not support {', '.join(names)}"
+            "kohaku_tt_b200: varlen attention does not support " + ", ".join(passed)
         )
 
 

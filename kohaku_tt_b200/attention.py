@@ -12,66 +12,76 @@ from . import aten, ops
 MASKED_LOGIT = -5e5
 
 
+def _lengths_error(what):
+    return ValueError(f"kohaku_tt_b200.sdpa: key_lengths must {what}")
+
+
 def device_lengths(key_lengths, batch, keys, device):
-    """`key_lengths` as an int32 [batch] tensor on `device`. A list or a CPU tensor is
-    checked (1 <= length <= keys) and uploaded; a device tensor is used as it is (no
-    download: the kernel clamps its values to [1, keys]). Same checks and messages as
-    kohakutt/torch_backend/lengths.py:10-29."""
-    if isinstance(key_lengths, torch.Tensor) and key_lengths.device.type != "cpu":
-        lengths = key_lengths.to(torch.int32)
-    else:
-        lengths = torch.as_tensor(key_lengths, dtype=torch.int32)
-        if lengths.numel() and (lengths.min() < 1 or lengths.max() > keys):
-            raise ValueError(
-                f"kohaku_tt_b200.sdpa: key_lengths must lie in [1, {keys}], "
-                f"got {lengths.tolist()}"
-            )
-        lengths = lengths.to(device)
-    if lengths.dim() != 1 or lengths.size(0) != batch:
-        raise ValueError(
-            f"kohaku_tt_b200.sdpa: key_lengths must hold one length per batch ({batch}), "
-            f"got shape {tuple(lengths.shape)}"
+    """One int32 length per batch row, resident on `device`.
+
+    Host values (a sequence or a CPU tensor) are validated here, every one in [1, keys],
+    and then copied over. Values already on a device cannot be inspected without a
+    round trip, so they are only converted; the kernels clamp what they read to that
+    range. The shape rule (rank 1, `batch` entries) holds for both. Messages and
+    exception type follow kohakutt/torch_backend/lengths.py:10-29, which the callers'
+    tests pin."""
+    on_host = not (isinstance(key_lengths, torch.Tensor) and key_lengths.device.type != "cpu")
+    values = torch.as_tensor(key_lengths, dtype=torch.int32) if on_host else key_lengths.to(torch.int32)
+    if on_host and values.numel() > 0:
+        low, high = int(values.min()), int(values.max())
+        if low < 1 or high > keys:
+            raise _lengths_error(f"lie in [1, {keys}], got {values.tolist()}")
+    if values.dim() != 1 or values.size(0) != batch:
+        raise _lengths_error(
+            f"hold one length per batch ({batch}), got shape {tuple(values.shape)}"
         )
-    return lengths
+    return values.to(device) if on_host else values
 
 
 class _Lengths(torch.autograd.Function):
-    """The kernel route with gradients: output and dq, dk, dv; the lengths get none
-    (lengths.py:52-68)."""
+    """Autograd node of the key-lengths route. The forward op hands back the row
+    statistics with the output; they, the inputs and the lengths are what the backward
+    op needs to produce dq, dk and dv. Nothing flows back to the lengths or the flags
+    (the role of kohakutt/torch_backend/lengths.py:52-68, which recomputes the
+    statistics instead of saving them)."""
 
     @staticmethod
     def forward(ctx, q, k, v, lengths, causal, scale):
         out, lse = torch.ops.ktt_b200._sdpa_lengths(q, k, v, lengths, causal, scale, True)
-        ctx.save_for_backward(q, k, v, lengths, out, lse)
-        ctx.args = (causal, scale)
+        ctx.causal, ctx.scale = causal, scale
+        ctx.save_for_backward(out, lse, q, k, v, lengths)
         return out
 
     @staticmethod
-    def backward(ctx, grad):
-        q, k, v, lengths, out, lse = ctx.saved_tensors
-        causal, scale = ctx.args
-        dq, dk, dv = torch.ops.ktt_b200._sdpa_lengths_backward(
-            grad.contiguous(), out, lse, q, k, v, lengths, causal, scale
+    def backward(ctx, grad_out):
+        out, lse, q, k, v, lengths = ctx.saved_tensors
+        grads = torch.ops.ktt_b200._sdpa_lengths_backward(
+            grad_out.contiguous(), out, lse, q, k, v, lengths, ctx.causal, ctx.scale
         )
-        return dq, dk, dv, None, None, None
+        return (*grads, None, None, None)
 
 
 def sdpa(q, k, v, key_lengths=None, is_causal=False, scale=None):
-    """F.scaled_dot_product_attention of q [B, H, Sq, D], k / v [B, Hk, Sk, D / Dv] with
-    the key mask key < key_lengths[b] (B ints in [1, Sk]: list, CPU or CUDA tensor),
-    built nowhere: the kernel skips and masks those keys. Query rows past a length see
-    the real keys. With few query rows and no gradients this is the split-K decode
-    kernel over a static KV cache."""
-    gqa = q.size(1) != k.size(1)
+    """Attention of q [B, H, Sq, D] over k [B, Hk, Sk, D] and v [B, Hk, Sk, Dv] in which
+    batch row b may only look at its first key_lengths[b] keys.
+
+    key_lengths holds B integers, each from 1 to Sk, as a list, a CPU tensor or a tensor
+    on the device. No mask tensor is ever materialised: whole key blocks past a length are
+    not visited and the block that straddles it is cut inside the kernel. The rule is
+    about keys only; a query row whose index lies beyond the length still attends to the
+    real keys. Without key_lengths this is F.scaled_dot_product_attention (grouped heads
+    enabled when H != Hk). A call with a handful of query rows per key head and no
+    gradient recording is served by the split-K decode kernel over a static KV cache.
+    Same arguments and meaning as kohakutt.sdpa (src/kohakutt/attention.py:10-23)."""
     if key_lengths is None:
-        return F.scaled_dot_product_attention(
-            q, k, v, is_causal=is_causal, scale=scale, enable_gqa=gqa
-        )
+        return F.scaled_dot_product_attention(q, k, v, is_causal=is_causal, scale=scale,
+                                              enable_gqa=q.size(1) != k.size(1))
     lengths = device_lengths(key_lengths, q.size(0), k.size(-2), q.device)
-    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v)):
-        return _Lengths.apply(q, k, v, lengths, bool(is_causal), scale)
-    out, _ = torch.ops.ktt_b200._sdpa_lengths(q, k, v, lengths, bool(is_causal), scale, False)
-    return out
+    causal = bool(is_causal)
+    wants_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if wants_grad:
+        return _Lengths.apply(q, k, v, lengths, causal, scale)
+    return torch.ops.ktt_b200._sdpa_lengths(q, k, v, lengths, causal, scale, False)[0]
 
 
 def decode_step(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin, scale=None, lengths_out=None):
@@ -91,11 +101,11 @@ def decode_step(q, k_new, v_new, k_cache, v_cache, lengths, cos, sin, scale=None
 
 
 def offsets(cu_seq):
-    """Cumulative sequence offsets as a tuple of ints (a list or an int tensor; a device
-    tensor is downloaded) (varlen.py:23-28)."""
-    if isinstance(cu_seq, torch.Tensor):
-        return tuple(int(x) for x in cu_seq.detach().cpu().tolist())
-    return tuple(int(x) for x in cu_seq)
+    """Host copy of a cumulative-offset vector as plain ints. Accepts any iterable of
+    integers or an integer tensor; one that lives on a device costs a download (the role
+    of kohakutt/torch_backend/varlen.py:23-28)."""
+    host = cu_seq.detach().to("cpu").tolist() if isinstance(cu_seq, torch.Tensor) else list(cu_seq)
+    return tuple(map(int, host))
 
 
 def check_offsets(cu_q, cu_k, tokens_q, tokens_k, causal):
@@ -148,41 +158,46 @@ class _Masked(torch.autograd.Function):
 
 def sdpa_varlen(q, k, v, cu_seq_q, cu_seq_k=None, max_q=None, max_k=None, is_causal=False,
                 scale=None, attn_mask=None):
-    """Scaled dot-product attention over packed variable-length sequences.
+    """Attention inside each sequence of a packed batch; the argument list of
+    kohakutt.sdpa_varlen (src/kohakutt/attention.py:26-76).
 
-    q [Tq, H, D], k [Tk, Hkv, D] and v [Tk, Hkv, Dv] (bf16, H a multiple of Hkv) hold the
-    tokens of every sequence back to back; nothing is padded. cu_seq_q / cu_seq_k are the
-    cumulative sequence offsets [0, ..., total] (a list or an int tensor; cu_seq_k
-    defaults to cu_seq_q). Each query attends to the keys of its own sequence; with
-    is_causal query r of a sequence sees its first min(Lk, r + 1 + Lk - Lq) keys.
-    Returns [Tq, H, Dv].
+    Layout: token-major bf16 tensors without padding, q [Tq, H, D], k [Tk, Hkv, D],
+    v [Tk, Hkv, Dv], H divisible by Hkv. Sequence i owns query rows
+    cu_seq_q[i]:cu_seq_q[i + 1] and key rows cu_seq_k[i]:cu_seq_k[i + 1]; both vectors
+    start at 0 and end at the token count, and the key vector may be omitted when it
+    equals the query one. They may be lists or integer tensors. A query never sees
+    another sequence's keys. Under is_causal the diagonal is aligned to the end of the
+    sequence: query r of a sequence with Lq queries and Lk keys sees keys
+    0 .. r + Lk - Lq. The result is [Tq, H, Dv].
 
-    attn_mask: a key mask [Tk], one value per packed key, for every query of the key's
-    sequence and every head. Bool: True keeps the key. Float: added to the key's scores
-    (clamped at -5e5). It gets no gradient. Other mask shapes are not taken.
+    attn_mask, when given, is a vector over the packed keys [Tk] shared by all heads and
+    all queries of the key's sequence: booleans select keys (True = visible), floats are
+    added to the logits and floored at -5e5. Masks of any other shape are rejected, and
+    the mask receives no gradient.
 
-    Offsets given on the host are checked there; the kernels read them on the device.
-    """
+    max_q / max_k default to the longest sequence found in the offsets. Offsets are
+    validated on the host before anything is launched; the kernels then read their
+    device copy."""
+    causal = bool(is_causal)
     cu_q = offsets(cu_seq_q)
-    cu_k = cu_q if cu_seq_k is None else offsets(cu_seq_k)
-    check_offsets(cu_q, cu_k, q.size(0), k.size(0), bool(is_causal))
-    lengths_q = [b - a for a, b in zip(cu_q, cu_q[1:])]
-    lengths_k = [b - a for a, b in zip(cu_k, cu_k[1:])]
-    max_q = max(lengths_q, default=0) if max_q is None else max_q
-    max_k = max(lengths_k, default=0) if max_k is None else max_k
+    cu_k = offsets(cu_seq_k) if cu_seq_k is not None else cu_q
+    check_offsets(cu_q, cu_k, q.size(0), k.size(0), causal)
+
+    def longest(cu):
+        return max((hi - lo for lo, hi in zip(cu[:-1], cu[1:])), default=0)
+
+    max_q = longest(cu_q) if max_q is None else max_q
+    max_k = longest(cu_k) if max_k is None else max_k
     dev_q = torch.tensor(cu_q, dtype=torch.int32, device=q.device)
     dev_k = dev_q if cu_k == cu_q else torch.tensor(cu_k, dtype=torch.int32, device=q.device)
-    if attn_mask is not None:
-        if attn_mask.dim() != 1 or attn_mask.size(0) != k.size(0):
-            raise ValueError(
-                f"kohaku_tt_b200.sdpa_varlen: attn_mask must be [{k.size(0)}] "
-                f"(one value per packed key), got {tuple(attn_mask.shape)}"
-            )
-        mask = attn_mask.to(q.device)
-        return _Masked.apply(q, k, v, mask, dev_q, dev_k, max_q, max_k, bool(is_causal), scale)
-    aten.install()
-    out, _, _ = torch.ops.torch_attn._varlen_attn(
-        q, k, v, dev_q, dev_k, max_q, max_k, bool(is_causal), scale,
-        [-1, 0] if is_causal else [-1, -1],
-    )
-    return out
+    if attn_mask is None:
+        aten.install()
+        window = [-1, 0] if causal else [-1, -1]
+        return torch.ops.torch_attn._varlen_attn(q, k, v, dev_q, dev_k, max_q, max_k, causal,
+                                                 scale, window)[0]
+    if attn_mask.dim() != 1 or attn_mask.size(0) != k.size(0):
+        raise ValueError(
+            f"kohaku_tt_b200.sdpa_varlen: attn_mask must be [{k.size(0)}] "
+            f"(one value per packed key), got {tuple(attn_mask.shape)}"
+        )
+    return _Masked.apply(q, k, v, attn_mask.to(q.device), dev_q, dev_k, max_q, max_k, causal, scale)

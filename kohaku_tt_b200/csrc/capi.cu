@@ -307,6 +307,30 @@ extern "C" int64_t ktt_b200_sdpa_backward_workspace(const ktt_b200_attn_args* a)
     return (total * 4 + 255) / 256 * 256 + backward_partial_bytes(p, backward_group_split(p));
 }
 
+// Packed calls: rows of dq, dk and dv that no sequence of the offsets covers (before the
+// first offset, after the last) get zeros here; every row inside a sequence is written by the
+// CTA that owns it, so callers need not clear the gradients first.
+__global__ void zero_uncovered_rows_kernel(const AttnParams p) {
+    const int64_t q_lo = p.cu_q[0], q_hi = p.cu_q[p.batch], k_lo = p.cu_k[0], k_hi = p.cu_k[p.batch];
+    const int64_t q_rows = q_lo + (p.total_q - q_hi), k_rows = k_lo + (p.total_k - k_hi);
+    if (q_rows <= 0 && k_rows <= 0) return;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x, t0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const __nv_bfloat16 zero = __float2bfloat16(0.f);
+    auto clear = [&](__nv_bfloat16* base, const int64_t (&st)[3], int heads, int d, int64_t lo, int64_t hi, int64_t total) {
+        const int64_t rows = lo + (total - hi);
+        for (int64_t i = t0; i < rows * heads * d; i += stride) {
+            const int e = static_cast<int>(i % d);
+            const int h = static_cast<int>((i / d) % heads);
+            const int64_t r = i / (static_cast<int64_t>(d) * heads);
+            const int64_t row = r < lo ? r : hi + (r - lo);
+            base[h * st[1] + row * st[2] + e] = zero;
+        }
+    };
+    clear(p.dq, p.dqs, p.heads, p.d, q_lo, q_hi, p.total_q);
+    clear(p.dk, p.dks, p.kv_heads, p.d, k_lo, k_hi, p.total_k);
+    clear(p.dv_out, p.dvs, p.kv_heads, p.dv, k_lo, k_hi, p.total_k);
+}
+
 extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream) {
     if (const char* why = backward_refusal(a)) {
         note_call(4);
@@ -334,6 +358,10 @@ extern "C" int ktt_b200_sdpa_backward(const ktt_b200_attn_args* a, void* stream)
         ? reinterpret_cast<int32_t*>(static_cast<unsigned char*>(a->workspace) + delta_bytes + backward_counter_offset(p, p.gsplit))
         : nullptr;
     note_call(2);
+    if (p.cu_q) {
+        zero_uncovered_rows_kernel<<<64, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+        if (int rc = check_cuda(cudaGetLastError(), "zero_uncovered_rows launch")) return rc;
+    }
     const char* why = nullptr;
     const bool tc5 = backward_tc5_takes(p, &why);
     if (a->kernel == KTT_B200_KERNEL_TC5 && !tc5) {

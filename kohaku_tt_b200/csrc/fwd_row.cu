@@ -22,7 +22,11 @@
 // which with tensor memory for two tiles (2 x 256 columns) means two threads per row. (Tried
 // and measured, not kept: making the two streams take turns at the exponential pass through
 // a lock per scheduler - slower, and locks on four schedulers can wait on one another in a
-// cycle; starting stream 1 late - the streams' phases made no difference.)
+// cycle; starting stream 1 late - the streams' phases made no difference; one pass over the
+// scores with the reference checked every 16 columns and P rescaled in tensor memory when it
+// moves - without any check the block period falls by only 10 %, and the check costs more
+// than that; ex2.approx.f16x2 for two exponentials per MUFU instruction - it issues at half
+// rate, 16.8 cycles per instruction and scheduler against 8.2.)
 // Tensor memory per stream (256 columns): S [0,128), P [128,192) as packed bf16 pairs,
 // O [192,256).
 //

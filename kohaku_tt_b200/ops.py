@@ -381,10 +381,11 @@ def varlen_backward(dout, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal=Fa
     if lse.dtype != torch.float32 or tuple(lse.shape) != (q.shape[1], q.shape[0]) or lse.stride(1) != 1:
         raise ValueError("kohaku_tt_b200: packed lse must be fp32 [H, Tq]")
     with torch.cuda.device(q.device):
-        # Rows of sequences without queries or keys are never visited: start from zero.
-        dq = torch.zeros(q.shape, dtype=q.dtype, device=q.device)
-        dk = torch.zeros(k.shape, dtype=k.dtype, device=k.device)
-        dv = torch.zeros(v.shape, dtype=v.dtype, device=v.device)
+        # No clearing: every row inside a sequence is written by the CTA that owns it (zeros
+        # where nothing reaches it) and the library zeroes the rows no sequence covers.
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
         args.out, args.lse, args.dout = out.data_ptr(), lse.data_ptr(), dout.data_ptr()
         args.dq, args.dk, args.dv_out = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         _set3(args.out_strides, _ths_strides(out))

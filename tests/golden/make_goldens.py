@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted (it cannot travel to a GPU box):
 
-    make -C oracle ref
+    make -C oracle ref REFERENCE=<reference>
     PYTHONPATH=<reference>/src python tests/golden/make_goldens.py
 
 Sources of truth used, all the reference's own code:
@@ -156,7 +156,7 @@ def main():
     # 5. The packed-sequence planner, through the reference's own header.
     exe = os.path.join(ROOT, "oracle", "_ref", "varlen_plan")
     if not os.path.exists(exe):
-        sys.exit("build oracle/_ref first: make -C oracle ref")
+        sys.exit("build oracle/_ref first: make -C oracle ref REFERENCE=<reference>")
     plans = []
     for lq, lk, causal in PLAN_CASES:
         cu_q, cu_k = cumulative(lq), cumulative(lk if lk is not None else lq)

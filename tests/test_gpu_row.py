@@ -50,6 +50,58 @@ def test_against_the_warp_mma_kernel_and_float64_rows(cuda, b, h, hk, s, causal)
         assert rms(lse[bi, hi, rows.to(cuda)], ruler_lse) <= LSE_RMS
 
 
+def _full_ruler(q, k, v, causal):
+    """float64 attention of every row (small sizes)."""
+    group = q.shape[1] // k.shape[1]
+    kk = k.double().repeat_interleave(group, dim=1)
+    vv = v.double().repeat_interleave(group, dim=1)
+    scores = q.double() @ kk.transpose(-1, -2) / math.sqrt(q.shape[-1])
+    if causal:
+        sq, sk = q.shape[2], k.shape[2]
+        hidden = torch.arange(sk)[None, :] > torch.arange(sq)[:, None] + (sk - sq)
+        scores = scores.masked_fill(hidden, float("-inf"))
+    return torch.softmax(scores, dim=-1) @ vv, torch.logsumexp(scores, dim=-1)
+
+
+# How the keys' magnitude runs along the sequence. The kernel rescales a row's running sum
+# and output lazily, only when a block's maximum exceeds the reference by more than 2^8, and
+# the row's two threads agree on each block's maximum through a 16-bit exchange. `rising` and
+# `steps` move the reference in every block by hundreds, `falling` leaves the first reference
+# far above everything after it, `spike` puts one huge key in the middle of a late block,
+# `halves` makes the two threads of a row see very different maxima.
+@pytest.mark.parametrize("profile", ["rising", "falling", "steps", "spike", "halves"])
+@pytest.mark.parametrize("s,causal", [(640, False), (640, True), (2048, True)])
+def test_references_that_move_inside_a_block(cuda, profile, s, causal):
+    q, k, v = qkv(1, 4, 2, s, s, 64, 11 + s)
+    pos = torch.arange(s, dtype=torch.float32)
+    if profile == "rising":
+        gain = 1.0 + pos * (60.0 / s)
+    elif profile == "falling":
+        gain = 60.0 - pos * (59.0 / s)
+    elif profile == "steps":
+        gain = 1.0 + 40.0 * ((pos // 16) % 5)
+    elif profile == "spike":
+        gain = torch.ones(s)
+        gain[s - 150] = 300.0
+        gain[200] = 80.0
+    else:
+        gain = torch.where((pos // 64) % 2 == 1, 50.0, 1.0)
+    k = (k.float() * gain[None, None, :, None]).to(torch.bfloat16)
+    qc, kc, vc = q.to(cuda), k.to(cuda), v.to(cuda)
+    out, lse = ops.sdpa_forward(qc, kc, vc, causal=causal, kernel="flash")
+    again, again_lse = ops.sdpa_forward(qc, kc, vc, causal=causal, kernel="flash", dynamic=False)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    assert torch.equal(out, again) and torch.equal(lse, again_lse)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    ruler, ruler_lse = _full_ruler(q, k, v, causal)
+    assert rel(out.cpu(), ruler) <= FWD_BOUND
+    # lse grows with the logits here (hundreds): compare relative to its size.
+    assert ((lse.cpu().double() - ruler_lse).abs() / ruler_lse.abs().clamp_min(1.0)).max().item() <= 1e-5
+    ref, _ = ops.sdpa_forward(qc, kc, vc, causal=causal, kernel="mma")
+    assert rel(out.float(), ref.float()) <= 4e-3
+
+
 def test_shared_tiles_give_the_same_bits_every_time(cuda):
     # 224 tiles on 148 SMs: every tile is shared by the two streams of a CTA. Which CTA draws
     # which tile differs from launch to launch; the bits must not.

@@ -120,6 +120,37 @@ def test_backward_sets(cuda, lq, lk, h, hk, d, causal):
                 assert gv[ck[b]:ck[b + 1]].abs().max() == 0
 
 
+def _poison_free_memory(cuda, like):
+    """Leaves NaN patterns in freed blocks the size of the gradients, so that a row the
+    backward does not write shows (torch.empty hands such blocks back)."""
+    junk = [torch.full(t.shape, float("nan"), dtype=t.dtype, device=cuda) for t in like for _ in range(2)]
+    torch.cuda.synchronize()
+    del junk
+
+
+@pytest.mark.parametrize("kernel", ["mma", "flash"])
+def test_rows_outside_the_offsets_get_zero_gradients(cuda, kernel):
+    # The gradients are not cleared by the caller: rows of sequences are written by their
+    # owners, rows before the first offset and after the last are zeroed by the library.
+    lq, lk = [40, 0, 90], [25, 70, 33]
+    q, k, v, do = packed(lq + [17], lk + [9], 2, 1, 64, 77, extra=1)   # 17 / 9 rows no offset covers
+    cq, ck = cumulative(lq), cumulative(lk)
+    tq, tk = cq[-1], ck[-1]
+    _, dq, dk, dv = ao.ruler_varlen(q[:tq], k[:tk], v[:tk], cq, ck, causal=False, dout=do[:tq])
+    qc, kc, vc, doc = (t.to(cuda) for t in (q, k, v, do))
+    out, lse = ops.varlen_forward(qc, kc, vc, cu(lq, cuda), cu(lk, cuda), max(lq), max(lk), kernel=kernel)
+    _poison_free_memory(cuda, (qc, kc, vc))
+    gq, gk, gv = ops.varlen_backward(doc, qc, kc, vc, out, lse, cu(lq, cuda), cu(lk, cuda),
+                                     max(lq), max(lk), kernel=kernel)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    for got, want, n in ((gq, dq, tq), (gk, dk, tk), (gv, dv, tk)):
+        assert torch.isfinite(got.float()).all()
+        assert rel(got[:n], want) <= VARLEN_GRAD_BOUND
+        assert got[n:].abs().max() == 0
+    assert gk[ck[1]:ck[2]].abs().max() == 0 and gv[ck[1]:ck[2]].abs().max() == 0
+
+
 def test_edge_sets(cuda):
     # test_flash_varlen_gaps.py:120-308: one long sequence, a long + short pair, Dv != D,
     # an explicit scale, 40 different lengths.
