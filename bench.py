@@ -329,13 +329,11 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # The ring leg's send / recv kernels run beside the persistent attention kernels: a
-        # few NCCL CTAs move 134 MB per step in well under a step's compute, and every SM
-        # they do not take keeps its attention CTA.
-        opts = torch.distributed.ProcessGroupNCCL.Options()
-        opts.config.max_ctas = 4
-        opts.config.min_ctas = 1
-        torch.distributed.init_process_group("nccl", device_id=dev, pg_options=opts)
+        # NCCL keeps its default CTA budget. Measured on two GPUs with the ring leg: capping
+        # its send / recv kernels at 4 or 8 CTAs (so that the persistent attention kernels keep
+        # more SMs) costs 15-20 % (the exchange then outlasts a step's compute); 16, 32 and no
+        # cap are within noise of one another.
+        torch.distributed.init_process_group("nccl", device_id=dev)
 
     import torch.nn.functional as F
 
@@ -775,6 +773,32 @@ def leg_decode(dev, peaks, warmup):
             "parity_vs_f64": dict(stats_of(out, ruler), sample="all 64 x 16 (batch, head) pairs, full float64")}
 
 
+def leg_plain_read(dev, peaks, warmup):
+    """For scale beside the decode leg: a kernel that only reads the decode workload's byte
+    count (two buffers alternating, so nothing survives in L2) with 16-byte grid-stride
+    loads and does nothing else. The decode kernel cannot be faster than this on its bytes."""
+    import ctypes
+
+    from kohaku_tt_b200 import _lib
+
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.randint(512, 4097, (64,), generator=g, dtype=torch.int32)
+    nbytes = int(lengths.sum()) * 2 * (128 + 128) * 2
+    bufs = [torch.full((nbytes // 4,), i + 1, dtype=torch.int32, device=dev) for i in range(2)]
+    sink = torch.zeros((1,), dtype=torch.int32, device=dev)
+    handle = _lib.lib()
+
+    def read(i):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(handle.ktt_b200_probe_read(ctypes.c_void_p(bufs[i % 2].data_ptr()), nbytes,
+                                              ctypes.c_void_p(sink.data_ptr()), stream), "probe_read")
+
+    ms = _time(read, 50, warmup)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"value": gbs, "ms": ms, "bytes": float(nbytes), "frac_of_measured_hbm": gbs / peaks["hbm"],
+            "workload": "read-only kernel over the decode leg's byte count, cold, 16-byte grid-stride loads"}
+
+
 def leg_decode_step(dev, peaks, warmup):
     """One decode token with its neighbours: rotary on q and the new key, cache append,
     attention. The fused launch beside the same work as separate ops (rotary by torch
@@ -965,6 +989,7 @@ LEGS = {
     "fwd_d128_tflops": leg_fwd_d128,
     "decode_kv_gbs": leg_decode,
     "decode_step_gbs": leg_decode_step,
+    "plain_read_gbs": leg_plain_read,
     "sdxl_self_tflops": leg_sdxl_self,
     "sdxl_cross_ms": leg_sdxl_cross,
     "varlen_tflops": leg_varlen,

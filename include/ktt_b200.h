@@ -175,6 +175,13 @@ KTT_B200_API int ktt_b200_device_status(int* code);
  * for longer than the limit. */
 KTT_B200_API int ktt_b200_selftest_wait_timeout(void* stream);
 
+/* Measurement support: reads `bytes` (a multiple of 16, 16-byte aligned) of device memory
+ * once with 16-byte loads dealt grid-stride over two CTAs per SM, and discards them. What a
+ * plain read of a buffer of that size reaches on this GPU is the yardstick the decode
+ * kernel's GB/s is put beside; `sink` (one int32) only keeps the loads alive. No
+ * counterpart in the reference. */
+KTT_B200_API int ktt_b200_probe_read(const void* data, int64_t bytes, int32_t* sink, void* stream);
+
 /* Profiling zones, the counterpart of the reference's FLASH_PROFILE device zones
  * (ktt_flash/compute.cpp:25-30, program.hpp:56-65): with a device buffer of 64 x 8 int64
  * set, CTA (0, 0, 0) of every tcgen05 forward launch stamps clock64 per key block (slots:

@@ -45,6 +45,7 @@ EXPORTS = (
     "ktt_b200_reset_counters",
     "ktt_b200_device_status",
     "ktt_b200_selftest_wait_timeout",
+    "ktt_b200_probe_read",
     "ktt_b200_set_trace",
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
@@ -278,6 +279,7 @@ def lib():
     handle.ktt_b200_decode_append.argtypes = [ctypes.POINTER(DecodeAppendArgs), _ptr]
     handle.ktt_b200_set_trace.argtypes = [_ptr]
     handle.ktt_b200_selftest_wait_timeout.argtypes = [_ptr]
+    handle.ktt_b200_probe_read.argtypes = [_ptr, ctypes.c_int64, _ptr, _ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]
     if handle.ktt_b200_abi_version() != 1:
         raise RuntimeError("kohaku_tt_b200: libktt_b200.so has another ABI version")
