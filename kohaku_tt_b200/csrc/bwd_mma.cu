@@ -29,6 +29,7 @@ __device__ __forceinline__ void zero_counters(int32_t* counters, int64_t n) {
 
 // delta[b, h, i] = sum_d dO * O, one warp per row (any width and alignment).
 __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p, int64_t ncounters) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     zero_counters(p.dkv_counters, ncounters);
     const int b = blockIdx.z, h = blockIdx.y;
     const SeqInfo si = seq_info(p, b);
@@ -50,6 +51,9 @@ __global__ void __launch_bounds__(kThreads) bwd_delta_kernel(const AttnParams p,
 // Needs Dv in {64, 128} and 16-byte aligned rows (the launcher checks).
 template <int DV>
 __global__ void __launch_bounds__(256) bwd_delta_vec_kernel(const AttnParams p, int64_t ncounters) {
+    // The backward kernel behind this one may start its set-up and input loads now; it waits
+    // (griddepcontrol.wait) for this kernel to finish before it reads delta or the tickets.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     zero_counters(p.dkv_counters, ncounters);
     constexpr int LANES = DV / 8, ROWS = 256 / LANES;
     const int b = blockIdx.z, h = blockIdx.y;

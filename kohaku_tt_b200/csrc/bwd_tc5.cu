@@ -46,6 +46,7 @@ struct BwdParams {
     AttnParams a;
     int* status;
     int dim_of[4][3];  // q, k, v, dout: tensor-map coordinate slot of row, head, batch
+    long long* trace;  // optional (ktt_b200_set_trace): per-CTA start / end / SM
 };
 
 
@@ -95,6 +96,15 @@ __device__ __forceinline__ void init_barriers(uint32_t bars, volatile int* abort
     fence_async_smem();
 }
 
+// Phase stamp of a CTA's first thread (slots 4..7 of its trace row), while a buffer is set.
+__device__ __forceinline__ void mark(const BwdParams& tp, int slot) {
+    if (tp.trace && threadIdx.x == 0 && blockIdx.x < 1024) {
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        tp.trace[(64 + blockIdx.x) * 8 + slot] = t;
+    }
+}
+
 // ---- dK / dV ----------------------------------------------------------------------------
 
 // Body of one dK/dV CTA; (bx, by, bz) = (kv head * gsplit + part, key block, batch).
@@ -140,26 +150,35 @@ __device__ __forceinline__ void dkv_body(
     const int per_head = (any_key && nq > qstart) ? nq - qstart : 0;
     const int nitems = per_head * group;
 
-    if (threadIdx.x == 0) init_barriers<D>(bars, abort_flag);
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    // S^T buffers at columns 0 and (D 64 only) 384; dP^T 128; dV 256; dK 256 + D.
-    constexpr int kSBufs = 256 + 2 * D + 128 <= kTmemCols ? 2 : 1;
-    const uint32_t tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 256 + D;
-    auto tmem_s_of = [&](int it) { return tmem + ((kSBufs == 2 && (it & 1)) ? 384u : 0u); };
-
     auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
         c[tp.dim_of[operand][0]] = row;
         c[tp.dim_of[operand][1]] = head;
         c[tp.dim_of[operand][2]] = batch;
     };
     const int batch_c = p.cu_q ? 0 : b;
+    // Q and dO tiles of item `it` into their ring stage (producer warp, converged).
+    auto load_item = [&](int it) {
+        int c[4], c2[4];
+        c[0] = c2[0] = 0;
+        const int st = it % P::kStages;
+        const int h = hk * full_group + g0 + it / per_head;
+        const int q0 = (qstart + it % per_head) * kBN;
+        coords(0, si.q_off + q0, h, batch_c, c);
+        coords(3, si.q_off + q0, h, batch_c, c2);
+        mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
+        for (int s = 0; s < P::kSub; ++s) {
+            tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_q, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
+            tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_do, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
+        }
+    };
 
+    // Set-up. The producer warp initialises the barriers itself and sends the CTA's first
+    // loads (K, V and the first ring stages; none of them is written by the delta kernel this
+    // launch may overlap) while warp 8 allocates tensor memory and the rest wait.
+    int issued = 0;
     if (warp == 9) {
-        // ---------------- producer ----------------
+        if (lane == 0) init_barriers<D>(bars, abort_flag);
+        __syncwarp();
         if (nitems > 0) {
             int c[4], c2[4];
             c[0] = c2[0] = 0;
@@ -170,21 +189,30 @@ __device__ __forceinline__ void dkv_body(
                 tma_load_4d(sbase + P::kA0 + s * P::kTile, &map_k, bar(P::bAFull), s * 64, c[1], c[2], c[3]);
                 tma_load_4d(sbase + P::kA1 + s * P::kTile, &map_v, bar(P::bAFull), s * 64, c2[1], c2[2], c2[3]);
             }
-            int issued = 0;
-            for (int it = 0; it < nitems; ++it) {
+            for (; issued < nitems && issued < P::kStages; ++issued) load_item(issued);
+        }
+    }
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    // Everything below may read what the previous kernel in the stream wrote (delta, the
+    // zeroed tickets): wait for it here (programmatic dependent launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    mark(tp, 4);   // set-up done
+    // S^T buffers at columns 0 and (D 64 only) 384; dP^T 128; dV 256; dK 256 + D.
+    constexpr int kSBufs = 256 + 2 * D + 128 <= kTmemCols ? 2 : 1;
+    const uint32_t tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 256 + D;
+    auto tmem_s_of = [&](int it) { return tmem + ((kSBufs == 2 && (it & 1)) ? 384u : 0u); };
+
+    if (warp == 9) {
+        // ---------------- producer ----------------
+        if (nitems > 0) {
+            for (int it = issued; it < nitems; ++it) {
                 const int st = it % P::kStages;
-                if (it >= P::kStages) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((it / P::kStages) - 1) & 1, abort_flag, 400 + st, tp.status))) break;
-                }
-                const int h = hk * full_group + g0 + it / per_head;
-                const int q0 = (qstart + it % per_head) * kBN;
-                coords(0, si.q_off + q0, h, batch_c, c);
-                coords(3, si.q_off + q0, h, batch_c, c2);
-                mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
-                for (int s = 0; s < P::kSub; ++s) {
-                    tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_q, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
-                    tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_do, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
-                }
+                if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((it / P::kStages) - 1) & 1, abort_flag, 400 + st, tp.status))) break;
+                load_item(it);
                 ++issued;
             }
             if (*abort_flag) {
@@ -327,6 +355,7 @@ __device__ __forceinline__ void dkv_body(
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + it % kSBufs), (it / kSBufs) & 1, abort_flag, 600 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            if (it == 0) mark(tp, 5);   // first scores
             // Column c of this half is query q0 + g * 64 + c; key kk sees it when
             // kk <= q + shift, i.e. c >= first_col.
             const int first_col = p.causal ? kk - si.shift - q0 - g * 64 : -1;
@@ -396,6 +425,7 @@ __device__ __forceinline__ void dkv_body(
         // sequence are not stored. Every lane takes part in the TMEM reads. With the GQA
         // group split over several CTAs the fp32 sums go to the partial buffer instead.
         if (ok && nitems > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 610, tp.status));
+        mark(tp, 6);   // last MMA done
         if (ok) {
             const bool real = kk < si.lk;
             const float mul = g == 0 ? 1.f : p.scale;
@@ -436,6 +466,7 @@ __device__ __forceinline__ void dkv_body(
                 }
             }
         }
+        mark(tp, 7);   // own results stored
         if (p.gsplit > 1 && p.dkv_counters) {
             // The CTAs sharing this key block take a ticket each once their partial is
             // stored; the one that draws the last sums the partials in the order of the
@@ -452,31 +483,54 @@ __device__ __forceinline__ void dkv_body(
                 *last_flag = ok && ticket == p.gsplit - 1;
             }
             met = meet(641) && met;
-            if (met && *last_flag && kk < si.lk) {
+            if (met && *last_flag) {
+                // The 128 threads of a group sum their plane (dV or dK) of the key block: 128
+                // rows x D fp32 per part, contiguous, taken as float4 positions dealt round-robin
+                // to the threads so that a warp reads 512 contiguous bytes per part. All parts
+                // of two positions are requested before any is used (the sums wait for L2 once
+                // per two positions, not once per part), and are added in the order of the
+                // parts: the same bits whoever is last.
                 const float mul = g == 0 ? 1.f : p.scale;
-                __nv_bfloat16* dst = g == 0
-                    ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] + static_cast<int64_t>(si.k_off + kk) * p.dvs[2]
-                    : p.dk + b * p.dks[0] + hk * p.dks[1] + static_cast<int64_t>(si.k_off + kk) * p.dks[2];
+                __nv_bfloat16* dst = g == 0 ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] : p.dk + b * p.dks[0] + hk * p.dks[1];
+                const int64_t dst_row = g == 0 ? p.dvs[2] : p.dks[2];
                 const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
                 const int64_t planes = static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * p.gsplit;
                 const float* src = p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit) * key_rows * D +
-                                   static_cast<int64_t>(si.k_off + kk) * D;
-#pragma unroll 2
-                for (int c8 = 0; c8 < D / 8; ++c8) {
-                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-                    for (int s_ = 0; s_ < p.gsplit; ++s_) {
-                        const float4 x = __ldcg(reinterpret_cast<const float4*>(src + s_ * key_rows * D + c8 * 8));
-                        const float4 y = __ldcg(reinterpret_cast<const float4*>(src + s_ * key_rows * D + c8 * 8 + 4));
-                        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-                        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                                   static_cast<int64_t>(si.k_off + k0) * D;
+                const int64_t part_stride = key_rows * D;
+                constexpr int kPositions = 128 * D / 4 / 128;   // float4 positions per thread
+                constexpr int kMaxParts = 8;                    // backward_group_split never asks for more
+                for (int i = 0; i < kPositions; i += 2) {
+                    float4 part[2][kMaxParts];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int f = (i + u) * 128 + row;
+#pragma unroll
+                        for (int s_ = 0; s_ < kMaxParts; ++s_) {
+                            if (s_ < p.gsplit) part[u][s_] = __ldcg(reinterpret_cast<const float4*>(src + s_ * part_stride) + f);
+                        }
                     }
-                    uint4 v;
-                    v.x = pack_bf16(acc[0] * mul, acc[1] * mul);
-                    v.y = pack_bf16(acc[2] * mul, acc[3] * mul);
-                    v.z = pack_bf16(acc[4] * mul, acc[5] * mul);
-                    v.w = pack_bf16(acc[6] * mul, acc[7] * mul);
-                    *reinterpret_cast<uint4*>(dst + c8 * 8) = v;
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int f = (i + u) * 128 + row;
+                        const int r = f / (D / 4), c4 = f % (D / 4);
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int s_ = 0; s_ < kMaxParts; ++s_) {
+                            if (s_ < p.gsplit) {
+                                acc.x += part[u][s_].x;
+                                acc.y += part[u][s_].y;
+                                acc.z += part[u][s_].z;
+                                acc.w += part[u][s_].w;
+                            }
+                        }
+                        if (k0 + r < si.lk) {
+                            uint2 v;
+                            v.x = pack_bf16(acc.x * mul, acc.y * mul);
+                            v.y = pack_bf16(acc.z * mul, acc.w * mul);
+                            *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(si.k_off + k0 + r) * dst_row + c4 * 4) = v;
+                        }
+                    }
                 }
             }
         }
@@ -530,24 +584,32 @@ __device__ __forceinline__ void dq_body(
     if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
     const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
 
-    if (threadIdx.x == 0) init_barriers<D>(bars, abort_flag);
-    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    // S buffers at columns 0 and 384, dP 128, dQ 256 (D <= 128 columns).
-    const uint32_t tmem_dp = tmem + 128, tmem_dq = tmem + 256;
-    auto tmem_s_of = [&](int j) { return tmem + ((j & 1) ? 384u : 0u); };
-
     auto coords = [&](int operand, int row, int head, int batch, int (&c)[4]) {
         c[tp.dim_of[operand][0]] = row;
         c[tp.dim_of[operand][1]] = head;
         c[tp.dim_of[operand][2]] = batch;
     };
     const int batch_c = p.cu_q ? 0 : b;
+    // K and V tiles of key block j into their ring stage (producer warp, converged).
+    auto load_block = [&](int j) {
+        int c[4], c2[4];
+        c[0] = c2[0] = 0;
+        const int st = j % P::kStages;
+        coords(1, si.k_off + j * kBN, hk, batch_c, c);
+        coords(2, si.k_off + j * kBN, hk, batch_c, c2);
+        mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
+        for (int s = 0; s < P::kSub; ++s) {
+            tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
+            tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
+        }
+    };
 
+    // Set-up as in the dK/dV body: the producer warp initialises the barriers and sends the
+    // first loads while tensor memory is being allocated.
+    int issued = 0;
     if (warp == 9) {
+        if (lane == 0) init_barriers<D>(bars, abort_flag);
+        __syncwarp();
         if (nblocks > 0) {
             int c[4], c2[4];
             c[0] = c2[0] = 0;
@@ -558,19 +620,26 @@ __device__ __forceinline__ void dq_body(
                 tma_load_4d(sbase + P::kA0 + s * P::kTile, &map_q, bar(P::bAFull), s * 64, c[1], c[2], c[3]);
                 tma_load_4d(sbase + P::kA1 + s * P::kTile, &map_do, bar(P::bAFull), s * 64, c2[1], c2[2], c2[3]);
             }
-            int issued = 0;
-            for (int j = 0; j < nblocks; ++j) {
+            for (; issued < nblocks && issued < P::kStages; ++issued) load_block(issued);
+        }
+    }
+    if (warp == 8) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // delta comes from the previous kernel in the stream
+    const uint32_t tmem = *tmem_slot;
+    mark(tp, 4);
+    // S buffers at columns 0 and 384, dP 128, dQ 256 (D <= 128 columns).
+    const uint32_t tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    auto tmem_s_of = [&](int j) { return tmem + ((j & 1) ? 384u : 0u); };
+
+    if (warp == 9) {
+        if (nblocks > 0) {
+            for (int j = issued; j < nblocks; ++j) {
                 const int st = j % P::kStages;
-                if (j >= P::kStages) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 700 + st, tp.status))) break;
-                }
-                coords(1, si.k_off + j * kBN, hk, batch_c, c);
-                coords(2, si.k_off + j * kBN, hk, batch_c, c2);
-                mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
-                for (int s = 0; s < P::kSub; ++s) {
-                    tma_load_4d(sbase + P::kB0 + (st * P::kSub + s) * P::kTile, &map_k, bar(P::bBFull + st), s * 64, c[1], c[2], c[3]);
-                    tma_load_4d(sbase + P::kB1 + (st * P::kSub + s) * P::kTile, &map_v, bar(P::bBFull + st), s * 64, c2[1], c2[2], c2[3]);
-                }
+                if (!__all_sync(0xffffffffu, mbar_wait(bar(P::bBEmpty + st), ((j / P::kStages) - 1) & 1, abort_flag, 700 + st, tp.status))) break;
+                load_block(j);
                 ++issued;
             }
             if (*abort_flag) {
@@ -682,6 +751,7 @@ __device__ __forceinline__ void dq_body(
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + (j & 1)), (j >> 1) & 1, abort_flag, 900 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            if (j == 0) mark(tp, 5);
             const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
             // Phase 1: P in registers while dP of this block is still being computed. Two
             // values per instruction on the packed fp32 pipe; wholly visible halves skip the
@@ -736,6 +806,7 @@ __device__ __forceinline__ void dq_body(
         }
 
         if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 910, tp.status));
+        mark(tp, 6);
         if (ok) {
             // Group g writes dQ columns [g * D / 2, (g + 1) * D / 2), scaled.
             const bool real = qi < si.lq;
@@ -788,6 +859,25 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc5_kernel(
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const BwdParams tp, int dkv_x, int dkv_y, int n_dkv, int dq_x, int dq_y) {
     int id = blockIdx.x;
+    long long t_start = 0;
+    if (tp.trace && threadIdx.x == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
+    struct Stamp {   // while a trace buffer is set: start, end, SM and index of every CTA (rows 64 + CTA)
+        const BwdParams& tp;
+        long long t0;
+        __device__ ~Stamp() {
+            if (tp.trace && threadIdx.x == 0 && blockIdx.x < 1024) {
+                long long t1;
+                unsigned smid;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                long long* out = tp.trace + (64 + blockIdx.x) * 8;
+                out[0] = t0;
+                out[1] = t1;
+                out[2] = smid;
+                out[3] = blockIdx.x;
+            }
+        }
+    } stamp{tp, t_start};
     if (id < n_dkv) {
         dkv_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id % dkv_x, (id / dkv_x) % dkv_y, id / (dkv_x * dkv_y), dkv_y);
     } else {
@@ -838,6 +928,7 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
         return fail(KTT_B200_ERR_DEVICE_WAIT, "an earlier tcgen05 launch gave up waiting (code %d)", code);
     }
     tp.status = dev_status;
+    tp.trace = tc5::trace_buffer();
     for (int o = 0; o < 4; ++o) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
@@ -851,9 +942,20 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
     const int64_t n_all = n_dkv + static_cast<int64_t>(dq_x) * dq_y * p.batch;
     if (n_all > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: too many tiles");
     if (p.gsplit > 1 && !p.dkv_counters) return fail(KTT_B200_ERR_BAD_ARGUMENT, "tcgen05 backward: the group split needs its ticket counters");
-    kernel<<<static_cast<unsigned>(n_all), kThreads, smem, stream>>>(
-        mq, mk, mv, mdo, tp, dkv_x, dkv_y, static_cast<int>(n_dkv), dq_x, dq_y);
-    return check_cuda(cudaGetLastError(), "bwd_tc5 launch");
+    // Programmatic dependent launch behind the delta kernel: set-up and the first loads of
+    // every CTA of the first wave run while that kernel drains.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(n_all));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, mdo, tp, dkv_x, dkv_y, static_cast<int>(n_dkv), dq_x, dq_y),
+                      "bwd_tc5 launch");
 }
 
 }  // namespace
@@ -876,7 +978,8 @@ int backward_group_split(const AttnParams& p) {
     const int64_t ctas = static_cast<int64_t>(p.batch) * p.kv_heads * ((p.sk + kBM - 1) / kBM);
     const int64_t want = ctas > 0 ? 256 / ctas : 1;
     if (want <= 1) return 1;
-    return static_cast<int>(want < group ? want : group);
+    const int64_t cap = want < group ? want : group;
+    return static_cast<int>(cap < 8 ? cap : 8);   // the ticketed sum holds at most 8 parts at a time
 }
 
 int64_t backward_counter_offset(const AttnParams& p, int gsplit) {
