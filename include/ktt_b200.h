@@ -188,9 +188,14 @@ KTT_B200_API int ktt_b200_probe_read(const void* data, int64_t bytes, int32_t* s
  * S ready, pass 1 done, previous P V done, pass 2 done, P published, MMA lane before the
  * next Q K^T, after the wait for P, after issuing P V), and rows 64 .. 64 + 1023 receive per
  * CTA its start and end on the global nanosecond timer, its SM and its key-block count; the
- * buffer then holds (64 + 1024) x 8 int64. The decode kernel writes, per CTA, rows 64.. with
- * six nanosecond stamps: start, dependency wait over, lengths scanned, first tile landed,
- * stream done, end. NULL turns it off (default). */
+ * buffer then holds (64 + 1024) x 8 int64. (The head-dim-64 forward's slots per key block:
+ * S ready, maximum known, exponentials done, P published, first chunk loaded, its
+ * exponentials done, previous P V done, second chunk loaded; row 60 holds its epilogue.)
+ * The decode kernel writes, per CTA, rows 64.. with six nanosecond stamps: start,
+ * dependency wait over, lengths scanned, first tile landed, stream done, end. The tcgen05
+ * backward writes, per CTA, rows 64..: start, end, SM, CTA index, set-up done, first scores,
+ * last MMA done, results stored. kohaku_tt_b200/trace.py reads all three. NULL turns it
+ * off (default). */
 KTT_B200_API int ktt_b200_set_trace(void* device_buffer);
 
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward
