@@ -10,10 +10,11 @@
 //
 //   plan    : every CTA scans ceil(len_b / 64) over the batch into shared memory (the
 //             lengths stay on the device; batch <= 512)
-//   stream  : CTA c owns tile units [c*upc, (c+1)*upc) of the (batch, kv head) pairs laid
-//             end to end. K/V rows arrive by 16-byte cp.async into a swizzled ring of
-//             stages, one private pipeline per warp (16 keys per tile each), scores and
-//             P.V on warp MMA, running max / sum in fp32.
+//   stream  : CTA c owns the tiles whose unit lies in [c*upc, (c+1)*upc) of the (batch, kv
+//             head) pairs laid end to end (a pair's last tile weighs 1 + kPairCost units).
+//             K/V rows arrive by 16-byte cp.async into a swizzled ring of stages, one
+//             private pipeline per warp (16 keys per tile each), scores and P.V on warp
+//             MMA, running max / sum in fp32.
 //   finish  : a pair that lies inside one CTA is normalised and written at once. Otherwise
 //             each CTA stores its unnormalised partial (O, m, l) in fp32 scratch and takes
 //             a ticket on the pair's counter; the CTA that draws the last ticket merges the
@@ -68,6 +69,10 @@ constexpr int kTile = 64;      // keys per tile (16 per warp)
 constexpr int kThreads = 128;
 constexpr int kMaxBatch = 512;   // clamped lengths and their prefix sums live in shared memory
 constexpr int kMaxPending = 8;   // stored partials per CTA before their tickets are drawn
+// Ending a (batch, kv head) pair costs a CTA about as much as streaming two tiles (the four
+// warps' states are merged, the result is written, the next pair's query is fetched): the
+// shares are cut in units in which a pair's last tile weighs 1 + kPairCost.
+constexpr int kPairCost = 2;
 constexpr int kMaxCtas = 1024;   // ticket counters in the scratch
 
 // Keys batch b attends over. Append mode: the cached count clamped to [0, sk - 1], plus the
@@ -100,7 +105,8 @@ __device__ __forceinline__ uint32_t rope_pair(const __nv_bfloat16* x, const __nv
                      __fadd_rn(__fmul_rn(a.y, co.y), __fmul_rn(r1, si.y)));
 }
 
-// prefix[b] = sum_{b' < b} ceil(len_b' / 64) for b in [0, batch], by one CTA of 128 threads.
+// prefix[b] = sum_{b' < b} (ceil(len_b' / 64) + kPairCost) for b in [0, batch], by one CTA of
+// 128 threads: the units of one kv head's pass over batch entries [0, b).
 template <bool kAppend>
 __device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix, int* lens, int* warp_sums) {
     constexpr int kPer = kMaxBatch / kThreads;  // consecutive entries per thread
@@ -111,7 +117,7 @@ __device__ __forceinline__ void scan_lengths(const DecodeParams& p, int* prefix,
         const int b = threadIdx.x * kPer + i;
         const int len = b < p.batch ? clamp_len<kAppend>(p, b) : 0;
         if (b < p.batch) lens[b] = len;
-        tiles[i] = (len + kTile - 1) / kTile;
+        tiles[i] = b < p.batch ? (len + kTile - 1) / kTile + kPairCost : 0;
         mine += tiles[i];
     }
     int x = mine;
@@ -139,19 +145,46 @@ struct Cursor {
     int b, hk, tile, ntiles, len;
 };
 
-__device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* prefix, const int* lens, Cursor& c, int unit) {
-    // Largest b with kv_heads * prefix[b] <= unit.
+// Largest b with kv_heads * prefix[b] <= unit.
+__device__ __forceinline__ int entry_of(const DecodeParams& p, const int* prefix, int unit) {
     int lo = 0, hi = p.batch - 1;
     while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
         if (p.kv_heads * prefix[mid] <= unit) lo = mid; else hi = mid - 1;
     }
-    c.b = lo;
-    c.ntiles = prefix[lo + 1] - prefix[lo];
-    c.len = lens[lo];
-    const int rem = unit - p.kv_heads * prefix[lo];
-    c.hk = rem / c.ntiles;
-    c.tile = rem % c.ntiles;
+    return lo;
+}
+
+// Tiles whose unit lies before `unit` (a pair's units: its tiles, then kPairCost units that
+// belong to its last tile).
+__device__ __forceinline__ int tiles_before(const DecodeParams& p, const int* prefix, int unit) {
+    const int b = entry_of(p, prefix, unit);
+    const int span = prefix[b + 1] - prefix[b], ntiles = span - kPairCost;
+    const int rem = unit - p.kv_heads * prefix[b];
+    const int hk = rem / span, pos = rem % span;
+    return p.kv_heads * (prefix[b] - kPairCost * b) + hk * ntiles + min(pos, ntiles);
+}
+
+// The first tile at or after `unit`.
+__device__ __forceinline__ void cursor_seek(const DecodeParams& p, const int* prefix, const int* lens, Cursor& c, int unit) {
+    const int b = entry_of(p, prefix, unit);
+    const int span = prefix[b + 1] - prefix[b];
+    c.b = b;
+    c.ntiles = span - kPairCost;
+    c.len = lens[b];
+    const int rem = unit - p.kv_heads * prefix[b];
+    c.hk = rem / span;
+    c.tile = rem % span;
+    if (c.tile >= c.ntiles) {   // inside a pair's closing units: the next pair's first tile
+        c.tile = 0;
+        if (++c.hk == p.kv_heads) {
+            c.hk = 0;
+            if (++c.b < p.batch) {
+                c.len = lens[c.b];
+                c.ntiles = prefix[c.b + 1] - prefix[c.b] - kPairCost;
+            }
+        }
+    }
 }
 
 __device__ __forceinline__ void cursor_next(const DecodeParams& p, const int* prefix, const int* lens, Cursor& c) {
@@ -161,7 +194,7 @@ __device__ __forceinline__ void cursor_next(const DecodeParams& p, const int* pr
     c.hk = 0;
     if (++c.b < p.batch) {
         c.len = lens[c.b];
-        c.ntiles = prefix[c.b + 1] - prefix[c.b];
+        c.ntiles = prefix[c.b + 1] - prefix[c.b] - kPairCost;
     }
 }
 
@@ -177,8 +210,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     constexpr int kStage = 2 * kTile * D * 2;  // K then V, bytes
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;
-    float* acc = reinterpret_cast<float*>(smem + NS * kStage);  // [16][D]
-    float* sm_m = acc + 16 * D;                                 // [4][16]
+    float* sm_m = reinterpret_cast<float*>(smem + NS * kStage);  // [4][16]
     float* sm_l = sm_m + 64;                                    // [4][16]
     float* fin_m = sm_l + 64;                                   // [16] merged maxima of a segment
     float* fin_l = fin_m + 16;                                  // [16] merged sums
@@ -201,6 +233,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             p.trace[(64 + blockIdx.x) * 8 + slot] = t;
+            if (slot == 0) {
+                unsigned smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                p.trace[(64 + blockIdx.x) * 8 + 6] = smid;
+            }
         }
     };
     stamp(0);
@@ -213,14 +250,16 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
     if (kAppend && blockIdx.x == 0 && p.lengths_out) {
         for (int b = threadIdx.x; b < p.batch; b += kThreads) p.lengths_out[b] = lens_s[b];
     }
+    // Equal shares of units; this CTA streams the tiles whose unit lies in its share.
     const int total = p.kv_heads * prefix_s[p.batch];
     const int upc = (total + gridDim.x - 1) / gridDim.x;
-    const int u0 = blockIdx.x * upc;
-    const int u1 = min(u0 + upc, total);
-    if (u0 >= u1) return;
+    const int first_unit = min(static_cast<int>(blockIdx.x) * upc, total), end_unit = min(first_unit + upc, total);
+    const int u0 = 0;
+    const int u1 = tiles_before(p, prefix_s, end_unit) - tiles_before(p, prefix_s, first_unit);
+    if (u1 <= 0) return;
 
     Cursor prod, cons;
-    cursor_seek(p, prefix_s, lens_s, cons, u0);
+    cursor_seek(p, prefix_s, lens_s, cons, first_unit);
     prod = cons;
 
     // One normalised output row chunk (4 columns) of (batch b, kv head hk, tile row r).
@@ -273,25 +312,35 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             const int* e = pend + 5 * i;
             const int pair = e[0], c_first = e[1], c_last = e[2];
             const int r = (idx % per_pair) / (D / 4), c4 = idx % (D / 4);
-            // Running merge in CTA order (deterministic); the loads do not depend on it.
+            // Running merge in CTA order (deterministic). The partials of four holders are
+            // requested together before any is used: one trip to L2 per four holders, not one
+            // per holder.
             float mm = -INFINITY, ll = 0.f;
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-            for (int c = c_first; c <= c_last; ++c) {
-                const int slot = c + pair;
-                const float ms = __ldcg(&p.part_m[slot * 16 + r]);
-                const float ls = __ldcg(&p.part_l[slot * 16 + r]);
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                    p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
-                const float m_new = fmaxf(mm, ms);
-                const float base = (m_new == -INFINITY) ? 0.f : m_new;
-                const float fa = fast_exp2(mm - base), fb = fast_exp2(ms - base);
-                ll = ll * fa + ls * fb;
-                sum.x = sum.x * fa + v.x * fb;
-                sum.y = sum.y * fa + v.y * fb;
-                sum.z = sum.z * fa + v.z * fb;
-                sum.w = sum.w * fa + v.w * fb;
-                mm = m_new;
+            for (int c0 = c_first; c0 <= c_last; c0 += 4) {
+                float ms[4], ls[4];
+                float4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int slot = min(c0 + j, c_last) + pair;   // past the last holder: a repeat, not used
+                    ms[j] = __ldcg(&p.part_m[slot * 16 + r]);
+                    ls[j] = __ldcg(&p.part_l[slot * 16 + r]);
+                    v[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (c0 + j <= c_last) {
+                        const float m_new = fmaxf(mm, ms[j]);
+                        const float base = (m_new == -INFINITY) ? 0.f : m_new;
+                        const float fa = fast_exp2(mm - base), fb = fast_exp2(ms[j] - base);
+                        ll = ll * fa + ls[j] * fb;
+                        sum.x = sum.x * fa + v[j].x * fb;
+                        sum.y = sum.y * fa + v[j].y * fb;
+                        sum.z = sum.z * fa + v[j].z * fb;
+                        sum.w = sum.w * fa + v[j].w * fb;
+                        mm = m_new;
+                    }
+                }
             }
             write_row(e[3], e[4], r, c4, sum, mm, ll);
         }
@@ -499,6 +548,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
 
         const bool last_of_pair = cons.tile + 1 == cons.ntiles;
         if (last_of_pair || u + 1 == u1) {
+            const long long fin_t0 = p.trace ? clock64() : 0;
             // Merge the four warps' states in a fixed order (deterministic).
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -529,45 +579,50 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                 }
                 f[r] = fast_exp2(m_run[r] - base);
             }
+            // Every warp leaves its rescaled 16 x D fp32 block in its own quarter of the stage
+            // it has just consumed (rows 0-7 where its 16 key rows were, rows 8-15 where its
+            // value rows were: no other warp reads or refills those bytes), all four at once;
+            // after one barrier the CTA adds the four blocks, warp 0's first (a fixed order:
+            // deterministic), and writes each sum straight to where it goes.
+            constexpr int kQuarter = 16 * D * 2;   // bytes of a warp's rows in a K or V tile
+            unsigned char* slab = ring + st * kStage + warp * kQuarter;
 #pragma unroll
-            for (int turn = 0; turn < 4; ++turn) {
-                if (warp == turn) {
-#pragma unroll
-                    for (int n = 0; n < D / 8; ++n) {
-                        float2* lo = reinterpret_cast<float2*>(&acc[g * D + n * 8 + t * 2]);
-                        float2* hi = reinterpret_cast<float2*>(&acc[(g + 8) * D + n * 8 + t * 2]);
-                        float2 vlo = make_float2(o[n][0] * f[0], o[n][1] * f[0]);
-                        float2 vhi = make_float2(o[n][2] * f[1], o[n][3] * f[1]);
-                        if (turn) {
-                            const float2 a0 = *lo, a1 = *hi;
-                            vlo.x += a0.x; vlo.y += a0.y;
-                            vhi.x += a1.x; vhi.y += a1.y;
-                        }
-                        *lo = vlo;
-                        *hi = vhi;
-                    }
-                }
-                __syncthreads();
+            for (int n = 0; n < D / 8; ++n) {
+                const int col = (n * 8 + t * 2) ^ (g << 3);   // rows spread over the banks
+                *reinterpret_cast<float2*>(slab + (g * D + col) * 4) = make_float2(o[n][0] * f[0], o[n][1] * f[0]);
+                *reinterpret_cast<float2*>(slab + kTile * D * 2 + (g * D + col) * 4) = make_float2(o[n][2] * f[1], o[n][3] * f[1]);
             }
+            __syncthreads();
+            auto merged = [&](int r, int c4) {
+                const unsigned char* base = ring + st * kStage + (r >= 8 ? kTile * D * 2 : 0) + (((r & 7) * D + ((c4 * 4) ^ ((r & 7) << 3))) * 4);
+                float4 sum = *reinterpret_cast<const float4*>(base);
+#pragma unroll
+                for (int w = 1; w < 4; ++w) {
+                    const float4 x = *reinterpret_cast<const float4*>(base + w * kQuarter);
+                    sum.x += x.x;
+                    sum.y += x.y;
+                    sum.z += x.z;
+                    sum.w += x.w;
+                }
+                return sum;
+            };
 
             // Which CTAs hold a piece of this pair?
             const int pair = cons.b * p.kv_heads + cons.hk;
-            const int t0 = p.kv_heads * prefix_s[cons.b] + cons.hk * cons.ntiles;
+            const int t0 = p.kv_heads * prefix_s[cons.b] + cons.hk * (cons.ntiles + kPairCost);   // the pair's first unit
             const int c_first = t0 / upc, c_last = (t0 + cons.ntiles - 1) / upc;
             if (c_first == c_last) {
                 // The whole pair lies in this CTA: normalise and write it now.
                 for (int idx = threadIdx.x; idx < rows * (D / 4); idx += kThreads) {
                     const int r = idx / (D / 4), c4 = idx % (D / 4);
-                    const float4 sum = *reinterpret_cast<const float4*>(&acc[r * D + c4 * 4]);
-                    write_row(cons.b, cons.hk, r, c4, sum, fin_m[r], fin_l[r]);
+                    write_row(cons.b, cons.hk, r, c4, merged(r, c4), fin_m[r], fin_l[r]);
                 }
             } else {
                 // Store the partial; the ticket is drawn at the end of the CTA so that the
                 // stream is not held up by a device-wide fence in the middle.
                 const int slot = blockIdx.x + pair;
                 float4* dst = reinterpret_cast<float4*>(p.part_o + static_cast<int64_t>(slot) * 16 * D);
-                const float4* src = reinterpret_cast<const float4*>(acc);
-                for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = src[idx];
+                for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = merged(idx / (D / 4), idx % (D / 4));
                 if (threadIdx.x < 16) {
                     p.part_m[slot * 16 + threadIdx.x] = fin_m[threadIdx.x];
                     p.part_l[slot * 16 + threadIdx.x] = fin_l[threadIdx.x];
@@ -582,6 +637,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             }
             __syncthreads();
             fresh = true;
+            if (p.trace && threadIdx.x == 0 && blockIdx.x < 1024) p.trace[(64 + blockIdx.x) * 8 + 7] += clock64() - fin_t0;
         }
         cursor_next(p, prefix_s, lens_s, cons);
     }
@@ -602,7 +658,7 @@ int stream_ctas_for_device() {
 
 template <int D, int NS, bool kAppend>
 int launch(const DecodeParams& p, int ctas, cudaStream_t stream) {
-    constexpr int smem = NS * 2 * kTile * D * 2 + 16 * D * 4 + (2 * 64 + 32) * 4 + (2 * kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
+    constexpr int smem = NS * 2 * kTile * D * 2 + (2 * 64 + 32) * 4 + (2 * kMaxBatch + 1 + 8 + 6 * kMaxPending + 1) * 4;
     if (int rc = ensure_smem(decode_kernel<D, NS, kAppend>, smem, "cudaFuncSetAttribute(decode)")) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
