@@ -40,6 +40,13 @@ using namespace tc5;
 namespace {
 
 constexpr int kThreads = 320;
+// Exponentials per 8 pairs that take the FMA-pipe polynomial instead of MUFU, spread evenly.
+#ifndef KTT_BWD_POLY_PAIRS
+#define KTT_BWD_POLY_PAIRS 3
+#endif
+__host__ __device__ constexpr bool poly_pair(int pair) {
+    return ((pair % 8) * KTT_BWD_POLY_PAIRS) % 8 < KTT_BWD_POLY_PAIRS && KTT_BWD_POLY_PAIRS > 0;
+}
 constexpr int kTmemCols = 512;
 
 struct BwdParams {
@@ -328,33 +335,56 @@ __device__ __forceinline__ void dkv_body(
             }
         };
 
-        // Row terms of one item: group 0 threads fetch lse (as base-2, +inf for rows that do
-        // not exist or saw no key), group 1 threads fetch delta.
-        auto fetch = [&](int it) -> float {
+        // Row terms of one item: group 0 threads fetch lse, group 1 threads fetch delta. The
+        // load is issued one item ahead and nothing looks at the loaded value until the next
+        // item starts (a select or a multiply right behind the load would make the warp sit
+        // out a trip to L2 in every item: measured, ~900 clk of a 3,300-clk item).
+        auto fetch = [&](int it, bool& exists) -> float {
             const int h = hk * full_group + g0 + it / per_head;
             const int qi = (qstart + it % per_head) * kBN + row;
-            if (qi >= si.lq) return g == 0 ? INFINITY : 0.f;
-            if (g == 0) {
-                const float l = p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qi) * p.ls[2]] * kLog2e;
-                return l == -INFINITY ? INFINITY : l;
-            }
-            return p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + qi];
+            exists = qi < si.lq;
+            const int qc = exists ? qi : 0;   // a row of this sequence, read and discarded
+            if (g == 0) return p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qc) * p.ls[2]];
+            return p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + qc];
         };
-        float pre = nitems > 0 ? fetch(0) : 0.f;
+        // What goes into the vectors: lse as base-2 (+inf for rows that do not exist or saw no
+        // key: P exactly 0), delta (0 for rows that do not exist).
+        auto row_term = [&](float raw, bool exists) -> float {
+            if (g == 0) {
+                const float l = raw * kLog2e;
+                return (!exists || l == -INFINITY) ? INFINITY : l;
+            }
+            return exists ? raw : 0.f;
+        };
+        bool pre_exists = false;
+        float pre = nitems > 0 ? fetch(0, pre_exists) : 0.f;
+        // While a trace buffer is set the CTA's first thread adds up where its item loop
+        // waits (row 64 + 512 + CTA: meeting, wait for S, phase 1, wait for dP, phase 2).
+        const bool timing = tp.trace && (threadIdx.x & 31) == 0 && blockIdx.x < 56;   // one row of 8 slots per warp
+        long long acc_t[5] = {0, 0, 0, 0, 0}, tick = timing ? clock64() : 0;
+        auto lap = [&](int slot) {
+            if (timing) {
+                const long long now = clock64();
+                acc_t[slot] += now - tick;
+                tick = now;
+            }
+        };
 
         for (int it = 0; it < nitems; ++it) {
             float* lse2 = vec + (it & 1) * 256;
             float* delta = lse2 + 128;
-            (g == 0 ? lse2 : delta)[row] = pre;
+            (g == 0 ? lse2 : delta)[row] = row_term(pre, pre_exists);
             ok = meet(630);
             if (!ok) break;
             mask_term(it);
-            if (it + 1 < nitems) pre = fetch(it + 1);
+            if (it + 1 < nitems) pre = fetch(it + 1, pre_exists);
+            lap(0);
             const int q0 = (qstart + it % per_head) * kBN;
             const uint32_t tmem_s = tmem_s_of(it);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + it % kSBufs), (it / kSBufs) & 1, abort_flag, 600 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            lap(1);
             if (it == 0) mark(tp, 5);   // first scores
             // Column c of this half is query q0 + g * 64 + c; key kk sees it when
             // kk <= q + shift, i.e. c >= first_col.
@@ -363,6 +393,7 @@ __device__ __forceinline__ void dkv_body(
             // scores as the operand of dV. Two values per instruction on the packed fp32 pipe;
             // a tile every key of which sees every query of this half skips the tests.
             const bool whole = key_ok && first_col <= 0;
+            const bool whole_w = __all_sync(0xffffffffu, whole);
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
             float2 pv[32];
 #pragma unroll
@@ -371,20 +402,35 @@ __device__ __forceinline__ void dkv_body(
                 tmem_ld32(tmem_s + lane_addr + g * 64 + c * 32, sc);
                 tmem_wait_ld();
                 const float4* l4 = reinterpret_cast<const float4*>(lse2 + g * 64 + c * 32);
+                if (whole_w) {
+                    // Every thread of the warp sees all its columns: no tests, and some pairs
+                    // of every 8 as a cubic on the FMA pipe (with two score warps per
+                    // scheduler the loop is bound by MUFU).
 #pragma unroll
-                for (int e4 = 0; e4 < 8; ++e4) {
-                    const float4 lv = l4[e4];
-                    float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
-                    float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
-                    if (!whole) {
-                        const int col = c * 32 + e4 * 4;
-                        x0.x = (key_ok && col >= first_col) ? x0.x : -INFINITY;
-                        x0.y = (key_ok && col + 1 >= first_col) ? x0.y : -INFINITY;
-                        x1.x = (key_ok && col + 2 >= first_col) ? x1.x : -INFINITY;
-                        x1.y = (key_ok && col + 3 >= first_col) ? x1.y : -INFINITY;
+                    for (int e4 = 0; e4 < 8; ++e4) {
+                        const float4 lv = l4[e4];
+                        const float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
+                        const float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
+                        pv[c * 16 + e4 * 2] = poly_pair(e4 * 2) ? exp2_poly2_zero(x0) : make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+                        pv[c * 16 + e4 * 2 + 1] = poly_pair(e4 * 2 + 1) ? exp2_poly2_zero(x1) : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
                     }
-                    pv[c * 16 + e4 * 2] = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-                    pv[c * 16 + e4 * 2 + 1] = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+                } else {
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; ++e4) {
+                        const float4 lv = l4[e4];
+                        float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
+                        float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
+                        if (!whole) {
+                            const int col = c * 32 + e4 * 4;
+                            x0.x = (key_ok && col >= first_col) ? x0.x : -INFINITY;
+                            x0.y = (key_ok && col + 1 >= first_col) ? x0.y : -INFINITY;
+                            x1.x = (key_ok && col + 2 >= first_col) ? x1.x : -INFINITY;
+                            x1.y = (key_ok && col + 3 >= first_col) ? x1.y : -INFINITY;
+                        }
+                        // Hidden columns take MUFU, whose 2^-inf is exactly 0.
+                        pv[c * 16 + e4 * 2] = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+                        pv[c * 16 + e4 * 2 + 1] = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+                    }
                 }
             }
 #pragma unroll
@@ -396,9 +442,11 @@ __device__ __forceinline__ void dkv_body(
                 tmem_st16(tmem_s + lane_addr + g * 64 + c * 16, wp);
             }
             // Phase 2: dS^T = P^T o (dP^T - delta) over dP^T.
+            lap(2);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDPReady), it & 1, abort_flag, 620 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            lap(3);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 float dp[32];
@@ -419,6 +467,12 @@ __device__ __forceinline__ void dkv_body(
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(bar(P::bPFull + g));
+            lap(4);
+        }
+        if (timing) {
+            long long* out = tp.trace + (64 + 512 + blockIdx.x * 8 + warp) * 8;
+            for (int i = 0; i < 5; ++i) out[i] = acc_t[i];
+            out[5] = nitems;
         }
 
         // Epilogue: group 0 writes dV, group 1 writes dK (scaled); rows past the end of the
@@ -757,6 +811,7 @@ __device__ __forceinline__ void dq_body(
             // values per instruction on the packed fp32 pipe; wholly visible halves skip the
             // tests.
             const bool whole = limit >= 64;
+            const bool whole_w = __all_sync(0xffffffffu, whole);
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(-lse2, -lse2);
             const float2 nd2 = make_float2(-delta, -delta);
             float2 pv[32];
@@ -765,18 +820,30 @@ __device__ __forceinline__ void dq_body(
                 float sc[32];
                 tmem_ld32(tmem_s_of(j) + lane_addr + g * 64 + c * 32, sc);
                 tmem_wait_ld();
+                if (whole_w) {
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    float2 x = __ffma2_rn(make_float2(sc[2 * e], sc[2 * e + 1]), sc2, nl2);
-                    if constexpr (kMask) {
-                        const float2 t = reinterpret_cast<const float2*>(vec + (j & 1) * 128 + g * 64 + c * 32)[e];
-                        x = __fadd2_rn(x, t);
+                    for (int e = 0; e < 16; ++e) {
+                        float2 x = __ffma2_rn(make_float2(sc[2 * e], sc[2 * e + 1]), sc2, nl2);
+                        if constexpr (kMask) {
+                            const float2 t = reinterpret_cast<const float2*>(vec + (j & 1) * 128 + g * 64 + c * 32)[e];
+                            x = __fadd2_rn(x, t);
+                        }
+                        pv[c * 16 + e] = poly_pair(e) ? exp2_poly2_zero(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
                     }
-                    if (!whole) {
-                        x.x = c * 32 + 2 * e < limit ? x.x : -INFINITY;
-                        x.y = c * 32 + 2 * e + 1 < limit ? x.y : -INFINITY;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        float2 x = __ffma2_rn(make_float2(sc[2 * e], sc[2 * e + 1]), sc2, nl2);
+                        if constexpr (kMask) {
+                            const float2 t = reinterpret_cast<const float2*>(vec + (j & 1) * 128 + g * 64 + c * 32)[e];
+                            x = __fadd2_rn(x, t);
+                        }
+                        if (!whole) {
+                            x.x = c * 32 + 2 * e < limit ? x.x : -INFINITY;
+                            x.y = c * 32 + 2 * e + 1 < limit ? x.y : -INFINITY;
+                        }
+                        pv[c * 16 + e] = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                     }
-                    pv[c * 16 + e] = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                 }
             }
             // Phase 2: dS = P o (dP - delta) over dP.

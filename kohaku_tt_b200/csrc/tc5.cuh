@@ -218,6 +218,15 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     return r;
 }
 
+// exp2_poly2 with exact zeros: anything below 2^-120 (a row whose lse is +inf, i.e. one that
+// does not exist or saw no key) gives 0, as MUFU's 2^-inf does.
+__device__ __forceinline__ float2 exp2_poly2_zero(float2 x) {
+    float2 r = exp2_poly2(x);
+    r.x = x.x < -120.f ? 0.f : r.x;
+    r.y = x.y < -120.f ? 0.f : r.y;
+    return r;
+}
+
 // Shared-memory matrix descriptor for a 128-byte swizzled tile (sm_100 format: version 1
 // at bit 46, layout type 2 = SWIZZLE_128B at bit 61). Offsets in bytes.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
