@@ -194,8 +194,10 @@ KTT_B200_API int ktt_b200_probe_read(const void* data, int64_t bytes, int32_t* s
  * The decode kernel writes, per CTA, rows 64.. with six nanosecond stamps: start,
  * dependency wait over, lengths scanned, first tile landed, stream done, end. The tcgen05
  * backward writes, per CTA, rows 64..: start, end, SM, CTA index, set-up done, first scores,
- * last MMA done, results stored. kohaku_tt_b200/trace.py reads all three. NULL turns it
- * off (default). */
+ * last MMA done, results stored; and for the first 56 CTAs, per score warp, rows
+ * 64 + 512 + 8 CTA + warp: the clocks its item loop spent meeting, waiting for S, in phase 1,
+ * waiting for dP, in phase 2, and the item count. kohaku_tt_b200/trace.py reads all three.
+ * NULL turns it off (default). */
 KTT_B200_API int ktt_b200_set_trace(void* device_buffer);
 
 /* ktt_flash::supports / refusal (ktt_flash/program.cpp:847-910): 1 when the forward

@@ -325,10 +325,11 @@ __device__ __forceinline__ void dkv_body(
         };
         // A mask of one row per (batch, head): this thread's key has one term per query head.
         float mterm = 0.f;
-        auto mask_term = [&](int it) {
+        int cur_head = 0, cur_qb = 0;   // the item at hand: head inside this CTA's part, query block from qstart
+        auto mask_term = [&](int) {
             if constexpr (kMask) {
-                if (it % per_head == 0) {
-                    const int h = hk * full_group + g0 + it / per_head;
+                if (cur_qb == 0) {
+                    const int h = hk * full_group + g0 + cur_head;
                     const int key = max(min(kk, si.klen - 1), 0);
                     mterm = mask_value(p, b, h, 0, static_cast<int64_t>(si.k_off) + key) * kLog2e;
                 }
@@ -339,13 +340,24 @@ __device__ __forceinline__ void dkv_body(
         // load is issued one item ahead and nothing looks at the loaded value until the next
         // item starts (a select or a multiply right behind the load would make the warp sit
         // out a trip to L2 in every item: measured, ~900 clk of a 3,300-clk item).
-        auto fetch = [&](int it, bool& exists) -> float {
-            const int h = hk * full_group + g0 + it / per_head;
-            const int qi = (qstart + it % per_head) * kBN + row;
+        // (Head and query block of the item to fetch are kept as running counters and the row's
+        // address as a running pointer: the divisions and 64-bit products they replace were a
+        // fifth of an item, one dependent chain per warp with nothing to overlap it.)
+        int nxt_head = 0, nxt_qb = 0;   // item to fetch next: head inside this CTA's part, query block from qstart
+        const float* src_row = g == 0
+            ? p.lse + b * p.ls[0] + (hk * full_group + g0) * p.ls[1] + static_cast<int64_t>(si.q_off) * p.ls[2]
+            : p.delta + b * p.delta_bs + (hk * full_group + g0) * p.delta_hs + si.q_off;
+        const int64_t src_head = g == 0 ? p.ls[1] : p.delta_hs, src_step = g == 0 ? p.ls[2] : 1;
+        auto fetch = [&](bool& exists) -> float {
+            const int qi = (qstart + nxt_qb) * kBN + row;
             exists = qi < si.lq;
             const int qc = exists ? qi : 0;   // a row of this sequence, read and discarded
-            if (g == 0) return p.lse[b * p.ls[0] + h * p.ls[1] + (si.q_off + qc) * p.ls[2]];
-            return p.delta[b * p.delta_bs + h * p.delta_hs + si.q_off + qc];
+            const float raw = src_row[nxt_head * src_head + qc * src_step];
+            if (++nxt_qb == per_head) {
+                nxt_qb = 0;
+                ++nxt_head;
+            }
+            return raw;
         };
         // What goes into the vectors: lse as base-2 (+inf for rows that do not exist or saw no
         // key: P exactly 0), delta (0 for rows that do not exist).
@@ -357,7 +369,7 @@ __device__ __forceinline__ void dkv_body(
             return exists ? raw : 0.f;
         };
         bool pre_exists = false;
-        float pre = nitems > 0 ? fetch(0, pre_exists) : 0.f;
+        float pre = nitems > 0 ? fetch(pre_exists) : 0.f;
         // While a trace buffer is set the CTA's first thread adds up where its item loop
         // waits (row 64 + 512 + CTA: meeting, wait for S, phase 1, wait for dP, phase 2).
         const bool timing = tp.trace && (threadIdx.x & 31) == 0 && blockIdx.x < 56;   // one row of 8 slots per warp
@@ -377,9 +389,9 @@ __device__ __forceinline__ void dkv_body(
             ok = meet(630);
             if (!ok) break;
             mask_term(it);
-            if (it + 1 < nitems) pre = fetch(it + 1, pre_exists);
+            if (it + 1 < nitems) pre = fetch(pre_exists);
             lap(0);
-            const int q0 = (qstart + it % per_head) * kBN;
+            const int q0 = (qstart + cur_qb) * kBN;
             const uint32_t tmem_s = tmem_s_of(it);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + it % kSBufs), (it / kSBufs) & 1, abort_flag, 600 + g, tp.status));
             if (!ok) break;
@@ -467,6 +479,10 @@ __device__ __forceinline__ void dkv_body(
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(bar(P::bPFull + g));
+            if (++cur_qb == per_head) {
+                cur_qb = 0;
+                ++cur_head;
+            }
             lap(4);
         }
         if (timing) {

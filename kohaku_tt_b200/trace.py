@@ -42,8 +42,8 @@ def _traced(dev, fn, warm=3):
     return buf.cpu().view(ROWS, 8)
 
 
-def _cta_rows(table):
-    rows = table[64:]
+def _cta_rows(table, limit=1024):
+    rows = table[64:64 + limit]
     return rows[rows[:, 0] > 0]
 
 
@@ -93,7 +93,7 @@ def backward(dev):
     v = _randn((1, c["kv_heads"], c["seq"], c["dim"]), gen, dev)
     out, lse = ops.sdpa_forward(q, k, v, causal=True)
     table = _traced(dev, lambda: ops.sdpa_backward(do, q, k, v, out, lse, causal=True))
-    rows = _cta_rows(table)
+    rows = _cta_rows(table, 512)   # rows past 512 hold the per-warp item-loop clocks of the first CTAs
     t0, per_sm = _by_sm(rows)
     print(f"CTAs {len(rows)} on {len(per_sm)} SMs, first start to last end {(int(rows[:, 1].max()) - t0) / 1e3:.1f} us")
     group = c["heads"] // c["kv_heads"]
@@ -120,6 +120,19 @@ def backward(dev):
             print(f"  {kind} median CTA ns: set-up {med[0]:.0f} | to first scores {med[1]:.0f} | item loop {med[2]:.0f} | "
                   f"results stored {med[3]:.0f} | ticket, sum of the parts, teardown {med[4]:.0f}")
     del group
+    # Where the item loop of a dK/dV CTA spends its clocks, per score warp (first 56 CTAs).
+    names = ["meeting + next fetch", "wait for S", "phase 1 (P)", "wait for dP", "phase 2 (dS)"]
+    per_warp = []
+    for w in range(8):
+        rws = torch.stack([table[64 + 512 + c * 8 + w] for c in range(56)])
+        rws = rws[rws[:, 5] >= 8]
+        if len(rws):
+            n = rws[:, 5].double()
+            per_warp.append([float((rws[:, i].double() / n).median()) for i in range(5)])
+    if per_warp:
+        med = [statistics.median(x[i] for x in per_warp) for i in range(5)]
+        print("  dK/dV item loop, clk per item (median over score warps): "
+              + " | ".join(f"{nm} {v:.0f}" for nm, v in zip(names, med)) + f" | sum {sum(med):.0f}")
 
 
 def decode(dev):
