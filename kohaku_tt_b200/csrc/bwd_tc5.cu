@@ -42,7 +42,7 @@ namespace {
 constexpr int kThreads = 320;
 // Exponentials per 8 pairs that take the FMA-pipe polynomial instead of MUFU, spread evenly.
 #ifndef KTT_BWD_POLY_PAIRS
-#define KTT_BWD_POLY_PAIRS 3
+#define KTT_BWD_POLY_PAIRS 2
 #endif
 __host__ __device__ constexpr bool poly_pair(int pair) {
     return ((pair % 8) * KTT_BWD_POLY_PAIRS) % 8 < KTT_BWD_POLY_PAIRS && KTT_BWD_POLY_PAIRS > 0;
@@ -359,12 +359,13 @@ __device__ __forceinline__ void dkv_body(
             }
             return raw;
         };
-        // What goes into the vectors: lse as base-2 (+inf for rows that do not exist or saw no
-        // key: P exactly 0), delta (0 for rows that do not exist).
+        // What goes into the vectors: minus lse as base-2, ready to be added to the scaled
+        // score (-inf for rows that do not exist or saw no key: P exactly 0), and delta (0 for
+        // rows that do not exist).
         auto row_term = [&](float raw, bool exists) -> float {
             if (g == 0) {
                 const float l = raw * kLog2e;
-                return (!exists || l == -INFINITY) ? INFINITY : l;
+                return (!exists || l == -INFINITY) ? -INFINITY : -l;
             }
             return exists ? raw : 0.f;
         };
@@ -421,8 +422,8 @@ __device__ __forceinline__ void dkv_body(
 #pragma unroll
                     for (int e4 = 0; e4 < 8; ++e4) {
                         const float4 lv = l4[e4];
-                        const float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
-                        const float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
+                        const float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, (kMask ? make_float2(mterm + lv.x, mterm + lv.y) : make_float2(lv.x, lv.y)));
+                        const float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, (kMask ? make_float2(mterm + lv.z, mterm + lv.w) : make_float2(lv.z, lv.w)));
                         pv[c * 16 + e4 * 2] = poly_pair(e4 * 2) ? exp2_poly2_zero(x0) : make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
                         pv[c * 16 + e4 * 2 + 1] = poly_pair(e4 * 2 + 1) ? exp2_poly2_zero(x1) : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
                     }
@@ -430,8 +431,8 @@ __device__ __forceinline__ void dkv_body(
 #pragma unroll
                     for (int e4 = 0; e4 < 8; ++e4) {
                         const float4 lv = l4[e4];
-                        float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, make_float2(mterm - lv.x, mterm - lv.y));
-                        float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, make_float2(mterm - lv.z, mterm - lv.w));
+                        float2 x0 = __ffma2_rn(make_float2(sc[e4 * 4], sc[e4 * 4 + 1]), sc2, (kMask ? make_float2(mterm + lv.x, mterm + lv.y) : make_float2(lv.x, lv.y)));
+                        float2 x1 = __ffma2_rn(make_float2(sc[e4 * 4 + 2], sc[e4 * 4 + 3]), sc2, (kMask ? make_float2(mterm + lv.z, mterm + lv.w) : make_float2(lv.z, lv.w)));
                         if (!whole) {
                             const int col = c * 32 + e4 * 4;
                             x0.x = (key_ok && col >= first_col) ? x0.x : -INFINITY;
