@@ -42,3 +42,29 @@ def test_a_wait_that_runs_out_is_reported_counted_and_survivable(cuda):
         _lib.device_status()
     _lib.device_status()
     assert ktt.counters()["device_wait_timeouts"] == before + 2
+
+
+def test_profiling_stamp_readers_run(cuda, capsys):
+    # kohaku_tt_b200.trace: one traced launch of each kernel family at the benchmark shapes.
+    from kohaku_tt_b200 import trace
+
+    trace.forward(cuda)
+    trace.backward(cuda)
+    trace.decode(cuda)
+    text = capsys.readouterr().out
+    assert "key block" in text and "dK/dV CTAs" in text and "stream end" in text
+    _lib.device_status()   # nothing gave up waiting while traced
+
+
+def test_plain_read_probe_checks_its_arguments(cuda):
+    import ctypes
+
+    handle = _lib.lib()
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device=cuda)
+    sink = torch.zeros(1, dtype=torch.int32, device=cuda)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    assert handle.ktt_b200_probe_read(ctypes.c_void_p(buf.data_ptr()), 1 << 20, ctypes.c_void_p(sink.data_ptr()), stream) == 0
+    torch.cuda.synchronize()
+    assert int(sink.item()) in (0, 1)
+    for ptr, nbytes in ((buf.data_ptr() + 8, 1 << 10), (buf.data_ptr(), (1 << 10) + 4), (0, 1 << 10)):
+        assert handle.ktt_b200_probe_read(ctypes.c_void_p(ptr), nbytes, ctypes.c_void_p(sink.data_ptr()), stream) == _lib.ERR_BAD_ARGUMENT
