@@ -806,6 +806,18 @@ __device__ __forceinline__ void dq_body(
         int row_limit = si.klen;
         if (p.causal) row_limit = min(row_limit, qi + si.shift + 1);
         float* vec = reinterpret_cast<float*>(smem + P::kVec);   // [block parity][128]: a block's mask terms
+        // Item-loop clocks per score warp while a trace buffer is set, as in the dK/dV body
+        // (rows 64 + 512 + 448 + 8 (CTA - first dQ CTA) + warp; first 8 dQ CTAs).
+        const int dq_index = static_cast<int>(blockIdx.x) - static_cast<int>(gridDim.x - static_cast<unsigned>(p.heads) * ny * p.batch);
+        const bool timing = tp.trace && lane == 0 && dq_index >= 0 && dq_index < 8;
+        long long acc_t[5] = {0, 0, 0, 0, 0}, tick = timing ? clock64() : 0;
+        auto lap = [&](int slot) {
+            if (timing) {
+                const long long now = clock64();
+                acc_t[slot] += now - tick;
+                tick = now;
+            }
+        };
 
         for (int j = 0; j < nblocks; ++j) {
             if constexpr (kMask) {
@@ -819,9 +831,11 @@ __device__ __forceinline__ void dq_body(
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bMeet), j & 1, abort_flag, 930 + g, tp.status));
                 if (!ok) break;
             }
+            lap(0);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bSReady + (j & 1)), (j >> 1) & 1, abort_flag, 900 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            lap(1);
             if (j == 0) mark(tp, 5);
             const int limit = row_limit - j * kBN - g * 64;  // this half's columns [0, limit) are visible
             // Phase 1: P in registers while dP of this block is still being computed. Two
@@ -864,9 +878,11 @@ __device__ __forceinline__ void dq_body(
                 }
             }
             // Phase 2: dS = P o (dP - delta) over dP.
+            lap(2);
             ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDPReady), j & 1, abort_flag, 920 + g, tp.status));
             if (!ok) break;
             tc_fence_after();
+            lap(3);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 float dp[32];
@@ -887,6 +903,12 @@ __device__ __forceinline__ void dq_body(
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive_warp(bar(P::bPFull + g));
+            lap(4);
+        }
+        if (timing) {
+            long long* out = tp.trace + (64 + 512 + 448 + dq_index * 8 + warp) * 8;
+            for (int i = 0; i < 5; ++i) out[i] = acc_t[i];
+            out[5] = nblocks;
         }
 
         if (ok && nblocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(P::bDone), 0, abort_flag, 910, tp.status));

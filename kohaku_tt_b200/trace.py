@@ -133,6 +133,19 @@ def backward(dev):
         med = [statistics.median(x[i] for x in per_warp) for i in range(5)]
         print("  dK/dV item loop, clk per item (median over score warps): "
               + " | ".join(f"{nm} {v:.0f}" for nm, v in zip(names, med)) + f" | sum {sum(med):.0f}")
+    # The same for the first dQ CTAs (the longest: all key blocks).
+    names = ["mask row", "wait for S", "phase 1 (P)", "wait for dP", "phase 2 (dS)"]
+    per_warp = []
+    for w in range(8):
+        rws = torch.stack([table[64 + 512 + 448 + c * 8 + w] for c in range(8)])
+        rws = rws[rws[:, 5] >= 8]
+        if len(rws):
+            n = rws[:, 5].double()
+            per_warp.append([float((rws[:, i].double() / n).median()) for i in range(5)])
+    if per_warp:
+        med = [statistics.median(x[i] for x in per_warp) for i in range(5)]
+        print("  dQ item loop, clk per item (median over score warps): "
+              + " | ".join(f"{nm} {v:.0f}" for nm, v in zip(names, med)) + f" | sum {sum(med):.0f}")
 
 
 def decode(dev):
