@@ -400,18 +400,54 @@ def run_ours(args):
         for t, off, n in zip(headline_inputs(2000 * rank + i), (0, counts[0], counts[0] + counts[1]), counts):
             stage[off:off + n] = t.reshape(-1)
         host.append(stage)
-    lanes = 3
-    streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
+    lanes = max(0, args.e2e_streams)
+    ring = 4
     out_host = [torch.empty((c["batch"], c["heads"], c["seq"], c["head_dim"]), dtype=torch.bfloat16).pin_memory()
-                for _ in range(lanes)]
+                for _ in range(max(lanes, ring))]
+    views = lambda flat: tuple(flat[off:off + n].view(sh) for off, n, sh in
+                               zip((0, counts[0], counts[0] + counts[1]), counts, shapes))
+    if lanes == 0:
+        # Three streams with one job each, the classic feed of a GPU: inputs come in on one,
+        # the attention call runs on the second, results leave on the third; events hand a
+        # step from one to the next and guard the ring of device staging buffers. Copies of
+        # one direction never run beside one another (they would only share the link).
+        s_in, s_run, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        streams = [s_in, s_run, s_out]
+        dev_in = [torch.empty((sum(counts),), dtype=torch.bfloat16, device=dev) for _ in range(ring)]
+        arrived = [torch.cuda.Event() for _ in range(ring)]
+        computed = [torch.cuda.Event() for _ in range(ring)]
+        left = [torch.cuda.Event() for _ in range(ring)]
+        results = [None] * ring   # a step's output stays referenced until its slot comes round again
 
-    def e2e_step(i):
-        with torch.cuda.stream(streams[i % lanes]):
-            flat = host[i % 4].to(dev, non_blocking=True)
-            q, k, v = (flat[off:off + n].view(sh) for off, n, sh in
-                       zip((0, counts[0], counts[0] + counts[1]), counts, shapes))
-            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-            out_host[i % lanes].copy_(o, non_blocking=True)
+        def e2e_step(i):
+            r = i % ring
+            with torch.cuda.stream(s_in):
+                if results[r] is not None:
+                    s_in.wait_event(computed[r])   # the kernel that read this buffer last is done
+                dev_in[r].copy_(host[i % 4], non_blocking=True)
+                arrived[r].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(arrived[r])
+                if results[r] is not None:
+                    # The slot's previous output goes back to this stream's allocator below:
+                    # nothing here may reuse it before its copy to the host has finished.
+                    s_run.wait_event(left[r])
+                q, k, v = views(dev_in[r])
+                results[r] = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                computed[r].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(computed[r])
+                out_host[r].copy_(results[r], non_blocking=True)
+                left[r].record(s_out)
+    else:
+        streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
+
+        def e2e_step(i):
+            with torch.cuda.stream(streams[i % lanes]):
+                flat = host[i % 4].to(dev, non_blocking=True)
+                q, k, v = views(flat)
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                out_host[i % lanes].copy_(o, non_blocking=True)
 
     def e2e_join():
         main = torch.cuda.current_stream()
@@ -441,6 +477,15 @@ def run_ours(args):
 
     # What bounds the end-to-end step: the copies alone, on the same three streams.
     def copies_only(i):
+        if lanes == 0:
+            r = i % ring
+            with torch.cuda.stream(s_in):
+                dev_in[r].copy_(host[i % 4], non_blocking=True)
+                arrived[r].record(s_in)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(arrived[r])
+                out_host[r].copy_(dev_in[r][:counts[0]].view(shapes[0]), non_blocking=True)
+            return
         with torch.cuda.stream(streams[i % lanes]):
             flat = host[i % 4].to(dev, non_blocking=True)
             out_host[i % lanes].copy_(flat[:counts[0]].view(shapes[0]), non_blocking=True)
@@ -468,7 +513,9 @@ def run_ours(args):
         "data": "synthetic", "config": workload_config(), "replays": replays,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
-                "api": "torch.nn.functional.scaled_dot_product_attention on CUDA tensors, steps issued round-robin on 3 streams",
+                "api": "torch.nn.functional.scaled_dot_product_attention on CUDA tensors; " + (
+                    "a copy-in stream, a compute stream and a copy-out stream chained by events" if lanes == 0
+                    else f"steps issued round-robin on {lanes} streams"),
                 "parts": e2e_parts},
         "gpu_launches": launches,
         "library_calls_counted": counted,
@@ -1024,6 +1071,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
     ap.add_argument("--headline-only", action="store_true", help="skip the extra legs and the CPU baseline")
+    ap.add_argument("--e2e-streams", type=int, default=0,
+                    help="0: copy-in / compute / copy-out streams chained by events; N > 0: whole steps issued round-robin on N streams")
     ap.add_argument("--leg", default=None, choices=sorted(LEGS), help="run one extra leg alone and print it")
     args = ap.parse_args()
     if args.leg:
