@@ -114,12 +114,13 @@ typedef struct ktt_b200_attn_args {
     int64_t dk_strides[3];
     int64_t dv_strides[3];
     /* Backward: workspace of ktt_b200_sdpa_backward_workspace() bytes, 256-byte aligned.
-     * Forward (optional), head dim 64: ktt_b200_sdpa_forward_workspace() bytes, 16-byte
-     * aligned, zero-filled once before the first use. With it the CTAs draw their query
-     * tiles, longest first, from a counter there instead of a fixed deal. The kernel leaves
-     * the counter zero; calls that share a buffer must not overlap on the GPU.
-     * Forward (optional), head dim 128: 4 to 255 bytes, zero-filled before EVERY call; the
-     * CTAs then draw their work items from a counter there. */
+     * Forward (optional): ktt_b200_sdpa_forward_workspace() bytes, 16-byte aligned,
+     * zero-filled once before the first use. With it the CTAs draw their query tiles from a
+     * counter there instead of a fixed deal, and the head-dim-128 kernel orders the tiles so
+     * that those in flight share the K / V of a few (batch, head) pairs (problems whose K / V
+     * exceed L2 otherwise re-read them several times). The kernel leaves the counter zero;
+     * calls that share a buffer must not overlap on the GPU. The head-dim-128 kernel also
+     * takes 4 to 255 bytes: one int32 the caller zero-fills before EVERY call. */
     void* workspace;
     int64_t workspace_bytes;
 } ktt_b200_attn_args;

@@ -299,9 +299,12 @@ extern "C" int ktt_b200_sdpa_forward(const ktt_b200_attn_args* a, void* stream) 
         if (a->kernel != KTT_B200_KERNEL_TC5_WIDE && forward_row_takes(p, &why_row)) {
             return launch_forward_row(p, a->workspace, a->workspace_bytes, st);
         }
-        // The one-CTA-per-SM kernel takes a 4..255-byte workspace as its work counter.
-        p.fwd_work_counter = (a->workspace && a->workspace_bytes >= 4 && a->workspace_bytes < 256)
-                                 ? static_cast<int32_t*>(a->workspace) : nullptr;
+        // The one-CTA-per-SM kernel draws its items from a counter in the workspace: with the
+        // full workspace (ktt_b200_sdpa_forward_workspace bytes) it puts the counter back to
+        // zero itself; a 4..255-byte workspace is one int32 the caller zeroes before every call.
+        const bool usable = a->workspace && (reinterpret_cast<uintptr_t>(a->workspace) & 3) == 0;
+        p.fwd_work_counter = (usable && a->workspace_bytes >= 4) ? static_cast<int32_t*>(a->workspace) : nullptr;
+        p.fwd_done_counter = (usable && a->workspace_bytes >= 256) ? static_cast<int32_t*>(a->workspace) + 1 : nullptr;
         return launch_forward_tc5(p, st);
     }
     note_call(1);
@@ -313,12 +316,12 @@ extern "C" int64_t ktt_b200_sdpa_forward_workspace(const ktt_b200_attn_args* a) 
         fail(KTT_B200_ERR_UNSUPPORTED, "%s", why);
         return 0;
     }
-    if (a->kernel == KTT_B200_KERNEL_MMA || a->kernel == KTT_B200_KERNEL_TC5_WIDE) return 0;
+    if (a->kernel == KTT_B200_KERNEL_MMA) return 0;
     AttnParams p;
     to_params(a, p);
     const char* why = nullptr;
-    if (!forward_row_takes(p, &why)) return 0;
-    return forward_row_workspace(p);
+    if (!forward_tc5_takes(p, &why)) return 0;   // the warp-MMA kernel has no use for one
+    return forward_row_workspace(p);             // the same 256 bytes for both tcgen05 kernels
 }
 
 extern "C" int ktt_b200_forward_streams_per_sm(void) { return forward_row_occupancy(); }

@@ -46,6 +46,7 @@ struct AttnParams {
     int gsplit;
     float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows][d]
     int32_t* fwd_work_counter;  // forward, optional: one zeroed int32 the persistent CTAs draw their items from
+    int32_t* fwd_done_counter;  // with it, optional: a second zeroed int32; the kernel then leaves both zero
     int32_t* dkv_counters;  // [batch][kv_heads][key blocks] tickets of the CTAs sharing a key block; zeroed by the delta kernel
 };
 
