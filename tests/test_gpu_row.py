@@ -125,6 +125,31 @@ def test_drawn_work_equals_the_fixed_deal_for_whole_tiles(cuda):
     assert torch.equal(drawn, fixed) and torch.equal(drawn_lse, fixed_lse)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_tiles_grouped_by_kv_head_when_kv_exceeds_l2(cuda, d):
+    # 268 MB of K / V: with a workspace the tiles of one (batch, head)
+    # are drawn together so that those in flight share K / V in L2. The order a tile is drawn
+    # in does not touch its arithmetic: the same bits as the fixed deal, and float64 rows.
+    b, h, s = (8 if d == 64 else 4), 16, 8192
+    g = torch.Generator(device=cuda).manual_seed(3 + d)
+    q, k, v = (torch.randn((b, h, s, d), generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+    out, lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    again, again_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    fixed, fixed_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash", dynamic=False)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    assert torch.equal(out, again) and torch.equal(lse, again_lse)
+    assert torch.equal(out, fixed) and torch.equal(lse, fixed_lse)
+    rows = torch.tensor([0, 127, 128, 4095, 8191])
+    for bi, hi in ((0, 0), (b - 1, h - 1)):
+        kk, vv = k[bi, hi].double().cpu(), v[bi, hi].double().cpu()
+        scores = (q[bi, hi].cpu()[rows].double() @ kk.T) / math.sqrt(d)
+        scores = scores.masked_fill(torch.arange(s)[None, :] > rows[:, None], float("-inf"))
+        ruler = torch.softmax(scores, dim=-1) @ vv
+        assert rel(out[bi, hi].cpu()[rows], ruler) <= FWD_BOUND
+        assert rms(lse[bi, hi].cpu()[rows], torch.logsumexp(scores, dim=-1)) <= LSE_RMS
+
+
 def test_the_workspace_is_left_zeroed(cuda):
     q, k, v = (t.to(cuda) for t in qkv(1, 14, 2, 2048, 2048, 64, 7))
     ops.drop_forward_workspaces()
