@@ -505,8 +505,14 @@ __device__ __forceinline__ void dkv_body(
                 : p.dk + b * p.dks[0] + hk * p.dks[1] + static_cast<int64_t>(si.k_off + kk) * p.dks[2];
             const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
             const int64_t planes = static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * p.gsplit;
-            float* pdst = p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit + part) * key_rows * D +
-                          static_cast<int64_t>(si.k_off + kk) * D;
+            // A part's partial block is stored column-major in float4 units ([D / 4][rows of the
+            // block that exist]): a warp's store then covers 512 contiguous bytes where a
+            // thread-per-row layout touched 32 sectors at a stride of a row (measured: 2.0 of
+            // the 2.5 us a dK/dV CTA spent storing its results).
+            const int block_rows = min(kBM, si.lk - k0);
+            float4* pdst = reinterpret_cast<float4*>(
+                p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit + part) * key_rows * D +
+                static_cast<int64_t>(si.k_off + k0) * D) + row;
             if (nitems > 0) tc_fence_after();
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -521,8 +527,7 @@ __device__ __forceinline__ void dkv_body(
                 if (real && p.gsplit > 1) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
-                        *reinterpret_cast<float4*>(pdst + c * 32 + e * 4) =
-                            make_float4(o[e * 4], o[e * 4 + 1], o[e * 4 + 2], o[e * 4 + 3]);
+                        pdst[(c * 8 + e) * block_rows] = make_float4(o[e * 4], o[e * 4 + 1], o[e * 4 + 2], o[e * 4 + 3]);
                     }
                 } else if (real) {
 #pragma unroll
@@ -555,51 +560,49 @@ __device__ __forceinline__ void dkv_body(
             }
             met = meet(641) && met;
             if (met && *last_flag) {
-                // The 128 threads of a group sum their plane (dV or dK) of the key block: 128
-                // rows x D fp32 per part, contiguous, taken as float4 positions dealt round-robin
-                // to the threads so that a warp reads 512 contiguous bytes per part. All parts
+                // The 128 threads of a group sum their plane (dV or dK) of the key block, thread
+                // r the row r: the parts are column-major in float4 units (see the stores
+                // above), so a warp reads 512 contiguous bytes per part and position. All parts
                 // of two positions are requested before any is used (the sums wait for L2 once
                 // per two positions, not once per part), and are added in the order of the
                 // parts: the same bits whoever is last.
                 const float mul = g == 0 ? 1.f : p.scale;
-                __nv_bfloat16* dst = g == 0 ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] : p.dk + b * p.dks[0] + hk * p.dks[1];
-                const int64_t dst_row = g == 0 ? p.dvs[2] : p.dks[2];
+                const int block_rows = min(kBM, si.lk - k0);
+                __nv_bfloat16* dst = (g == 0 ? p.dv_out + b * p.dvs[0] + hk * p.dvs[1] : p.dk + b * p.dks[0] + hk * p.dks[1]) +
+                                     static_cast<int64_t>(si.k_off + k0 + row) * (g == 0 ? p.dvs[2] : p.dks[2]);
                 const int64_t key_rows = p.cu_q ? p.total_k : p.sk;
                 const int64_t planes = static_cast<int64_t>(p.cu_q ? 1 : p.batch) * p.kv_heads * p.gsplit;
                 const float* src = p.dkv_partial + (g * planes + (static_cast<int64_t>(p.cu_q ? 0 : b) * p.kv_heads + hk) * p.gsplit) * key_rows * D +
                                    static_cast<int64_t>(si.k_off + k0) * D;
                 const int64_t part_stride = key_rows * D;
-                constexpr int kPositions = 128 * D / 4 / 128;   // float4 positions per thread
-                constexpr int kMaxParts = 8;                    // backward_group_split never asks for more
-                for (int i = 0; i < kPositions; i += 2) {
-                    float4 part[2][kMaxParts];
+                constexpr int kPositions = D / 4;   // float4 positions per thread: the row's columns
+                constexpr int kMaxParts = 8;        // backward_group_split never asks for more
+                if (row < block_rows) {
+                    for (int i = 0; i < kPositions; i += 2) {
+                        float4 part[2][kMaxParts];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int f = (i + u) * 128 + row;
+                        for (int u = 0; u < 2; ++u) {
 #pragma unroll
-                        for (int s_ = 0; s_ < kMaxParts; ++s_) {
-                            if (s_ < p.gsplit) part[u][s_] = __ldcg(reinterpret_cast<const float4*>(src + s_ * part_stride) + f);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int f = (i + u) * 128 + row;
-                        const int r = f / (D / 4), c4 = f % (D / 4);
-                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                        for (int s_ = 0; s_ < kMaxParts; ++s_) {
-                            if (s_ < p.gsplit) {
-                                acc.x += part[u][s_].x;
-                                acc.y += part[u][s_].y;
-                                acc.z += part[u][s_].z;
-                                acc.w += part[u][s_].w;
+                            for (int s_ = 0; s_ < kMaxParts; ++s_) {
+                                if (s_ < p.gsplit) part[u][s_] = __ldcg(reinterpret_cast<const float4*>(src + s_ * part_stride) + (i + u) * block_rows + row);
                             }
                         }
-                        if (k0 + r < si.lk) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int s_ = 0; s_ < kMaxParts; ++s_) {
+                                if (s_ < p.gsplit) {
+                                    acc.x += part[u][s_].x;
+                                    acc.y += part[u][s_].y;
+                                    acc.z += part[u][s_].z;
+                                    acc.w += part[u][s_].w;
+                                }
+                            }
                             uint2 v;
                             v.x = pack_bf16(acc.x * mul, acc.y * mul);
                             v.y = pack_bf16(acc.z * mul, acc.w * mul);
-                            *reinterpret_cast<uint2*>(dst + static_cast<int64_t>(si.k_off + k0 + r) * dst_row + c4 * 4) = v;
+                            *reinterpret_cast<uint2*>(dst + (i + u) * 4) = v;
                         }
                     }
                 }

@@ -44,7 +44,7 @@ struct AttnParams {
     // tcgen05 backward with grouped heads: the query heads of a group are split over
     // `gsplit` CTAs per key block, which leave fp32 partial dV / dK here for a reduction.
     int gsplit;
-    float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows][d]
+    float* dkv_partial;  // [2 (dV, dK)][batch or 1][kv_heads][gsplit][key rows x d], each 128-key block column-major in float4 units
     int32_t* fwd_work_counter;  // forward, optional: one zeroed int32 the persistent CTAs draw their items from
     int32_t* fwd_done_counter;  // with it, optional: a second zeroed int32; the kernel then leaves both zero
     int32_t* dkv_counters;  // [batch][kv_heads][key blocks] tickets of the CTAs sharing a key block; zeroed by the delta kernel
