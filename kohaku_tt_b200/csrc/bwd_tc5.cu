@@ -68,7 +68,7 @@ struct BwdPlan {
     static constexpr int kA1 = kA0 + kSub * kTile;
     static constexpr int kB0 = kA1 + kSub * kTile;
     static constexpr int kB1 = kB0 + kStages * kSub * kTile;
-    static constexpr int kVec = kB1 + kStages * kSub * kTile;  // float [2 buffers][3 vectors][128]
+    static constexpr int kVec = kB1 + kStages * kSub * kTile;  // float [3 buffers][2 vectors][128] (dK/dV), [2][128] mask terms (dQ)
     static constexpr int kBars = kVec + 2 * 3 * 128 * 4;
     static constexpr int kBytes = kBars + 256;
     static constexpr int bAFull = 0;
@@ -134,7 +134,7 @@ __device__ __forceinline__ void dkv_body(
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kBars + P::bCount * 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::kBars + P::bCount * 8 + 8);
-    float* vec = reinterpret_cast<float*>(smem + P::kVec);  // [buf][0: lse2, 1: delta][128]
+    float* vec = reinterpret_cast<float*>(smem + P::kVec);  // [item mod 3][0: lse2, 1: delta][128]
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -369,8 +369,30 @@ __device__ __forceinline__ void dkv_body(
             }
             return exists ? raw : 0.f;
         };
+        // The vectors have three buffers (item mod 3) so that a warp can publish the terms of
+        // item i + 1 and sign in at that item's meeting while it starts on item i: the buffer
+        // it overwrites was read in item i - 2, which every warp has left (all have signed
+        // in at meeting i, which they do at the top of item i - 1). By the time a warp
+        // waits for meeting i + 1 the others have usually long signed in; met right after
+        // the write, the warps waited for the slowest of them in every item (560 clk of a
+        // 2,750-clk item).
+        auto publish = [&](int it, float raw, bool exists) {
+            float* buf = vec + (it % 3) * 256;
+            (g == 0 ? buf : buf + 128)[row] = row_term(raw, exists);
+            mbar_arrive_warp(bar(P::bMeet));
+        };
+        auto met_for = [&](int code) -> bool {
+            const bool met = __all_sync(0xffffffffu, mbar_wait(bar(P::bMeet), meets & 1, abort_flag, code, tp.status));
+            ++meets;
+            return met;
+        };
         bool pre_exists = false;
-        float pre = nitems > 0 ? fetch(pre_exists) : 0.f;
+        float pre = 0.f;
+        if (nitems > 0) {
+            pre = fetch(pre_exists);
+            publish(0, pre, pre_exists);
+            if (nitems > 1) pre = fetch(pre_exists);
+        }
         // While a trace buffer is set the CTA's first thread adds up where its item loop
         // waits (row 64 + 512 + CTA: meeting, wait for S, phase 1, wait for dP, phase 2).
         const bool timing = tp.trace && (threadIdx.x & 31) == 0 && blockIdx.x < 56;   // one row of 8 slots per warp
@@ -384,13 +406,13 @@ __device__ __forceinline__ void dkv_body(
         };
 
         for (int it = 0; it < nitems; ++it) {
-            float* lse2 = vec + (it & 1) * 256;
+            float* lse2 = vec + (it % 3) * 256;
             float* delta = lse2 + 128;
-            (g == 0 ? lse2 : delta)[row] = row_term(pre, pre_exists);
-            ok = meet(630);
+            ok = met_for(630);   // everybody's terms of item `it` are in
             if (!ok) break;
+            if (it + 1 < nitems) publish(it + 1, pre, pre_exists);
             mask_term(it);
-            if (it + 1 < nitems) pre = fetch(pre_exists);
+            if (it + 2 < nitems) pre = fetch(pre_exists);
             lap(0);
             const int q0 = (qstart + cur_qb) * kBN;
             const uint32_t tmem_s = tmem_s_of(it);
