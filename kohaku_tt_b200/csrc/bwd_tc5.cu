@@ -49,11 +49,33 @@ __host__ __device__ constexpr bool poly_pair(int pair) {
 }
 constexpr int kTmemCols = 512;
 
+// Division by a number fixed at launch, for 0 <= n < 2^31: a multiply and a shift where the
+// hardware's integer division is a chain of some twenty dependent instructions. A CTA does
+// about ten of them one after the other before it knows its tile, with nothing to overlap.
+struct Divisor {
+    uint32_t mul, shift, d;
+};
+inline Divisor divisor_of(int d) {
+    Divisor f;
+    f.d = static_cast<uint32_t>(d);
+    f.shift = 0;
+    while ((1u << f.shift) < f.d) ++f.shift;   // ceil(log2 d)
+    f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << f.shift) - f.d)) / f.d + 1);
+    return f;
+}
+__device__ __forceinline__ int div_by(int n, const Divisor& f) {
+    return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shift);
+}
+__device__ __forceinline__ int mod_by(int n, const Divisor& f) {
+    return n - div_by(n, f) * static_cast<int>(f.d);
+}
+
 struct BwdParams {
     AttnParams a;
     int* status;
     int dim_of[4][3];  // q, k, v, dout: tensor-map coordinate slot of row, head, batch
     long long* trace;  // optional (ktt_b200_set_trace): per-CTA start / end / SM
+    Divisor by_dkv_x, by_dkv_y, by_dq_x, by_dq_y, by_gsplit, by_group;   // group: query heads per kv head
 };
 
 
@@ -140,13 +162,13 @@ __device__ __forceinline__ void dkv_body(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // blockIdx.x = kv head * gsplit + part: this CTA handles query heads [g0, g0 + group) of
     // the kv head's GQA group.
-    const int hk = bx / p.gsplit, part = bx % p.gsplit, kb = by, b = bz;
+    const int hk = div_by(bx, tp.by_gsplit), part = bx - hk * p.gsplit, kb = by, b = bz;
     const SeqInfo si = seq_info(p, b);
     const int k0 = kb * kBM;
     if (k0 >= si.lk) return;
-    const int full_group = p.heads / p.kv_heads;
-    const int g0 = part * full_group / p.gsplit;
-    const int group = (part + 1) * full_group / p.gsplit - g0;
+    const int full_group = static_cast<int>(tp.by_group.d);
+    const int g0 = div_by(part * full_group, tp.by_gsplit);
+    const int group = div_by((part + 1) * full_group, tp.by_gsplit) - g0;
     const int nq = (si.lq + kBN - 1) / kBN;
     int qstart = 0;
     if (p.causal) {
@@ -163,13 +185,19 @@ __device__ __forceinline__ void dkv_body(
         c[tp.dim_of[operand][2]] = batch;
     };
     const int batch_c = p.cu_q ? 0 : b;
-    // Q and dO tiles of item `it` into their ring stage (producer warp, converged).
+    // Q and dO tiles of item `it` into their ring stage (producer warp, converged; called for
+    // it = 0, 1, 2, ... in turn, so head and query block are counted, not divided out).
+    int ld_head = 0, ld_qb = 0;
     auto load_item = [&](int it) {
         int c[4], c2[4];
         c[0] = c2[0] = 0;
         const int st = it % P::kStages;
-        const int h = hk * full_group + g0 + it / per_head;
-        const int q0 = (qstart + it % per_head) * kBN;
+        const int h = hk * full_group + g0 + ld_head;
+        const int q0 = (qstart + ld_qb) * kBN;
+        if (++ld_qb == per_head) {
+            ld_qb = 0;
+            ++ld_head;
+        }
         coords(0, si.q_off + q0, h, batch_c, c);
         coords(3, si.q_off + q0, h, batch_c, c2);
         mbar_expect_tx(bar(P::bBFull + st), 2 * P::kSub * P::kTile);
@@ -675,7 +703,7 @@ __device__ __forceinline__ void dq_body(
     const SeqInfo si = seq_info(p, b);
     const int q0 = qb * kBM;
     if (q0 >= si.lq) return;
-    const int hk = h / (p.heads / p.kv_heads);
+    const int hk = div_by(h, tp.by_group);
     int kend = si.klen;
     if (p.causal) kend = min(kend, min(q0 + kBM, si.lq) - 1 + si.shift + 1);
     const int nblocks = kend > 0 ? (kend + kBN - 1) / kBN : 0;
@@ -1010,10 +1038,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc5_kernel(
         }
     } stamp{tp, t_start};
     if (id < n_dkv) {
-        dkv_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id % dkv_x, (id / dkv_x) % dkv_y, id / (dkv_x * dkv_y), dkv_y);
+        const int rest = div_by(id, tp.by_dkv_x), bz = div_by(rest, tp.by_dkv_y);
+        dkv_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id - rest * dkv_x, rest - bz * dkv_y, bz, dkv_y);
     } else {
         id -= n_dkv;
-        dq_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id % dq_x, (id / dq_x) % dq_y, id / (dq_x * dq_y), dq_y);
+        const int rest = div_by(id, tp.by_dq_x), bz = div_by(rest, tp.by_dq_y);
+        dq_body<D, kMask>(&map_q, &map_k, &map_v, &map_do, tp, id - rest * dq_x, rest - bz * dq_y, bz, dq_y);
     }
 }
 
@@ -1069,6 +1099,12 @@ int launch_bwd(const AttnParams& p, cudaStream_t stream) {
     if (int rc = ensure_smem(kernel, smem, "cudaFuncSetAttribute(bwd_tc5)")) return rc;
     const int dkv_x = p.kv_heads * p.gsplit, dkv_y = (p.sk + kBM - 1) / kBM;
     const int dq_x = p.heads, dq_y = (p.sq + kBM - 1) / kBM;
+    tp.by_dkv_x = divisor_of(dkv_x);
+    tp.by_dkv_y = divisor_of(dkv_y > 0 ? dkv_y : 1);
+    tp.by_dq_x = divisor_of(dq_x);
+    tp.by_dq_y = divisor_of(dq_y > 0 ? dq_y : 1);
+    tp.by_gsplit = divisor_of(p.gsplit);
+    tp.by_group = divisor_of(p.heads / p.kv_heads);
     const int64_t n_dkv = static_cast<int64_t>(dkv_x) * dkv_y * p.batch;
     const int64_t n_all = n_dkv + static_cast<int64_t>(dq_x) * dq_y * p.batch;
     if (n_all > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 backward: too many tiles");
