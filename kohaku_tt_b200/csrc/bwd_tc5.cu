@@ -49,27 +49,6 @@ __host__ __device__ constexpr bool poly_pair(int pair) {
 }
 constexpr int kTmemCols = 512;
 
-// Division by a number fixed at launch, for 0 <= n < 2^31: a multiply and a shift where the
-// hardware's integer division is a chain of some twenty dependent instructions. A CTA does
-// about ten of them one after the other before it knows its tile, with nothing to overlap.
-struct Divisor {
-    uint32_t mul, shift, d;
-};
-inline Divisor divisor_of(int d) {
-    Divisor f;
-    f.d = static_cast<uint32_t>(d);
-    f.shift = 0;
-    while ((1u << f.shift) < f.d) ++f.shift;   // ceil(log2 d)
-    f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << f.shift) - f.d)) / f.d + 1);
-    return f;
-}
-__device__ __forceinline__ int div_by(int n, const Divisor& f) {
-    return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shift);
-}
-__device__ __forceinline__ int mod_by(int n, const Divisor& f) {
-    return n - div_by(n, f) * static_cast<int>(f.d);
-}
-
 struct BwdParams {
     AttnParams a;
     int* status;

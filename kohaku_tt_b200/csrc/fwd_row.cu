@@ -128,6 +128,7 @@ struct RowParams {
     int* work_counter;  // null: a fixed deal
     int* done_counter;
     int grouped;        // tile order (decode_unit): 1 when K / V exceed what L2 keeps (needs the counter)
+    Divisor by_heads, by_batch, by_kv_heads, by_group, by_per_pair;   // group: query heads per K/V head; per_pair: q_tiles * group
 };
 
 struct Unit {
@@ -148,17 +149,17 @@ __device__ __forceinline__ Unit decode_unit(const RowParams& tp, int u, int stre
     if (tp.grouped) {
         // All query tiles of one (batch, K / V head) follow one another, longest first, the
         // heads of the GQA group fastest: the tiles in flight share a few pairs' K / V in L2.
-        const int group = p.heads / p.kv_heads;
-        const int per_pair = tp.q_tiles * group;
-        const int pair = u / per_pair, r = u % per_pair;
-        k.b = pair / p.kv_heads;
-        k.h = (pair % p.kv_heads) * group + r % group;
-        qb = tp.q_tiles - 1 - r / group;
+        const int group = static_cast<int>(tp.by_group.d);
+        const int pair = div_by(u, tp.by_per_pair), r = u - pair * static_cast<int>(tp.by_per_pair.d);
+        const int tile = div_by(r, tp.by_group);
+        k.b = div_by(pair, tp.by_kv_heads);
+        k.h = (pair - k.b * p.kv_heads) * group + (r - tile * group);
+        qb = tp.q_tiles - 1 - tile;
     } else {
-        k.h = u % p.heads;
-        const int t = u / p.heads;
-        k.b = t % p.batch;
-        qb = tp.q_tiles - 1 - t / p.batch;
+        const int t = div_by(u, tp.by_heads), level = div_by(t, tp.by_batch);
+        k.h = u - t * p.heads;
+        k.b = t - level * p.batch;
+        qb = tp.q_tiles - 1 - level;
     }
     k.si = seq_info(p, k.b);
     k.q0 = qb * kBM;
@@ -235,7 +236,6 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
     volatile int* work_slot = reinterpret_cast<volatile int*>(small + P::kBars + P::bCount * 8 + 16);  // [2], per stream (bytes 16..23)
 
     const AttnParams& p = tp.a;
-    const int group_size = p.heads / p.kv_heads;
 
     if (is_producer) {
         if (lane < P::bCount) {
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
             const Unit k = decode_unit(tp, u, stream);
             const int nb = k.j1 - k.j0;
             if (!k.valid || nb <= 0) continue;
-            const int hk = k.h / group_size;
+            const int hk = div_by(k.h, tp.by_group);
             int c[4], cv[4];
             const int batch = p.cu_q ? 0 : k.b;
             c[0] = cv[0] = 0;
@@ -764,17 +764,22 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
             // The row sum: half 1 hands its part to half 0, which adds (always in this order)
             // and hands the total back.
             float l_row = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
-            volatile float* lsum = reinterpret_cast<volatile float*>(pair_words);
-            if (group == 1) lsum[row] = l_row;
+            // The word of this row lies inside the 128 bytes that hold the maxima of this pair
+            // of warps (16-bit words [half][row], 64 bytes per half and pair): the pair's own
+            // meetings order every access to them. (Indexed by row as floats, the sums of one
+            // pair lay over the maxima of another, which may already be in its next tile:
+            // sixteen rows of a tile came out wrong once in a few hundred tiles.)
+            volatile float* lsum = reinterpret_cast<volatile float*>(pair_words + (lane < 16 ? 0 : 256) + quarter * 64 + (lane & 15) * 4);
+            if (group == 1) *lsum = l_row;
             ok = pair_meet(370);
             if (!ok) break;
             if (group == 0) {
-                l_row += lsum[row];
-                lsum[row] = l_row;
+                l_row += *lsum;
+                *lsum = l_row;
             }
             ok = pair_meet(371);
             if (!ok) break;
-            if (group == 1) l_row = lsum[row];
+            if (group == 1) l_row = *lsum;
             // Half 0 writes these words again in the next unit's first exchange: not before
             // half 1 has read the total.
             ok = pair_meet(372);
@@ -946,6 +951,11 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
     tp.q_tiles = (p.sq + kBM - 1) / kBM;
+    tp.by_heads = divisor_of(p.heads);
+    tp.by_batch = divisor_of(p.batch > 0 ? p.batch : 1);
+    tp.by_kv_heads = divisor_of(p.kv_heads);
+    tp.by_group = divisor_of(p.heads / p.kv_heads);
+    tp.by_per_pair = divisor_of(tp.q_tiles > 0 ? tp.q_tiles * (p.heads / p.kv_heads) : 1);
     const int64_t tiles = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;
     if (tiles > 0x3fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: too many query tiles");
     tp.units = static_cast<int>(tiles);

@@ -113,6 +113,7 @@ struct Tc5Params {
     int* work_counter;  // optional (zero before the launch): the CTAs draw their items from it
     int* done_counter;  // with it: producers that have drawn their last; the last one puts both back to zero
     int grouped;        // item order (decode_work): 1 with a counter
+    Divisor by_heads, by_batch, by_kv_heads, by_group, by_per_pair;   // group: query heads per K/V head; per_pair: q_tiles * group
 };
 
 // Profiling zones (the counterpart of the reference's FLASH_PROFILE device zones,
@@ -149,17 +150,17 @@ __device__ __forceinline__ Work decode_work(const Tc5Params& tp, int w) {
     Work k;
     int qb;
     if (tp.grouped) {
-        const int group = p.heads / p.kv_heads;
-        const int per_pair = tp.q_tiles * group;
-        const int pair = w / per_pair, r = w % per_pair;
-        k.b = pair / p.kv_heads;
-        k.h = (pair % p.kv_heads) * group + r % group;
-        qb = tp.q_tiles - 1 - r / group;
+        const int group = static_cast<int>(tp.by_group.d);
+        const int pair = div_by(w, tp.by_per_pair), r = w - pair * static_cast<int>(tp.by_per_pair.d);
+        const int tile = div_by(r, tp.by_group);
+        k.b = div_by(pair, tp.by_kv_heads);
+        k.h = (pair - k.b * p.kv_heads) * group + (r - tile * group);
+        qb = tp.q_tiles - 1 - tile;
     } else {
-        k.h = w % p.heads;
-        const int t = w / p.heads;
-        k.b = t % p.batch;
-        qb = tp.q_tiles - 1 - t / p.batch;
+        const int t = div_by(w, tp.by_heads), level = div_by(t, tp.by_batch);
+        k.h = w - t * p.heads;
+        k.b = t - level * p.batch;
+        qb = tp.q_tiles - 1 - level;
     }
     k.si = seq_info(p, k.b);
     k.q0 = qb * kBM;
@@ -211,7 +212,6 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
 
     const AttnParams& p = tp.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int group_size = p.heads / p.kv_heads;
 
     // The producer warp sets the barriers up itself and goes straight to its first loads;
     // it only arrives at the start-up barrier, the others wait there for it and for the
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
             if (w == -2) continue;
             const Work k = decode_work(tp, w);
             if (k.nblocks == 0) continue;
-            const int hk = k.h / group_size;
+            const int hk = div_by(k.h, tp.by_group);
             int c[4], cv[4];
             const int batch = p.cu_q ? 0 : k.b;
             c[0] = cv[0] = 0;
@@ -1061,6 +1061,11 @@ int launch_tc5(const AttnParams& p, cudaStream_t stream) {
                          : (tp.trace ? fwd_tc5_kernel<D, true, false> : fwd_tc5_kernel<D, false, false>);
     if (int rc = ensure_smem(kernel, smem, "cudaFuncSetAttribute(fwd_tc5)")) return rc;
     tp.q_tiles = (p.sq + kBM - 1) / kBM;
+    tp.by_heads = divisor_of(p.heads);
+    tp.by_batch = divisor_of(p.batch > 0 ? p.batch : 1);
+    tp.by_kv_heads = divisor_of(p.kv_heads);
+    tp.by_group = divisor_of(p.heads / p.kv_heads);
+    tp.by_per_pair = divisor_of(tp.q_tiles > 0 ? tp.q_tiles * (p.heads / p.kv_heads) : 1);
     const int64_t work = static_cast<int64_t>(p.heads) * p.batch * tp.q_tiles;
     if (work > 0x7fffffff) return fail(KTT_B200_ERR_UNSUPPORTED, "tcgen05 forward: too many query tiles");
     tp.work = static_cast<int>(work);

@@ -44,6 +44,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Division by a number fixed at launch, for 0 <= n < 2^31: a multiply and a shift where the
+// integer division of a runtime value is a chain of some twenty dependent instructions. A
+// kernel that finds its tile from an index does several of them one after the other, with
+// nothing to overlap.
+struct Divisor {
+    uint32_t mul, shift, d;
+};
+inline Divisor divisor_of(int d) {
+    Divisor f;
+    f.d = static_cast<uint32_t>(d);
+    f.shift = 0;
+    while ((1u << f.shift) < f.d) ++f.shift;   // ceil(log2 d)
+    f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << f.shift) - f.d)) / f.d + 1);
+    return f;
+}
+__device__ __forceinline__ int div_by(int n, const Divisor& f) {
+    return static_cast<int>((__umulhi(static_cast<uint32_t>(n), f.mul) + static_cast<uint32_t>(n)) >> f.shift);
+}
+__device__ __forceinline__ int mod_by(int n, const Divisor& f) {
+    return n - div_by(n, f) * static_cast<int>(f.d);
+}
+
 // Bounded wait. Returns false when it gave up (its own limit, or another role's).
 __device__ __noinline__ inline bool mbar_wait_slow(
     uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status, long long limit = kWaitCycles) {

@@ -125,6 +125,24 @@ def test_drawn_work_equals_the_fixed_deal_for_whole_tiles(cuda):
     assert torch.equal(drawn, fixed) and torch.equal(drawn_lse, fixed_lse)
 
 
+def test_fixed_deal_is_reproducible_over_thousands_of_tiles(cuda):
+    # 4,096 tiles without a workspace: every stream walks its own list of tiles and the warps
+    # of a stream drift apart by up to a tile. What two warps exchange through shared memory
+    # must stay inside their own words whatever the others do (the row sums of one pair of
+    # warps once lay over the maxima of another pair: sixteen rows of a tile in a few hundred
+    # came out wrong, differently on every run). Two runs give the same bits, and the same
+    # bits as the drawn order.
+    g = torch.Generator(device=cuda).manual_seed(11)
+    q, k, v = (torch.randn((8, 16, 4096, 64), generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+    first, first_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash", dynamic=False)
+    second, second_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash", dynamic=False)
+    drawn, drawn_lse = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    torch.cuda.synchronize()
+    _lib.device_status()
+    assert torch.equal(first, second) and torch.equal(first_lse, second_lse)
+    assert torch.equal(first, drawn) and torch.equal(first_lse, drawn_lse)
+
+
 @pytest.mark.parametrize("d", [64, 128])
 def test_tiles_grouped_by_kv_head_when_kv_exceeds_l2(cuda, d):
     # 268 MB of K / V: with a workspace the tiles of one (batch, head)
