@@ -192,3 +192,28 @@ def test_key_lengths_and_one_row_masks_on_shared_tiles(cuda):
     out, _ = ops.sdpa_forward(q.to(cuda), k.to(cuda), v.to(cuda), mask=keep.to(cuda), kernel="flash")
     assert rel(out, ao.ruler_dense(q, k, v, mask=keep)) <= FWD_BOUND
     assert ktt.counters()["attention_flash"] > 0
+
+
+# Both tcgen05 forward kernels and the tcgen05 backward, launched three times on the same
+# inputs, with and without a workspace (drawn and fixed order of the tiles): every launch gives
+# the same bits. Which CTA takes which tile, and how far the warps of a CTA drift apart,
+# differs from launch to launch; nothing in the arithmetic may depend on it.
+@pytest.mark.parametrize("b,h,hk,s,d,causal", [
+    (8, 14, 2, 2048, 64, True), (4, 16, 4, 4096, 64, True), (2, 10, 10, 4096, 64, False),
+    (8, 16, 4, 2048, 128, True), (3, 8, 2, 1500, 128, False),
+])
+def test_every_launch_gives_the_same_bits(cuda, b, h, hk, s, d, causal):
+    g = torch.Generator(device=cuda).manual_seed(b * 1000 + s + d)
+    q, k, v, do = (torch.randn((b, n, s, d), generator=g, device=cuda, dtype=torch.float32).to(torch.bfloat16) for n in (h, hk, hk, h))
+    runs = []
+    for _ in range(3):
+        runs.append(ops.sdpa_forward(q, k, v, causal=causal, kernel="flash"))
+        runs.append(ops.sdpa_forward(q, k, v, causal=causal, kernel="flash", dynamic=False))
+    out, lse = runs[0]
+    grads = [ops.sdpa_backward(do, q, k, v, out, lse, causal=causal) for _ in range(3)]
+    torch.cuda.synchronize()
+    _lib.device_status()
+    for other, other_lse in runs[1:]:
+        assert torch.equal(out, other) and torch.equal(lse, other_lse)
+    for other in grads[1:]:
+        assert all(torch.equal(x, y) for x, y in zip(grads[0], other))
