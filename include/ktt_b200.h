@@ -191,7 +191,9 @@ KTT_B200_API int ktt_b200_probe_read(const void* data, int64_t bytes, int32_t* s
  * CTA its start and end on the global nanosecond timer, its SM and its key-block count; the
  * buffer then holds (64 + 1024) x 8 int64. (The head-dim-64 forward's slots per key block:
  * S ready, maximum known, exponentials done, P published, first chunk loaded, its
- * exponentials done, previous P V done, second chunk loaded; row 60 holds its epilogue.)
+ * exponentials done, previous P V done, second chunk loaded; row 60 holds its epilogue:
+ * last P V done, outputs written, row sums exchanged and, for a tile the CTA's two streams
+ * share, the other stream's half published, read, merged.)
  * The decode kernel writes, per CTA, rows 64.. with six nanosecond stamps: start,
  * dependency wait over, lengths scanned, first tile landed, stream done, end. The tcgen05
  * backward writes, per CTA, rows 64..: start, end, SM, CTA index, set-up done, first scores,

@@ -73,8 +73,9 @@ def forward(dev):
         print(f"  {j:2d}: " + " | ".join(f"{int(table[j, s]) - base:6d}" if int(table[j, s]) else "     -" for s in order))
     epi = table[60]
     if int(epi[0]):
-        print("epilogue: last P V done %d, row sums exchanged %d, written %d (clk after the first S)"
-              % (int(epi[0]) - base, int(epi[2]) - base, int(epi[1]) - base))
+        other = ", other stream's half in %d, read %d, merged %d" % tuple(int(epi[i]) - base for i in (3, 4, 5)) if int(epi[3]) else ""
+        print("epilogue: last P V done %d, row sums exchanged %d%s, written %d (clk after the first S)"
+              % (int(epi[0]) - base, int(epi[2]) - base, other, int(epi[1]) - base))
     rows = _cta_rows(table)
     _, per_sm = _by_sm(rows)
     ends = sorted(max(e for _, e, _ in v_) for v_ in per_sm.values())
