@@ -183,6 +183,30 @@ KTT_B200_API int ktt_b200_selftest_wait_timeout(void* stream);
  * counterpart in the reference. */
 KTT_B200_API int ktt_b200_probe_read(const void* data, int64_t bytes, int32_t* sink, void* stream);
 
+/* Debug dump of one query tile, the counterpart of the reference's FLASH_DUMP build
+ * (ktt_flash/program.hpp:56-65, aten_attention.cpp:814-831: `_debug_flash_dump(q, k, v,
+ * is_causal, row)`, the intermediate tiles of one query tile row). While a device buffer is
+ * set, every head-dim-64 tcgen05 forward launch runs its traced instantiation, and the
+ * tile (batch, head, q_tile: rows q_tile * 128 ..) writes out what its row threads hold,
+ * straight from their registers:
+ *   per key block j < max_blocks, KTT_B200_DUMP_BLOCK_FLOATS floats:
+ *     x [128][128]   the exponents, logit * scale * log2(e) (+ mask term) - reference, -inf
+ *                    where the key is hidden;
+ *     p [128][128]   2^x as the bf16 values that feed P V;
+ *     m [2][128]     the reference maximum of each half row (keys 0-63, 64-127 of the block)
+ *                    while this block was processed (it moves only when a block exceeds it
+ *                    by 2^8, and the two halves of a row agree on it);
+ *   then, at float offset max_blocks * KTT_B200_DUMP_BLOCK_FLOATS:
+ *     o [128][64]    the unnormalised output accumulator at the end of the tile (of a tile
+ *                    shared by a CTA's two streams: after their halves were merged);
+ *     m [128], l [128]   the final reference maximum and the row sum; lse = ln 2 (m + log2 l).
+ * Blocks of a shared tile's second half are measured against that stream's own reference.
+ * Entries of rows or blocks the tile does not have are left as they were. Null clears the
+ * request. Process-wide, like the trace buffer; not meant for concurrent launches. */
+#define KTT_B200_DUMP_BLOCK_FLOATS (2 * 128 * 128 + 2 * 128)
+#define KTT_B200_DUMP_TAIL_FLOATS (128 * 64 + 2 * 128)
+KTT_B200_API int ktt_b200_set_dump(float* device_buffer, int32_t batch, int32_t head, int32_t q_tile, int32_t max_blocks);
+
 /* Profiling zones, the counterpart of the reference's FLASH_PROFILE device zones
  * (ktt_flash/compute.cpp:25-30, program.hpp:56-65): with a device buffer of 64 x 8 int64
  * set, CTA (0, 0, 0) of every tcgen05 forward launch stamps clock64 per key block (slots:

@@ -17,6 +17,7 @@ from .aten import fused_sdp_choice, install, installed, installed_for, uninstall
 from .attention import decode_step, sdpa, sdpa_varlen
 from .numerics import KERNELS, sdpa_kernel
 from .stats import diff_stats, format_stats, rel_rms
+from .trace import debug_flash_dump
 
 AVAILABLE = True
 
@@ -45,6 +46,7 @@ __all__ = [
     "reset_counters",
     "sdpa",
     "sdpa_kernel",
+    "debug_flash_dump",
     "sdpa_varlen",
     "uninstall",
 ]

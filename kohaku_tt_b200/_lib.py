@@ -47,6 +47,7 @@ EXPORTS = (
     "ktt_b200_selftest_wait_timeout",
     "ktt_b200_probe_read",
     "ktt_b200_set_trace",
+    "ktt_b200_set_dump",
     "ktt_b200_sdpa_supported",
     "ktt_b200_sdpa_backward_supported",
     "ktt_b200_sdpa_forward",
@@ -278,6 +279,8 @@ def lib():
     handle.ktt_b200_decode_static.argtypes = [ctypes.POINTER(DecodeArgs), _ptr]
     handle.ktt_b200_decode_append.argtypes = [ctypes.POINTER(DecodeAppendArgs), _ptr]
     handle.ktt_b200_set_trace.argtypes = [_ptr]
+    handle.ktt_b200_set_dump.argtypes = [_ptr, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    handle.ktt_b200_set_dump.restype = ctypes.c_int
     handle.ktt_b200_selftest_wait_timeout.argtypes = [_ptr]
     handle.ktt_b200_probe_read.argtypes = [_ptr, ctypes.c_int64, _ptr, _ptr]
     handle.ktt_b200_merge_partials.argtypes = [_ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _ptr]

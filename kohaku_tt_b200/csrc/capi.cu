@@ -240,6 +240,20 @@ extern "C" int ktt_b200_selftest_wait_timeout(void* stream) {
     return selftest_wait_timeout(static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int ktt_b200_set_dump(float* device_buffer, int32_t batch, int32_t head, int32_t q_tile, int32_t max_blocks) {
+    if (device_buffer && (batch < 0 || head < 0 || q_tile < 0 || max_blocks < 1)) {
+        return fail(KTT_B200_ERR_BAD_ARGUMENT, "set_dump: negative index or no room for a key block");
+    }
+    DumpRequest r;
+    r.buffer = device_buffer;
+    r.batch = batch;
+    r.head = head;
+    r.q_tile = q_tile;
+    r.max_blocks = max_blocks;
+    set_dump_request(r);
+    return 0;
+}
+
 extern "C" int ktt_b200_set_trace(void* device_buffer) {
     set_trace_buffer(static_cast<long long*>(device_buffer));
     return 0;

@@ -210,6 +210,13 @@ int device_status(int* code);
 int selftest_wait_timeout(cudaStream_t stream);
 // Profiling zones of the tcgen05 forward: a device buffer of 64 x 8 int64, or null.
 void set_trace_buffer(long long* device_buffer);
+// One query tile whose intermediate values the head-dim-64 forward writes out (ktt_b200_set_dump).
+struct DumpRequest {
+    float* buffer;   // device, null: no dump
+    int batch, head, q_tile, max_blocks;
+};
+void set_dump_request(const DumpRequest& r);
+DumpRequest get_dump_request();
 long long* get_trace_buffer();   // what set_trace_buffer was given last, or null
 
 }  // namespace ktt

@@ -129,7 +129,16 @@ struct RowParams {
     int* done_counter;
     int grouped;        // tile order (decode_unit): 1 when K / V exceed what L2 keeps (needs the counter)
     Divisor by_heads, by_batch, by_kv_heads, by_group, by_per_pair;   // group: query heads per K/V head; per_pair: q_tiles * group
+    // Optional (ktt_b200_set_dump, traced instantiation only): the tile (dump_b, dump_h, first row
+    // dump_q0) writes what its row threads hold to `dump`: per key block kDumpBlock floats (the
+    // exponents x = logit - reference [128][128], P = 2^x as the bf16 fed to P V [128][128], the
+    // reference maximum of each half row [2][128]), then, behind dump_blocks blocks, the
+    // unnormalised O [128][64], the final maximum [128] and the row sum [128].
+    float* dump;
+    int dump_b, dump_h, dump_q0, dump_blocks;
 };
+constexpr int kDumpBlock = 2 * 128 * 128 + 2 * 128;
+constexpr int kDumpTail = 128 * 64 + 2 * 128;
 
 struct Unit {
     int b, h, q0;
@@ -526,6 +535,8 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
             // What the block loop needs of the unit, as a few scalars: the unit is decoded again
             // for the epilogue rather than kept in registers across the loop.
             int nb, col0, row_limit;
+            bool dumping = false;   // traced instantiation: this is the tile whose values are written out
+            int dump_j0 = 0;
             int mask_b = 0, mask_h = 0, mask_koff = 0, mask_klen = 1;
             {
                 const Unit k = decode_unit(tp, u, stream);
@@ -543,6 +554,10 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                     continue;
                 }
                 nb = k.j1 - k.j0;
+                if constexpr (kTrace) {
+                    dumping = tp.dump && k.b == tp.dump_b && k.h == tp.dump_h && k.q0 == tp.dump_q0;
+                    dump_j0 = k.j0;
+                }
                 col0 = k.j0 * kBN + group * 64;   // first key column of this thread in the unit's first block
                 row_limit = k.si.klen;
                 if (p.causal) row_limit = min(row_limit, qi + k.si.shift + 1);
@@ -553,7 +568,7 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                     mask_klen = k.si.klen;
                 }
             }
-            const bool tracer = kTrace && first_unit && row == 0 && group == 0 && blockIdx.x == 0 && stream == 0;
+            const bool tracer = kTrace && tp.trace && first_unit && row == 0 && group == 0 && blockIdx.x == 0 && stream == 0;
             float m_ref = -INFINITY;
             float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             const float sc1 = kMask ? 1.f : p.scale_log2;   // masked logits are scaled when read
@@ -675,6 +690,26 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                 const float2 sc2 = make_float2(sc1, sc1), nm2 = make_float2(-m_use, -m_use);
 
                 // ---- pass 2: P = 2^(logit - m) as packed bf16, 16 columns at a time ----
+                // (Traced instantiation, the dumped tile only: the exponents and P as they are,
+                // and the reference maximum this block is measured against.)
+                float* dump_block = nullptr;
+                if constexpr (kTrace) {
+                    if (dumping && dump_j0 + jj < tp.dump_blocks) {
+                        dump_block = tp.dump + static_cast<int64_t>(dump_j0 + jj) * kDumpBlock;
+                        dump_block[2 * 128 * 128 + group * 128 + row] = m_ref;
+                    }
+                }
+                auto dump_pair = [&](int c, int e, const float2& x, uint32_t packed) {
+                    if constexpr (kTrace) {
+                        if (dump_block) {
+                            float* at = dump_block + row * 128 + group * 64 + c * 16 + 2 * e;
+                            at[0] = x.x;
+                            at[1] = x.y;
+                            at[128 * 128] = __uint_as_float(packed << 16);
+                            at[128 * 128 + 1] = __uint_as_float(packed & 0xffff0000u);
+                        }
+                    }
+                };
                 auto exps = [&](float (&s)[16], int c, uint32_t (&wv)[8]) {
                     logits(s, c);
                     if (whole) {
@@ -692,6 +727,7 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                             }
                             l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
                             wv[e] = pack_bf16(pr.x, pr.y);
+                            dump_pair(c, e, x, wv[e]);
                         }
                     } else {
                         // Hidden columns take MUFU, whose 2^-inf is exactly 0.
@@ -701,6 +737,7 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                             const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
                             l2[e & 1] = __fadd2_rn(l2[e & 1], pr);
                             wv[e] = pack_bf16(pr.x, pr.y);
+                            dump_pair(c, e, x, wv[e]);
                         }
                     }
                 };
@@ -833,6 +870,17 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                 ++didx;
             }
             rzone<kTrace>(tp, tracer, 60, 5);   // the tile's (m, l, O) are final
+            if constexpr (kTrace) {
+                if (dumping && finish) {
+                    float* tail = tp.dump + static_cast<int64_t>(tp.dump_blocks) * kDumpBlock;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) tail[row * 64 + group * 32 + e] = o[e];
+                    if (group == 0) {
+                        tail[128 * 64 + row] = m_row;
+                        tail[128 * 64 + 128 + row] = l_row;
+                    }
+                }
+            }
             if (finish && real) {
                 const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
                 uint32_t w[16];
@@ -881,7 +929,7 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
         tc_fence_after();
         tmem_dealloc(tmem_base, P::kTmemCols * S);
     }
-    if (kTrace && is_mma && lane == 0) {   // lane 0 of a stream's MMA warp knows its block count
+    if (kTrace && tp.trace && is_mma && lane == 0) {   // lane 0 of a stream's MMA warp knows its block count
         const int cta = blockIdx.x * S + stream;
         if (cta < 1024) {
             long long t1;
@@ -962,6 +1010,12 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
     }
     tp.status = dev_status;
     tp.trace = tc5::trace_buffer();
+    const DumpRequest dump = get_dump_request();
+    tp.dump = dump.buffer;
+    tp.dump_b = dump.batch;
+    tp.dump_h = dump.head;
+    tp.dump_q0 = dump.q_tile * kBM;
+    tp.dump_blocks = dump.max_blocks;
     for (int o = 0; o < 3; ++o) {
         for (int i = 0; i < 3; ++i) tp.dim_of[o][i] = orders[o].slot_of[i];
     }
@@ -992,8 +1046,9 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
     const int64_t kv_rows = p.cu_q ? p.total_k : static_cast<int64_t>(p.batch) * p.sk;
     tp.grouped = (have_ws && !tp.dual && kv_rows * p.kv_heads * (p.d + p.dv) * 2 > (192ll << 20)) ? 1 : 0;
     const bool masked = p.mask_dtype != KTT_B200_MASK_NONE;
-    auto kernel = masked ? (tp.trace ? fwd_row_kernel<true, true> : fwd_row_kernel<false, true>)
-                         : (tp.trace ? fwd_row_kernel<true, false> : fwd_row_kernel<false, false>);
+    const bool traced = tp.trace || tp.dump;
+    auto kernel = masked ? (traced ? fwd_row_kernel<true, true> : fwd_row_kernel<false, true>)
+                         : (traced ? fwd_row_kernel<true, false> : fwd_row_kernel<false, false>);
     if (int rc = ensure_smem(kernel, P::kBytes, "cudaFuncSetAttribute(fwd_row)")) return rc;
     const int lanes = tp.dual ? 1 : P::kStreams;
     const int64_t want = (tiles + lanes - 1) / lanes;
@@ -1010,6 +1065,12 @@ int launch_forward_row(const AttnParams& p, void* workspace, int64_t workspace_b
     cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, tp), "fwd_row launch");
 }
+
+namespace {
+DumpRequest g_dump = {nullptr, 0, 0, 0, 0};
+}
+void set_dump_request(const DumpRequest& r) { g_dump = r; }
+DumpRequest get_dump_request() { return g_dump; }
 
 // Streams (independent query tiles in flight) of the head-dim-64 forward kernel per SM of
 // the current device: 2 when a CTA fits.

@@ -7,7 +7,11 @@ reference's FLASH_PROFILE device zones (ktt_flash/compute.cpp:25-30, program.hpp
 
 Each runs the workload a few times untraced, once with a trace buffer set, and prints where
 the time of that launch went. The stamps are SM clocks (forward, per key block) or the
-global nanosecond timer (per CTA)."""
+global nanosecond timer (per CTA).
+
+`debug_flash_dump(q, k, v, is_causal, row)` is the counterpart of the reference's
+`torch.ops.ktt._debug_flash_dump` (aten_attention.cpp:814-831): the intermediate values of
+one query tile of the head-dim-64 forward, read out of the kernel's own registers."""
 
 import collections
 import statistics
@@ -171,6 +175,48 @@ def decode(dev):
         col = sorted(int(x) - t0 for x in rows[:, i] if int(x))
         if col:
             print(f"  {name:18s} ns min / median / max {col[0]} / {col[len(col) // 2]} / {col[-1]}")
+
+
+def debug_flash_dump(q, k, v, is_causal, row, scale=None):
+    """Runs the head-dim-64 tcgen05 forward on (q, k, v) [B, H, S, 64] and returns what the
+    kernel held for query tile `row` (index over B x H x query tiles of 128 rows, as in the
+    reference's op): a dict with, per key block of the tile, `x` [blocks, 128, 128] (the
+    exponents: scaled logit minus the reference maximum, -inf where the key is hidden), `p`
+    (2^x as the bf16 values fed to P V) and `m` [blocks, 2, 128] (the reference maximum of
+    each half row during the block); and `o` [128, 64] (unnormalised accumulator), `m_row`,
+    `l_row` [128] at the end of the tile, plus the launch's `out` and `lse`. Blocks the tile
+    does not have (causal) stay NaN."""
+    if q.shape[-1] != 64 or q.dim() != 4:
+        raise _lib.UnsupportedAttention("debug_flash_dump: the head-dim-64 forward only ([B, H, S, 64])")
+    b, h, s, _ = q.shape
+    tiles = (s + 127) // 128
+    blocks = (k.shape[2] + 127) // 128
+    bi, hi, ti = row // (h * tiles), (row // tiles) % h, row % tiles
+    if not 0 <= bi < b:
+        raise ValueError("debug_flash_dump: row %d of %d" % (row, b * h * tiles))
+    block_floats, tail_floats = 2 * 128 * 128 + 2 * 128, 128 * 64 + 2 * 128
+    buf = torch.full((blocks * block_floats + tail_floats,), float("nan"), dtype=torch.float32, device=q.device)
+    handle = _lib.lib()
+    if handle.ktt_b200_set_dump(buf.data_ptr(), bi, hi, ti, blocks) != 0:
+        raise RuntimeError(_lib.last_error())
+    try:
+        out, lse = ops.sdpa_forward(q, k, v, causal=is_causal, scale=scale, kernel="flash")
+        torch.cuda.synchronize(q.device)
+    finally:
+        handle.ktt_b200_set_dump(None, 0, 0, 0, 0)
+    _lib.device_status()
+    per_block = buf[:blocks * block_floats].view(blocks, block_floats)
+    tail = buf[blocks * block_floats:]
+    return {
+        "batch": bi, "head": hi, "q_tile": ti,
+        "x": per_block[:, :128 * 128].reshape(blocks, 128, 128),
+        "p": per_block[:, 128 * 128:2 * 128 * 128].reshape(blocks, 128, 128),
+        "m": per_block[:, 2 * 128 * 128:].reshape(blocks, 2, 128),
+        "o": tail[:128 * 64].view(128, 64),
+        "m_row": tail[128 * 64:128 * 64 + 128],
+        "l_row": tail[128 * 64 + 128:],
+        "out": out, "lse": lse,
+    }
 
 
 def main(argv):

@@ -217,3 +217,46 @@ def test_every_launch_gives_the_same_bits(cuda, b, h, hk, s, d, causal):
         assert torch.equal(out, other) and torch.equal(lse, other_lse)
     for other in grads[1:]:
         assert all(torch.equal(x, y) for x, y in zip(grads[0], other))
+
+
+# The dump of one query tile (the counterpart of the reference's _debug_flash_dump,
+# aten_attention.cpp:814-831) against float64: a tile the CTA's two streams share (small
+# launch) and a whole tile of one stream (1,792 tiles).
+@pytest.mark.parametrize("b,h,hk,s,tile", [(1, 4, 2, 512, (0, 3, 3)), (1, 4, 2, 512, (0, 1, 0)), (8, 14, 2, 2048, (5, 9, 11))])
+def test_debug_dump_of_one_query_tile(cuda, b, h, hk, s, tile):
+    import kohaku_tt_b200 as ktt
+
+    q, k, v = (t.to(cuda) for t in qkv(b, h, hk, s, s, 64, 21))
+    bi, hi, ti = tile
+    tiles = s // 128
+    d = ktt.debug_flash_dump(q, k, v, True, (bi * h + hi) * tiles + ti)
+    assert (d["batch"], d["head"], d["q_tile"]) == tile
+    nblk = ti + 1
+    x, pr, m = d["x"].double().cpu(), d["p"].double().cpu(), d["m"].double().cpu()
+    assert torch.isnan(x[nblk:]).all() and not torch.isnan(x[:nblk]).any()
+    assert torch.equal(m[:nblk, 0], m[:nblk, 1])   # the two halves of a row agree on the reference
+    qq = q[bi, hi, ti * 128:(ti + 1) * 128].double().cpu()
+    kk = k[bi, hi // (h // hk)].double().cpu()
+    logit2 = (qq @ kk.T) / math.sqrt(64) * math.log2(math.e)   # [128, s]
+    rows = torch.arange(128)[:, None] + ti * 128
+    l_ref = torch.zeros(128, dtype=torch.float64)
+    m_row, l_row = d["m_row"].double().cpu(), d["l_row"].double().cpu()
+    for j in range(nblk):
+        cols = torch.arange(128)[None, :] + j * 128
+        seen = cols <= rows
+        want = logit2[:, j * 128:(j + 1) * 128] - m[j, 0][:, None]
+        assert (x[j][~seen] == float("-inf")).all() and (pr[j][~seen] == 0).all()
+        assert (x[j][seen] - want[seen]).abs().max() <= 2e-3
+        # P is 2^x rounded to bf16 (MUFU or the cubic: both well inside bf16's 2^-9)
+        assert ((pr[j][seen] - torch.exp2(x[j][seen])).abs() <= 6e-3 * torch.exp2(x[j][seen]) + 1e-30).all()
+        l_ref += (torch.exp2(x[j] + m[j, 0][:, None] - m_row[:, None]) * seen).sum(dim=1)
+    assert ((l_row - l_ref).abs() <= 1e-3 * l_ref).all()
+    lse = d["lse"][bi, hi, ti * 128:(ti + 1) * 128].double().cpu()
+    assert (lse - math.log(2.0) * (m_row + torch.log2(l_row))).abs().max() <= 1e-4
+    out = d["out"][bi, hi, ti * 128:(ti + 1) * 128].double().cpu()
+    assert rel(out, d["o"].double().cpu() / l_row[:, None]) <= 3e-3   # the output is this, rounded to bf16
+    ruler = torch.softmax((logit2 * math.log(2.0)).masked_fill(torch.arange(s)[None, :] > rows, float("-inf")), dim=-1) @ v[bi, hi // (h // hk)].double().cpu()
+    assert rel(out, ruler) <= FWD_BOUND
+    # a launch after the request was cleared leaves the buffer alone and gives the same output
+    again, _ = ops.sdpa_forward(q, k, v, causal=True, kernel="flash")
+    assert torch.equal(again, d["out"])
