@@ -553,6 +553,9 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        from kohaku_tt_b200 import parallel
+
+        parallel._PeerRing.release_all()   # the ring leg's shared slots, before the processes part
         torch.distributed.destroy_process_group()
 
 

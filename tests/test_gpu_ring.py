@@ -1,5 +1,7 @@
-"""Ring attention on real GPUs (needs two): NCCL send/recv of K/V blocks, the CUDA kernels
-per block, merge by log-sum-exp; against the float64 ruler of the whole sequence."""
+"""Ring attention on real GPUs (needs two): K/V blocks pulled out of the previous rank's
+memory by device-to-device copies (the default on GPUs) and sent by NCCL send/recv (the
+fallback), the CUDA kernels per block, merge by log-sum-exp; against the float64 ruler of the
+whole sequence, and the two exchanges against each other bit for bit."""
 
 import os
 import socket
@@ -41,7 +43,19 @@ def _worker(rank, world, port, result):
         gq, gk, gv = parallel.ring_backward(doc, qc, kc, vc, out, lse)
         for got, want in ((gq, dq), (gk, dk), (gv, dv)):
             assert ktt.rel_rms(got, mine(want)) <= 2e-2
+        # The same through the process group's send / recv: the exchange moves bytes, the
+        # arithmetic is the same, twice over (a second call reuses the shared slots).
+        for _ in range(2):
+            out2, lse2 = parallel.ring_forward(qc, kc, vc, exchange="p2p")
+            again, again_lse = parallel.ring_forward(qc, kc, vc, exchange="peer")
+            assert torch.equal(out, out2) and torch.equal(lse, lse2)
+            assert torch.equal(out, again) and torch.equal(lse, again_lse)
+            grads2 = parallel.ring_backward(doc, qc, kc, vc, out, lse, exchange="p2p")
+            grads3 = parallel.ring_backward(doc, qc, kc, vc, out, lse, exchange="peer")
+            assert all(torch.equal(a, b_) for a, b_ in zip((gq, gk, gv), grads2))
+            assert all(torch.equal(a, b_) for a, b_ in zip((gq, gk, gv), grads3))
         torch.cuda.synchronize()
+        parallel._PeerRing.release_all()
         result[rank] = "ok"
     finally:
         dist.destroy_process_group()
