@@ -151,17 +151,36 @@ class _PeerRing:
         self.flat = torch.empty((2, numel), dtype=dtype, device=device)
         self.flag = torch.zeros((1,), dtype=torch.int32, device=device)
         self.copy_stream = torch.cuda.Stream(device=device)
+        self.prev_flat = None
+        # Every rank takes part in both collectives below whatever happens to it, and all
+        # ranks reach the same verdict: a ring that one rank could not set up is used by none.
+        try:
+            mine = reduce_tensor(self.flat)
+        except Exception:   # no CUDA IPC for this memory in this environment
+            mine = None
         handles = [None] * self.world
-        dist.all_gather_object(handles, reduce_tensor(self.flat), group=group)
-        rebuild, args = handles[(self.rank - 1) % self.world]
-        self.prev_flat = rebuild(*args)   # the previous rank's two slots, mapped into this process
+        dist.all_gather_object(handles, mine, group=group)
+        good = torch.ones((1,), dtype=torch.int32, device=device)
+        if any(h is None for h in handles):
+            good.zero_()
+        else:
+            try:
+                rebuild, args = handles[(self.rank - 1) % self.world]
+                self.prev_flat = rebuild(*args)   # the previous rank's two slots, mapped into this process
+            except Exception:
+                good.zero_()
+        dist.all_reduce(good, op=dist.ReduceOp.MIN, group=group)
+        self.usable = bool(good.item())
 
     @classmethod
     def get(cls, numel, dtype, device, group):
+        """The ring of this size for this group, or None where the ranks cannot read each
+        other's memory (the callers then use the process group's send / recv)."""
         key = (numel, dtype, device, id(group) if group is not None else None)
         if key not in cls._cache:
             cls._cache[key] = cls(numel, dtype, device, group)
-        return cls._cache[key]
+        ring = cls._cache[key]
+        return ring if ring.usable else None
 
     @classmethod
     def release_all(cls):
@@ -245,6 +264,9 @@ def ring_forward(q, k, v, group=None, scale=None, attend=None, merge=None, excha
     if world > 1 and (exchange == "peer" or (exchange == "auto" and q.is_cuda and k.dtype == v.dtype)):
         # One flat buffer per slot: K then V.
         peer = _PeerRing.get(k.numel() + v.numel(), k.dtype, k.device, group)
+        if peer is None and exchange == "peer":
+            raise RuntimeError("ring_forward: the ranks cannot read each other's memory (CUDA IPC)")
+    if peer is not None:
         peer.flat[0, :k.numel()].view(k.shape).copy_(k)
         peer.flat[0, k.numel():].view(v.shape).copy_(v)
         peer.barrier()   # every rank's slot 0 is filled, and nobody still works on an earlier call
@@ -282,7 +304,7 @@ def ring_forward(q, k, v, group=None, scale=None, attend=None, merge=None, excha
     return out, torch.cat(acc_lse, dim=2)
 
 
-def _ring_backward_peer(dout, q, k, v, out, lse, group, scale, attend_backward):
+def _ring_backward_peer(dout, q, k, v, out, lse, group, scale, attend_backward, rings):
     """ring_backward with the blocks and the accumulators pulled out of the previous rank's
     memory (`_PeerRing`). Slot s % 2 of the accumulator ring holds, after step s, the sum of
     the contributions of every rank that has held the block this rank holds at step s; the
@@ -297,8 +319,7 @@ def _ring_backward_peer(dout, q, k, v, out, lse, group, scale, attend_backward):
     lh = [lse[:, :, :c].contiguous(), lse[:, :, c:].contiguous()]
     dq = [torch.zeros(qh[0].shape, dtype=torch.float32, device=dev) for _ in range(2)]
     nk, nv = k.numel(), v.numel()
-    blocks = _PeerRing.get(nk + nv, k.dtype, dev, group)
-    sums = _PeerRing.get(nk + nv, torch.float32, dev, group)
+    blocks, sums = rings
     arrived = torch.empty((nk + nv,), dtype=torch.float32, device=dev)   # the previous rank's sums for the block in hand
     blocks.flat[0, :nk].view(k.shape).copy_(k)
     blocks.flat[0, nk:].view(v.shape).copy_(v)
@@ -347,7 +368,12 @@ def ring_backward(dout, q, k, v, out, lse, group=None, scale=None, attend_backwa
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if world > 1 and (exchange == "peer" or (exchange == "auto" and q.is_cuda and k.dtype == v.dtype)):
-        return _ring_backward_peer(dout, q, k, v, out, lse, group, scale, attend_backward)
+        n = k.numel() + v.numel()
+        rings = (_PeerRing.get(n, k.dtype, q.device, group), _PeerRing.get(n, torch.float32, q.device, group))
+        if rings[0] is not None and rings[1] is not None:
+            return _ring_backward_peer(dout, q, k, v, out, lse, group, scale, attend_backward, rings)
+        if exchange == "peer":
+            raise RuntimeError("ring_backward: the ranks cannot read each other's memory (CUDA IPC)")
     c = q.shape[2] // 2
     halves = lambda t: [t[:, :, :c].contiguous(), t[:, :, c:].contiguous()]
     qh, doh, oh = halves(q), halves(dout), halves(out)
