@@ -547,8 +547,10 @@ def run_ours(args):
     if world > 1 and not args.headline_only:
         extra = sharded_legs(dev, peaks, rank, world, warmup)
         ring = ring_leg(dev, peaks, rank, world)
+        copies = host_copies_leg(dev, rank, world)
         if rank == 0:
             extra["ring_attention"] = ring
+            extra["host_copies"] = copies
             line["extra"] = extra
     if rank == 0:
         print(json.dumps(line))
@@ -565,6 +567,59 @@ def _max_min_over_ranks(ms, dev):
     t = torch.tensor([ms, -ms], dtype=torch.float64, device=dev)
     torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     return t[0].item(), -t[1].item()
+
+
+def host_copies_leg(dev, rank, world):
+    """Where the end-to-end rate of N ranks goes: the headline step's host-to-device and
+    device-to-host copies alone (pinned buffers, one stream each way, no kernel), run by all
+    ranks at once, by one rank at a time and by subsets. One rank alone shows what a GPU's
+    link gives; the growth with the number of active ranks is the host's share (PCIe switches,
+    root complex, memory), which no kernel can buy back."""
+    import time
+
+    c = HEADLINE
+    n_in = c["batch"] * (c["heads"] + 2 * c["kv_heads"]) * c["seq"] * c["head_dim"]
+    n_out = c["batch"] * c["heads"] * c["seq"] * c["head_dim"]
+    hin, hout = torch.empty((n_in,), dtype=torch.bfloat16).pin_memory(), torch.empty((n_out,), dtype=torch.bfloat16).pin_memory()
+    hin.fill_(1)
+    hout.fill_(1)
+    din, dout = torch.empty((n_in,), dtype=torch.bfloat16, device=dev), torch.empty((n_out,), dtype=torch.bfloat16, device=dev)
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def loop(steps, h2d, d2h):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            if h2d:
+                with torch.cuda.stream(s_in):
+                    din.copy_(hin, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s_out):
+                    hout.copy_(dout, non_blocking=True)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / steps * 1e6
+
+    def case(active, h2d=True, d2h=True):
+        torch.distributed.barrier()
+        us = loop(200, h2d, d2h) if rank in active else 0.0
+        t = torch.tensor([us], dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return round(t.item(), 1)
+
+    loop(20, True, True)
+    everyone = set(range(world))
+    out = {
+        "unit": "us per step on the slowest active rank (4.72 MB in, 3.67 MB out per rank and step)",
+        "all_ranks": case(everyone),
+        "all_ranks_h2d_only": case(everyone, d2h=False),
+        "all_ranks_d2h_only": case(everyone, h2d=False),
+        "one_rank_alone": [case({r}) for r in sorted({0, world // 2, world - 1})],
+    }
+    if world >= 4:
+        out["first_two_ranks"] = case({0, 1})
+        out["first_half_of_the_ranks"] = case(set(range(world // 2)))
+        out["every_other_rank"] = case(set(range(0, world, 2)))
+    return out
 
 
 def sharded_legs(dev, peaks, rank, world, warmup):
