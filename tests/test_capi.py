@@ -75,6 +75,14 @@ def test_null_pointers_are_rejected_before_any_launch(built_lib):
     assert built_lib.ktt_b200_merge_partials(None, None, None, None, 4, 64, 0, None) == _lib.ERR_BAD_ARGUMENT
 
 
+def test_dump_request_checks_its_arguments(built_lib):
+    # Setting and clearing the request is host state only; nothing is launched.
+    fake = ctypes.c_void_p(4096)
+    assert built_lib.ktt_b200_set_dump(fake, -1, 0, 0, 4) == _lib.ERR_BAD_ARGUMENT
+    assert built_lib.ktt_b200_set_dump(fake, 0, 0, 0, 0) == _lib.ERR_BAD_ARGUMENT
+    assert built_lib.ktt_b200_set_dump(None, 0, 0, 0, 0) == 0
+
+
 def test_backward_workspace_size(built_lib):
     # One fp32 per (batch, head, query row), rows padded to 64 ...
     delta = 2 * 4 * 128 * 4
