@@ -560,13 +560,11 @@ __device__ __forceinline__ void dkv_body(
                     }
                 } else if (real) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 v;
-                        v.x = pack_bf16(o[e * 8 + 0] * mul, o[e * 8 + 1] * mul);
-                        v.y = pack_bf16(o[e * 8 + 2] * mul, o[e * 8 + 3] * mul);
-                        v.z = pack_bf16(o[e * 8 + 4] * mul, o[e * 8 + 5] * mul);
-                        v.w = pack_bf16(o[e * 8 + 6] * mul, o[e * 8 + 7] * mul);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = v;
+                    for (int e = 0; e < 2; ++e) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) w[i] = pack_bf16(o[e * 16 + 2 * i] * mul, o[e * 16 + 2 * i + 1] * mul);
+                        store_32_bytes(dst + c * 32 + e * 16, w);
                     }
                 }
             }
@@ -962,13 +960,11 @@ __device__ __forceinline__ void dq_body(
                 }
                 if (real) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 v;
-                        v.x = pack_bf16(o[e * 8 + 0] * p.scale, o[e * 8 + 1] * p.scale);
-                        v.y = pack_bf16(o[e * 8 + 2] * p.scale, o[e * 8 + 3] * p.scale);
-                        v.z = pack_bf16(o[e * 8 + 4] * p.scale, o[e * 8 + 5] * p.scale);
-                        v.w = pack_bf16(o[e * 8 + 6] * p.scale, o[e * 8 + 7] * p.scale);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = v;
+                    for (int e = 0; e < 2; ++e) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) w[i] = pack_bf16(o[e * 16 + 2 * i] * p.scale, o[e * 16 + 2 * i + 1] * p.scale);
+                        store_32_bytes(dst + c * 32 + e * 16, w);
                     }
                 }
             }

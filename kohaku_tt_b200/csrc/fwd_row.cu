@@ -891,18 +891,10 @@ __global__ void __launch_bounds__(RowPlan::kThreads, 1) fwd_row_kernel(
                 // instructions, and with it the time the load/store unit spends on the tile
                 // (measured: 1,560 clk from the final values to the stores' issue with four
                 // 16-byte stores per thread).
-                if ((reinterpret_cast<uintptr_t>(og) & 31) == 0) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                                     ::"l"(og + c * 16), "r"(w[c * 8]), "r"(w[c * 8 + 1]), "r"(w[c * 8 + 2]), "r"(w[c * 8 + 3]),
-                                       "r"(w[c * 8 + 4]), "r"(w[c * 8 + 5]), "r"(w[c * 8 + 6]), "r"(w[c * 8 + 7]) : "memory");
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        *reinterpret_cast<uint4*>(og + c * 8) = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
-                    }
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t part[8] = {w[c * 8], w[c * 8 + 1], w[c * 8 + 2], w[c * 8 + 3], w[c * 8 + 4], w[c * 8 + 5], w[c * 8 + 6], w[c * 8 + 7]};
+                    store_32_bytes(og + c * 16, part);
                 }
                 if (group == 0 && p.lse) {
                     p.lse[k.b * p.ls[0] + k.h * p.ls[1] + (si.q_off + qi) * p.ls[2]] =

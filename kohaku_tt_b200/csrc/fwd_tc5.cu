@@ -757,13 +757,11 @@ __global__ void __launch_bounds__(Plan<D>::kThreads, 1) fwd_tc5_kernel(
                     }
                     if (real) {
 #pragma unroll
-                        for (int e = 0; e < kChunk / 8; ++e) {
-                            uint4 v;
-                            v.x = pack_bf16(acc[e * 8 + 0], acc[e * 8 + 1]);
-                            v.y = pack_bf16(acc[e * 8 + 2], acc[e * 8 + 3]);
-                            v.z = pack_bf16(acc[e * 8 + 4], acc[e * 8 + 5]);
-                            v.w = pack_bf16(acc[e * 8 + 6], acc[e * 8 + 7]);
-                            *reinterpret_cast<uint4*>(og + c * kChunk + e * 8) = v;
+                        for (int e = 0; e < kChunk / 16; ++e) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) w[i] = pack_bf16(acc[e * 16 + 2 * i], acc[e * 16 + 2 * i + 1]);
+                            store_32_bytes(og + c * kChunk + e * 16, w);
                         }
                     }
                 }

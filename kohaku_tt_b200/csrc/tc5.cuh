@@ -66,6 +66,20 @@ __device__ __forceinline__ int mod_by(int n, const Divisor& f) {
     return n - div_by(n, f) * static_cast<int>(f.d);
 }
 
+// Sixteen bf16 values (eight packed words) to global memory: one 32-byte store where the
+// address allows it, else two 16-byte ones. A thread that owns a row of a tile writes into a
+// line of its own, so the load/store unit's time on the tile goes with the number of store
+// instructions, not with their width.
+__device__ __forceinline__ void store_32_bytes(void* dst, const uint32_t (&w)[8]) {
+    if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+    } else {
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
 // Bounded wait. Returns false when it gave up (its own limit, or another role's).
 __device__ __noinline__ inline bool mbar_wait_slow(
     uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int* status, long long limit = kWaitCycles) {
