@@ -304,45 +304,74 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
             if (ticket == parts - 1) p.counters[e[1]] = 0;  // all holders have drawn
         }
         __syncthreads();
-        // All pairs this CTA finishes, flattened so that their loads are in flight together.
+        // All pairs this CTA finishes, flattened, two positions per thread at a time: the
+        // partials of four holders for both positions are requested before any is used, so
+        // a thread waits for L2 once per two positions and four holders. (One position at a
+        // time, every position's loads waited for the previous position's sums: with two
+        // pairs to finish that was four trips to L2 in a row behind the slowest stream.)
         const int per_pair = rows * (D / 4);
-        for (int idx = threadIdx.x; idx < n * per_pair; idx += kThreads) {
-            const int i = idx / per_pair;
-            if (!last_s[i]) continue;
-            const int* e = pend + 5 * i;
-            const int pair = e[0], c_first = e[1], c_last = e[2];
-            const int r = (idx % per_pair) / (D / 4), c4 = idx % (D / 4);
-            // Running merge in CTA order (deterministic). The partials of four holders are
-            // requested together before any is used: one trip to L2 per four holders, not one
-            // per holder.
-            float mm = -INFINITY, ll = 0.f;
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int c0 = c_first; c0 <= c_last; c0 += 4) {
-                float ms[4], ls[4];
-                float4 v[4];
+        constexpr int kIlp = 2;
+        for (int base = 0; base < n * per_pair; base += kIlp * kThreads) {
+            bool act[kIlp];
+            int r_[kIlp], c4_[kIlp], slot0[kIlp], parts[kIlp], b_[kIlp], hk_[kIlp];
+            float mm[kIlp], ll[kIlp];
+            float4 sum[kIlp];
+            int most = 0;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int slot = min(c0 + j, c_last) + pair;   // past the last holder: a repeat, not used
-                    ms[j] = __ldcg(&p.part_m[slot * 16 + r]);
-                    ls[j] = __ldcg(&p.part_l[slot * 16 + r]);
-                    v[j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (static_cast<int64_t>(slot) * 16 + r) * D + c4 * 4));
+            for (int u = 0; u < kIlp; ++u) {
+                const int idx = base + u * kThreads + static_cast<int>(threadIdx.x);
+                const int i = idx < n * per_pair ? idx / per_pair : 0;
+                act[u] = idx < n * per_pair && last_s[i];
+                const int* e = pend + 5 * i;
+                const int rem = idx - i * per_pair;
+                r_[u] = rem / (D / 4);
+                c4_[u] = rem % (D / 4);
+                slot0[u] = e[1] + e[0];           // first holder's slot: first CTA + pair
+                parts[u] = act[u] ? e[2] - e[1] + 1 : 0;
+                b_[u] = e[3];
+                hk_[u] = e[4];
+                mm[u] = -INFINITY;
+                ll[u] = 0.f;
+                sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                most = max(most, parts[u]);
+            }
+            // Running merge in CTA order (deterministic), four holders per round.
+            for (int c0 = 0; c0 < most; c0 += 4) {
+                float ms[kIlp][4], ls[kIlp][4];
+                float4 v[kIlp][4];
+#pragma unroll
+                for (int u = 0; u < kIlp; ++u) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // Past the last holder (or an idle position): a repeat of a valid slot, not used.
+                        const int slot = slot0[u] + max(min(c0 + j, parts[u] - 1), 0);
+                        ms[u][j] = __ldcg(&p.part_m[slot * 16 + r_[u]]);
+                        ls[u][j] = __ldcg(&p.part_l[slot * 16 + r_[u]]);
+                        v[u][j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (static_cast<int64_t>(slot) * 16 + r_[u]) * D + c4_[u] * 4));
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (c0 + j <= c_last) {
-                        const float m_new = fmaxf(mm, ms[j]);
-                        const float base = (m_new == -INFINITY) ? 0.f : m_new;
-                        const float fa = fast_exp2(mm - base), fb = fast_exp2(ms[j] - base);
-                        ll = ll * fa + ls[j] * fb;
-                        sum.x = sum.x * fa + v[j].x * fb;
-                        sum.y = sum.y * fa + v[j].y * fb;
-                        sum.z = sum.z * fa + v[j].z * fb;
-                        sum.w = sum.w * fa + v[j].w * fb;
-                        mm = m_new;
+                for (int u = 0; u < kIlp; ++u) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (c0 + j < parts[u]) {
+                            const float m_new = fmaxf(mm[u], ms[u][j]);
+                            const float base_m = (m_new == -INFINITY) ? 0.f : m_new;
+                            const float fa = fast_exp2(mm[u] - base_m), fb = fast_exp2(ms[u][j] - base_m);
+                            ll[u] = ll[u] * fa + ls[u][j] * fb;
+                            sum[u].x = sum[u].x * fa + v[u][j].x * fb;
+                            sum[u].y = sum[u].y * fa + v[u][j].y * fb;
+                            sum[u].z = sum[u].z * fa + v[u][j].z * fb;
+                            sum[u].w = sum[u].w * fa + v[u][j].w * fb;
+                            mm[u] = m_new;
+                        }
                     }
                 }
             }
-            write_row(e[3], e[4], r, c4, sum, mm, ll);
+#pragma unroll
+            for (int u = 0; u < kIlp; ++u) {
+                if (act[u]) write_row(b_[u], hk_[u], r_[u], c4_[u], sum[u], mm[u], ll[u]);
+            }
         }
         __syncthreads();
         if (threadIdx.x == 0) npend_s[0] = 0;
