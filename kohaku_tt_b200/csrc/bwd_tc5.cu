@@ -922,7 +922,7 @@ __device__ __forceinline__ void dq_body(
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     float2 a = __fmul2_rn(pv[c * 16 + e], __fadd2_rn(make_float2(dp[2 * e], dp[2 * e + 1]), nd2));
-                    if (!whole) {   // hidden keys: exactly 0 whatever dP holds there
+                    if (!whole_w) {   // hidden keys: exactly 0 whatever dP holds there (a warp-wide test: no selects in whole tiles)
                         a.x = c * 32 + 2 * e < limit ? a.x : 0.f;
                         a.y = c * 32 + 2 * e + 1 < limit ? a.y : 0.f;
                     }
