@@ -69,13 +69,14 @@ constexpr int kTile = 64;      // keys per tile (16 per warp)
 constexpr int kThreads = 128;
 constexpr int kMaxBatch = 512;   // clamped lengths and their prefix sums live in shared memory
 constexpr int kMaxPending = 8;   // stored partials per CTA before their tickets are drawn
-// Ending a (batch, kv head) pair costs a CTA about as much as streaming four tiles (the four
+// Ending a (batch, kv head) pair costs a CTA about as much as streaming five tiles (the four
 // warps' states are merged, the result or a partial is written, a ticket may be drawn, the
 // next pair's query is fetched): the shares are cut in units in which a pair's last tile
 // weighs 1 + kPairCost. Measured on B 64, lengths U[512, 4096], D 128: 36.3, 35.4, 35.0,
-// 34.6, 34.5, 34.9 us for a cost of 1 to 6.
+// 34.6, 34.5, 34.9 us for a cost of 1 to 6 with every ticket drawn at a CTA's end; 34.95,
+// 34.25, 33.8, 34.4 us for 3 to 6 with a finished pair's ticket drawn in mid-stream.
 #ifndef KTT_DECODE_PAIR_COST
-#define KTT_DECODE_PAIR_COST 4
+#define KTT_DECODE_PAIR_COST 5
 #endif
 constexpr int kPairCost = KTT_DECODE_PAIR_COST;
 constexpr int kMaxCtas = 1024;   // ticket counters in the scratch
@@ -652,8 +653,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                     write_row(cons.b, cons.hk, r, c4, merged(r, c4), fin_m[r], fin_l[r]);
                 }
             } else {
-                // Store the partial; the ticket is drawn at the end of the CTA so that the
-                // stream is not held up by a device-wide fence in the middle.
+                // Store the partial and note the ticket to draw.
                 const int slot = blockIdx.x + pair;
                 float4* dst = reinterpret_cast<float4*>(p.part_o + static_cast<int64_t>(slot) * 16 * D);
                 for (int idx = threadIdx.x; idx < rows * D / 4; idx += kThreads) dst[idx] = merged(idx / (D / 4), idx % (D / 4));
@@ -667,7 +667,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_kernel(const DecodeParams 
                     npend_s[0] += 1;
                 }
                 __syncthreads();
-                if (npend_s[0] == kMaxPending) draw_tickets();
+                // A pair that ends in the middle of this CTA's share draws its ticket now: the
+                // other holder of that pair is then almost always the last one, so a CTA ends
+                // with one pair to merge, not with whichever pairs it happened to finish last
+                // (the three-stage ring rides out the fence; measured 34.6 -> 34.25 us, and
+                // 33.8 us with the pair cost re-swept).
+                if (npend_s[0] == kMaxPending || u + 1 < u1) draw_tickets();
             }
             __syncthreads();
             fresh = true;
